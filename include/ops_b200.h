@@ -1,0 +1,331 @@
+/*
+ * ops_b200.h — flat C ABI of the B200 (sm_100a) operator library.
+ *
+ * Every entry point mirrors one item of the operators-rs crate's per-operator interface
+ * (`trait Operator { new; scheme; launch }`, operators/src/lib.rs:105-144) so that a Rust
+ * `impl Operator` can bind it one to one:
+ *
+ *     Operator::new(node)                   -> ops_<op>_create(device|topo, &handle)
+ *     Operator::scheme(args, max_workspace) -> ops_<op>_scheme(handle, &args, max_ws, &ws_out)
+ *     Operator::launch(args, workspace, qa) -> ops_<op>_launch(handle, &args, ws, ws_len, stream)
+ *     Drop                                  -> ops_<op>_destroy(handle)
+ *
+ * Conventions
+ *   - All tensor base pointers are DEVICE pointers; `stream` is a `cudaStream_t` passed as `void*`.
+ *     `launch` only enqueues on that stream (same contract as the crate's GPU backends).
+ *   - Layouts carry BYTE strides (operators/src/common/tensor.rs:10-47).
+ *   - "Dynamic" values (operators/src/common/maybe_dyn.rs:6-37): shape == SIZE_MAX,
+ *     stride == PTRDIFF_MAX, float == +inf, pointer == NULL.  `scheme` accepts them,
+ *     `launch` answers OPS_DYNAMIC_NOT_SUPPORT.
+ *   - Return value: 0 on success, else the error kind below; a human readable message for the
+ *     calling thread is available from ops_last_error().  Nothing throws, nothing aborts.
+ *   - Workspace: `scheme` reports the bytes `launch` wants (never more than `max_ws`, 0 if unknown,
+ *     operators/src/lib.rs:116-131).  `launch` with a shorter workspace answers
+ *     OPS_WORKSPACE_TOO_SMALL and ops_last_workspace_need() tells the size; the caller's allocator
+ *     (the crate's `Workspace::new` fallback, operators/src/common/workspace.rs:12-21) provides it
+ *     and calls again.  The library itself never allocates device memory in `launch`.
+ *   - There is no CPU path: without a CUDA device `create` fails with OPS_EXECUTION_FAILED.
+ */
+#ifndef OPS_B200_H
+#define OPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error kinds: SchemeErrorKind order of operators/src/common/error.rs:2-12, then
+ *      LaunchErrorKind::ExecutionFailed (:21-25) ---- */
+enum {
+  OPS_OK = 0,
+  OPS_TYPE_NOT_SUPPORT = 1,
+  OPS_TYPE_MISMATCH = 2,
+  OPS_RANK_NOT_SUPPORT = 3,
+  OPS_RANK_MISMATCH = 4,
+  OPS_SHAPE_NOT_SUPPORT = 5,
+  OPS_SHAPE_MISMATCH = 6,
+  OPS_STRIDES_NOT_SUPPORT = 7,
+  OPS_ARGS_NOT_SUPPORT = 8,
+  OPS_DYNAMIC_NOT_SUPPORT = 9,
+  OPS_EXECUTION_FAILED = 100,
+  OPS_WORKSPACE_TOO_SMALL = 101 /* not an error of the crate: the shim allocates and retries */
+};
+
+/* ---- element types (the subset of digit-layout's types the path uses) ---- */
+enum {
+  OPS_DT_F16 = 1,
+  OPS_DT_BF16 = 2,
+  OPS_DT_F32 = 3,
+  OPS_DT_F64 = 4,
+  OPS_DT_U8 = 5,
+  OPS_DT_U16 = 6,
+  OPS_DT_U32 = 7,
+  OPS_DT_U64 = 8,
+  OPS_DT_I8 = 9,
+  OPS_DT_I16 = 10,
+  OPS_DT_I32 = 11,
+  OPS_DT_I64 = 12,
+  OPS_DT_KVPAIR = 13 /* KVPair::LAYOUT = u32 x 2, operators/src/random_sample/kv_pair.rs:8-17 */
+};
+
+#define OPS_DYN_SIZE ((size_t)-1)          /* usize::MAX */
+#define OPS_DYN_STRIDE ((ptrdiff_t)(((size_t)-1) >> 1)) /* isize::MAX */
+
+/* TensorLayout (operators/src/common/tensor.rs:10-98): dtype, rank, shape, byte strides. */
+typedef struct {
+  uint32_t dt;
+  uint32_t ndim;
+  const size_t *shape;
+  const ptrdiff_t *strides;
+} ops_layout;
+
+/* AttnMask (operators/src/fuesd_softmax/args.rs:11-16) */
+enum { OPS_MASK_NONE = 0, OPS_MASK_CAUSAL = 1 };
+/* ReduceOp (operators/src/all_reduce/mod.rs:14-22) */
+enum { OPS_REDUCE_SUM = 0, OPS_REDUCE_PROD = 1, OPS_REDUCE_MIN = 2, OPS_REDUCE_MAX = 3, OPS_REDUCE_MEAN = 4 };
+
+const char *ops_last_error(void);          /* message of the calling thread's last failure */
+size_t ops_last_workspace_need(void);      /* bytes wanted by the calling thread's last OPS_WORKSPACE_TOO_SMALL */
+size_t ops_dtype_nbytes(uint32_t dt);      /* digit_layout::DigitLayout::nbytes */
+int ops_device_count(void);                /* 0 when there is no usable CUDA device */
+const char *ops_build_info(void);          /* "sm_100a ..." */
+
+/* ---------------------------------------------------------------------------------------------
+ * rms_norm — rms_norm::Args (operators/src/rms_norm/args.rs:7-15); replaces
+ * rms_norm::common_cpu::Operator (operators/src/rms_norm/common_cpu/mod.rs:10-93).
+ * y[i,j] = x[i,j] * w[j] / sqrt(mean_j(x[i,:]^2) + epsilon); y,x f16 or f32, w f16 or f32.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_rms_norm ops_rms_norm;
+typedef struct {
+  ops_layout y_layout; void *y_base;
+  ops_layout x_layout; const void *x_base;
+  ops_layout w_layout; const void *w_base;
+  float epsilon;
+} ops_rms_norm_args;
+int ops_rms_norm_create(int device, ops_rms_norm **out);
+int ops_rms_norm_scheme(ops_rms_norm *op, const ops_rms_norm_args *args, size_t max_ws, size_t *ws_out);
+int ops_rms_norm_launch(const ops_rms_norm *op, const ops_rms_norm_args *args, void *ws, size_t ws_len, void *stream);
+void ops_rms_norm_destroy(ops_rms_norm *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * rope — rope::Args (operators/src/rope/args.rs:8-18); replaces rope::common_cpu::Operator
+ * (operators/src/rope/common_cpu/mod.rs:10-130).  In place on t [nt, nh, dh], adjacent pairs
+ * (2k, 2k+1), angle = pos / theta^(k/(dh/2)).  sin/cos layouts are validated and otherwise unused,
+ * exactly as on the crate's CPU path.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_rope ops_rope;
+typedef struct {
+  ops_layout t_layout; void *t_base;
+  ops_layout p_layout; const void *p_base;
+  ops_layout sin_layout; const void *sin_base;
+  ops_layout cos_layout; const void *cos_base;
+  float theta;
+} ops_rope_args;
+int ops_rope_create(int device, ops_rope **out);
+int ops_rope_scheme(ops_rope *op, const ops_rope_args *args, size_t max_ws, size_t *ws_out);
+int ops_rope_launch(const ops_rope *op, const ops_rope_args *args, void *ws, size_t ws_len, void *stream);
+void ops_rope_destroy(ops_rope *op);
+/* Rope::build_pos (operators/src/rope/mod.rs:17-21, fill_pos :44-58): writes, for every (pos,len)
+ * sequence in order, pos..pos+len into a HOST buffer of `nt` u32 or u64; the caller uploads it. */
+int ops_rope_build_pos(uint32_t dt, size_t nt, const size_t *seq_pos, const size_t *seq_len, size_t nseq, void *host_out);
+
+/* ---------------------------------------------------------------------------------------------
+ * fused_softmax — fuesd_softmax::Args (operators/src/fuesd_softmax/args.rs:5-16); replaces
+ * fuesd_softmax::common_cpu::Operator (operators/src/fuesd_softmax/common_cpu/mod.rs:9-82).
+ * In place over the last dim of att [nh, seq, att]; causal row k keeps att - seq + k + 1 entries.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_fused_softmax ops_fused_softmax;
+typedef struct {
+  uint8_t att_mask;
+  ops_layout att_layout; void *att_base;
+} ops_fused_softmax_args;
+int ops_fused_softmax_create(int device, ops_fused_softmax **out);
+int ops_fused_softmax_scheme(ops_fused_softmax *op, const ops_fused_softmax_args *args, size_t max_ws, size_t *ws_out);
+int ops_fused_softmax_launch(const ops_fused_softmax *op, const ops_fused_softmax_args *args, void *ws, size_t ws_len, void *stream);
+void ops_fused_softmax_destroy(ops_fused_softmax *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * swiglu — swiglu::Args (operators/src/swiglu/args.rs:7-12); replaces
+ * swiglu::common_cpu::Operator (operators/src/swiglu/common_cpu/mod.rs:9-81).
+ * gate <- gate * sigmoid(gate) * up, in place on gate.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_swiglu ops_swiglu;
+typedef struct {
+  ops_layout gate_layout; void *gate_base;
+  ops_layout up_layout; const void *up_base;
+} ops_swiglu_args;
+int ops_swiglu_create(int device, ops_swiglu **out);
+int ops_swiglu_scheme(ops_swiglu *op, const ops_swiglu_args *args, size_t max_ws, size_t *ws_out);
+int ops_swiglu_launch(const ops_swiglu *op, const ops_swiglu_args *args, void *ws, size_t ws_len, void *stream);
+void ops_swiglu_destroy(ops_swiglu *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * rearrange — rearrange::Args (operators/src/rearrange/args.rs:11-17); replaces
+ * rearrange::common_cpu::Operator (operators/src/rearrange/common_cpu/mod.rs:8-59).
+ * Byte-exact strided copy of any rank and dtype; src stride 0 broadcasts.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_rearrange ops_rearrange;
+typedef struct {
+  ops_layout dst_layout; void *dst_base;
+  ops_layout src_layout; const void *src_base;
+} ops_rearrange_args;
+int ops_rearrange_create(int device, ops_rearrange **out);
+int ops_rearrange_scheme(ops_rearrange *op, const ops_rearrange_args *args, size_t max_ws, size_t *ws_out);
+int ops_rearrange_launch(const ops_rearrange *op, const ops_rearrange_args *args, void *ws, size_t ws_len, void *stream);
+void ops_rearrange_destroy(ops_rearrange *op);
+/* rearrange::Scheme::new (operators/src/rearrange/args.rs:34-153) as host arithmetic: writes
+ * [unit, idx_strides(count first)…, 1, dst_strides…, src_strides…] (2 + 3*ndim words) to `out`
+ * (capacity `cap` words) and the merged rank to *ndim_out.  No device needed. */
+int ops_rearrange_plan(const ops_rearrange_args *args, ptrdiff_t *out, size_t cap, size_t *ndim_out);
+
+/* ---------------------------------------------------------------------------------------------
+ * mat_mul — mat_mul::Args (operators/src/mat_mul/args.rs:11-20); replaces
+ * mat_mul::common_cpu::Operator (operators/src/mat_mul/common_cpu/mod.rs:9-107).
+ * C <- beta*C + alpha*A*B, rank 2 or 3 (one batch dim, batch 1 broadcasts), every matrix with a
+ * unit stride in one of its two dims.  f16 runs on tcgen05 tensor cores with f32 accumulation.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_mat_mul ops_mat_mul;
+typedef struct {
+  ops_layout c_layout; void *c_base;
+  float beta;
+  ops_layout a_layout; const void *a_base;
+  ops_layout b_layout; const void *b_base;
+  float alpha;
+} ops_mat_mul_args;
+int ops_mat_mul_create(int device, ops_mat_mul **out);
+int ops_mat_mul_scheme(ops_mat_mul *op, const ops_mat_mul_args *args, size_t max_ws, size_t *ws_out);
+int ops_mat_mul_launch(const ops_mat_mul *op, const ops_mat_mul_args *args, void *ws, size_t ws_len, void *stream);
+void ops_mat_mul_destroy(ops_mat_mul *op);
+/* 0, or which bounded wait inside the tensor-core kernel ran out (1 producer, 2/3 issuer, 4 epilogue).
+ * Synchronises the device: for tests and post-mortems.  No counterpart in the crate. */
+int ops_mat_mul_status(const ops_mat_mul *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * attention — attention::Args (operators/src/attention/args.rs:10-24); replaces
+ * attention::Operator<Cpu, …> (operators/src/attention/operator.rs:9-277).
+ * o = softmax_mask(q k^T / sqrt(dh)) v with grouped-query heads; q [nh,seq,dh], k,v [nkvh,att,dh].
+ * As in the crate, q may be overwritten when its (nh, seq) dims are mergeable.
+ * `algo`: 0 = the crate's own chain (rearrange, mat_mul, fused_softmax, mat_mul, rearrange) with
+ * the score matrix in workspace; 1 = one fused flash-attention kernel (no score matrix).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_attention ops_attention;
+typedef struct {
+  ops_layout q_layout; void *q_base;
+  ops_layout k_layout; const void *k_base;
+  ops_layout v_layout; const void *v_base;
+  ops_layout o_layout; void *o_base;
+  uint8_t mask;
+} ops_attention_args;
+enum { OPS_ATTENTION_CHAIN = 0, OPS_ATTENTION_FUSED = 1 };
+int ops_attention_create(int device, ops_attention **out);
+int ops_attention_set_algo(ops_attention *op, int algo);
+int ops_attention_scheme(ops_attention *op, const ops_attention_args *args, size_t max_ws, size_t *ws_out);
+int ops_attention_launch(const ops_attention *op, const ops_attention_args *args, void *ws, size_t ws_len, void *stream);
+void ops_attention_destroy(ops_attention *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * attention_kv_cached — attention_kv_cached::Args (operators/src/attention_kv_cached/args.rs:8-30);
+ * replaces attention_kv_cached::Operator (operators/src/attention_kv_cached/operator.rs:76-183).
+ * Copies k,v into the caches at [pos, pos+seq) and attends over cache rows [0, pos+seq).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_attention_kv_cached ops_attention_kv_cached;
+typedef struct {
+  ops_layout q_layout; void *q_base;
+  ops_layout k_layout; const void *k_base;
+  ops_layout v_layout; const void *v_base;
+  ops_layout o_layout; void *o_base;
+  ops_layout k_cache_layout; void *k_cache_base;
+  ops_layout v_cache_layout; void *v_cache_base;
+  uint8_t mask;
+  size_t pos;
+} ops_attention_kv_cached_args;
+int ops_attention_kv_cached_create(int device, ops_attention_kv_cached **out);
+int ops_attention_kv_cached_set_algo(ops_attention_kv_cached *op, int algo);
+int ops_attention_kv_cached_scheme(ops_attention_kv_cached *op, const ops_attention_kv_cached_args *args, size_t max_ws, size_t *ws_out);
+int ops_attention_kv_cached_launch(const ops_attention_kv_cached *op, const ops_attention_kv_cached_args *args, void *ws, size_t ws_len, void *stream);
+void ops_attention_kv_cached_destroy(ops_attention_kv_cached *op);
+
+/* ---------------------------------------------------------------------------------------------
+ * random_sample — random_sample::Args, SampleArgs (operators/src/random_sample/args.rs:9-84);
+ * replaces random_sample::common_cpu::Operator (operators/src/random_sample/common_cpu/mod.rs:11-144).
+ * One row of logits (f16 or f32, contiguous) -> one KVPair {u32 idx, u32 val-bits}.
+ * argmax when temperature == 0 or top_k == 1 (last index among equal maxima, val = the logit);
+ * otherwise seeded sampling where `seed` is the caller's uniform draw in [0,1) and val = the
+ * cumulative mass at the chosen entry converted to the logit type.
+ * `indices` is accepted for signature parity and never read (as on the crate's CPU path).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_random_sample ops_random_sample;
+typedef struct {
+  float temperature;
+  float top_p;
+  size_t top_k;
+} ops_sample_args;
+typedef struct {
+  ops_layout kv_pair; void *kv_pair_base;
+  ops_layout logits; const void *logits_base;
+  ops_layout indices; const void *indices_base;
+  ops_sample_args config;
+  float seed;
+} ops_random_sample_args;
+/* SampleArgs::new (operators/src/random_sample/args.rs:66-78): 0 ok (top_p clamped to <= 1),
+ * 1 NegativeTemperature, 2 NonPositiveTop. */
+int ops_sample_args_new(float temperature, float top_p, size_t top_k, ops_sample_args *out);
+int ops_random_sample_create(int device, ops_random_sample **out);
+int ops_random_sample_scheme(ops_random_sample *op, const ops_random_sample_args *args, size_t max_ws, size_t *ws_out);
+int ops_random_sample_launch(const ops_random_sample *op, const ops_random_sample_args *args, void *ws, size_t ws_len, void *stream);
+void ops_random_sample_destroy(ops_random_sample *op);
+/* RandomSample::build_indices (operators/src/random_sample/mod.rs:16-19): 0..n as u32 on the HOST. */
+int ops_random_sample_build_indices(size_t n, uint32_t *host_out);
+/* Extension with no counterpart in the crate (its API samples one row per launch): `rows` rows of
+ * `n` logits, row stride `row_stride` bytes, one seed per row (device array of f32), `rows` KVPairs
+ * out; one kernel launch for all rows.  Workspace as reported by the _batched_workspace call. */
+size_t ops_random_sample_batched_workspace(uint32_t dt, size_t rows, size_t n, const ops_sample_args *config);
+int ops_random_sample_launch_batched(const ops_random_sample *op, uint32_t dt, size_t rows, size_t n,
+                                     const void *logits_base, ptrdiff_t row_stride, void *kv_pairs_base,
+                                     const ops_sample_args *config, const float *seeds_dev,
+                                     void *ws, size_t ws_len, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * all_reduce — all_reduce::Args {pair: rearrange::Args, op} (operators/src/all_reduce/args.rs:9-12);
+ * replaces all_reduce::common_cpu::Operator over InprocNode (operators/src/all_reduce/common_cpu.rs:15-104)
+ * and the NCCL operator (operators/src/all_reduce/nccl.rs:12-62).  The topology node
+ * (TopoNode: rank, group_size; operators/src/lib.rs:62-66) is an ops_comm: one per process/GPU.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ops_comm ops_comm;
+#define OPS_COMM_ID_BYTES 128
+/* rank 0 makes the id, the caller ships the 128 bytes to every rank (any transport), each rank
+ * calls _init_rank with its own device current.  group_size 1 needs no id (NULL). */
+int ops_comm_unique_id(uint8_t id_out[OPS_COMM_ID_BYTES]);
+int ops_comm_init_rank(int device, int rank, int group_size, const uint8_t id[OPS_COMM_ID_BYTES], ops_comm **out);
+int ops_comm_rank(const ops_comm *c);
+int ops_comm_group_size(const ops_comm *c);
+void ops_comm_destroy(ops_comm *c);
+/* Peer-to-peer (NVLink) path: each rank allocates a symmetric staging buffer inside the library,
+ * exports an IPC handle (64 bytes) per rank, the caller all-gathers the handles (group_size*64
+ * bytes, rank order) and hands them back.  After _p2p_attach the all_reduce operator may use the
+ * one-shot / two-shot kernels; before it, NCCL only. */
+#define OPS_COMM_P2P_HANDLE_BYTES 128
+int ops_comm_p2p_export(ops_comm *c, size_t staging_bytes, uint8_t handle_out[OPS_COMM_P2P_HANDLE_BYTES]);
+int ops_comm_p2p_attach(ops_comm *c, const uint8_t *all_handles /* group_size * OPS_COMM_P2P_HANDLE_BYTES */);
+/* Status word of the last P2P kernel on this rank: 0 ok, else a bounded wait ran out
+ * (read after the stream is synchronised). */
+int ops_comm_p2p_status(ops_comm *c);
+
+typedef struct ops_all_reduce ops_all_reduce;
+typedef struct {
+  ops_rearrange_args pair;
+  uint8_t op;
+} ops_all_reduce_args;
+enum { OPS_ALL_REDUCE_AUTO = 0, OPS_ALL_REDUCE_NCCL = 1, OPS_ALL_REDUCE_P2P_ONE_SHOT = 2, OPS_ALL_REDUCE_P2P_TWO_SHOT = 3 };
+int ops_all_reduce_create(ops_comm *node, ops_all_reduce **out);
+int ops_all_reduce_set_algo(ops_all_reduce *op, int algo);
+int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args *args, size_t max_ws, size_t *ws_out);
+int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream);
+void ops_all_reduce_destroy(ops_all_reduce *op);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPS_B200_H */

@@ -1,0 +1,573 @@
+// all_reduce.cu — tensor-parallel all_reduce over the GPUs of one NVLink/NVSwitch box.
+//
+// Replaces all_reduce::common_cpu::Operator over InprocNode (operators/src/all_reduce/common_cpu.rs:43-104)
+// and the crate's NCCL operator (operators/src/all_reduce/nccl.rs:36-62); argument checks follow
+// Args::meta (operators/src/all_reduce/args.rs:26-75).  The topology node (rank, group size,
+// communicator) is `ops_comm`, one per process and GPU.
+//
+// Two data paths:
+//   * NCCL: one ncclAllReduce on the caller's stream (any dtype NCCL knows, every ReduceOp).  NCCL is
+//     opened at run time (the copy PyTorch ships, already loaded in a torch process).
+//   * peer-to-peer kernels for f16/f32 sums.  Every rank owns a staging buffer that all peers map
+//     through CUDA IPC.  ONE kernel per call does copy-in, signalling, waiting and reduction with
+//     ordinary loads from peer memory:
+//       one-shot (small messages): every rank sums all p staged copies in rank order in f32 -> all
+//         ranks produce bit-identical results after one NVLink read of (p-1) messages;
+//       two-shot (large messages): rank r reduces the r-th 1/p of the message from all peers
+//         (reduce-scatter), publishes it in its staging buffer, then gathers the other reduced parts
+//         from the peers straight into dst -> 2 (p-1)/p message bytes over NVLink per rank.
+//     CTA b of every rank works on slice b, so synchronisation is pairwise between same-index CTAs
+//     through per-CTA epoch flags in peer memory; no grid-wide barrier.  Staging is double buffered by
+//     epoch parity, which makes one signalling round per phase sufficient.  Every spin is bounded: after
+//     WAIT_LIMIT_NS the kernel records the phase in the communicator's status word and returns.
+//
+// NVLink-bound: bus bytes per rank 2 (p-1)/p S (two-shot) or (p-1) S read (one-shot).
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <string>
+
+#include "common.h"
+#include "device_utils.cuh"
+#include "internal.h"
+
+namespace ops {
+
+constexpr int MAX_RANKS = 8;
+constexpr int P2P_MAX_CTAS = 256;
+constexpr unsigned long long P2P_WAIT_LIMIT_NS = 1000000000ull;  // 1 s
+
+// ------------------------------------------------------------------------------------------------
+// NCCL, bound at run time
+// ------------------------------------------------------------------------------------------------
+struct NcclApi {
+  void *lib = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+  std::string error;
+};
+
+static NcclApi &nccl_api() {
+  static NcclApi api = [] {
+    NcclApi a;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+      a.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (a.lib) break;
+    }
+    if (!a.lib) {
+      a.error = std::string("cannot open libnccl.so.2: ") + (dlerror() ? dlerror() : "?");
+      return a;
+    }
+    a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(a.lib, "ncclGetUniqueId");
+    a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.lib, "ncclCommInitRank");
+    a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.lib, "ncclCommDestroy");
+    a.AllReduce = (decltype(a.AllReduce))dlsym(a.lib, "ncclAllReduce");
+    a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.lib, "ncclGetErrorString");
+    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.GetErrorString) a.error = "libnccl lacks a required symbol";
+    return a;
+  }();
+  return api;
+}
+
+// ------------------------------------------------------------------------------------------------
+// peer-to-peer state
+// ------------------------------------------------------------------------------------------------
+// Staging buffer of one rank: [flags | in(parity 0) | in(parity 1) | out(parity 0) | out(parity 1)]
+struct P2PFlags {
+  unsigned int ready[MAX_RANKS][P2P_MAX_CTAS];   // ready[q][b]: epoch up to which rank q's CTA b has staged its input
+  unsigned int reduced[MAX_RANKS][P2P_MAX_CTAS]; // reduced[q][b]: epoch up to which rank q's CTA b has published its reduced slice
+};
+
+struct P2PHandleBlob {  // what ops_comm_p2p_export ships (<= OPS_COMM_P2P_HANDLE_BYTES)
+  cudaIpcMemHandle_t mem;
+  unsigned long long region_bytes;
+  int rank;
+  int valid;
+};
+static_assert(sizeof(P2PHandleBlob) <= OPS_COMM_P2P_HANDLE_BYTES, "handle blob too large");
+
+struct P2PKernelArgs {
+  char *peers[MAX_RANKS];  // peers[q]: base of rank q's staging buffer as mapped here (own buffer for q == rank)
+  unsigned long long region_bytes;
+  int rank, size;
+  unsigned int epoch;
+  int *status;
+};
+
+}  // namespace ops
+
+struct ops_comm {
+  int device;
+  int rank, size;
+  ncclComm_t nccl;
+  bool has_nccl;
+  // p2p
+  char *staging;               // own buffer (cudaMalloc)
+  size_t staging_bytes;        // total allocation
+  size_t region_bytes;         // bytes of each of the four data regions
+  char *peers[ops::MAX_RANKS];
+  bool p2p_ready;
+  unsigned int epoch;
+  int *status_dev;
+  int sm_count;
+};
+
+namespace ops {
+
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void *p) {  // system-scope relaxed load: never served from a stale L1 line
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long p2p_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Thread q < size waits until flags[q] has reached `epoch`; returns false for the whole CTA on time-out.
+__device__ __forceinline__ bool wait_flags(const unsigned int *flags_row0, int size, unsigned int epoch, int *status, int code) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < size) {
+    const unsigned int *f = flags_row0 + (size_t)threadIdx.x * P2P_MAX_CTAS;
+    const unsigned long long t0 = p2p_now();
+    while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+      if (p2p_now() - t0 > P2P_WAIT_LIMIT_NS) {
+        atomicCAS(status, 0, code + 16 * ((int)threadIdx.x + 1));
+        s_fail = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+template <class T> struct Acc8;  // 16 bytes of T widened to f32 and back
+template <> struct Acc8<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void add(float *acc, uint4 raw) {
+    const __half *h = reinterpret_cast<const __half *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __half2float(h[i]);
+  }
+  static __device__ __forceinline__ uint4 pack(const float *acc) {
+    Pack8 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.h[i] = __float2half_rn(acc[i]);
+    return o.u;
+  }
+};
+template <> struct Acc8<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void add(float *acc, uint4 raw) {
+    const float *f = reinterpret_cast<const float *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += f[i];
+  }
+  static __device__ __forceinline__ uint4 pack(const float *acc) {
+    uint4 o;
+    o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]); o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]);
+    return o;
+  }
+};
+
+__device__ __forceinline__ char *region_in(char *base, unsigned long long region, unsigned int parity) {
+  return base + sizeof(P2PFlags) + (unsigned long long)parity * region;
+}
+__device__ __forceinline__ char *region_out(char *base, unsigned long long region, unsigned int parity) {
+  return base + sizeof(P2PFlags) + (2ull + parity) * region;
+}
+
+// One-shot: stage own input, tell the peers, wait for theirs, sum everything in rank order.
+// `vecs` = number of 16-byte vectors; CTA b owns vectors [b*per, (b+1)*per).
+template <class T>
+__global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+                                                                  uint4 *__restrict__ dst, long long vecs) {
+  const unsigned int parity = a.epoch & 1u;
+  const long long per = (vecs + gridDim.x - 1) / gridDim.x;
+  const long long lo = (long long)blockIdx.x * per, hi = min(vecs, lo + per);
+  uint4 *mine = reinterpret_cast<uint4 *>(region_in(a.peers[a.rank], a.region_bytes, parity));
+  for (long long v = lo + threadIdx.x; v < hi; v += blockDim.x) mine[v] = src[v];
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < a.size) {
+    P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
+    st_release_sys(&pf->ready[a.rank][blockIdx.x], a.epoch);
+  }
+  const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
+  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, a.epoch, a.status, 1)) return;
+  for (long long v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+    float acc[Acc8<T>::N] = {};
+    for (int q = 0; q < a.size; ++q) {
+      const uint4 *pin = reinterpret_cast<const uint4 *>(region_in(a.peers[q], a.region_bytes, parity));
+      Acc8<T>::add(acc, ld_peer_16(pin + v));
+    }
+    dst[v] = Acc8<T>::pack(acc);
+  }
+}
+
+// Two-shot: the message is cut into `size` parts of `part_vecs` vectors; CTA b owns slice b of every part.
+template <class T>
+__global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+                                                                  uint4 *__restrict__ dst, long long vecs, long long part_vecs) {
+  const unsigned int parity = a.epoch & 1u;
+  const long long per = (part_vecs + gridDim.x - 1) / gridDim.x;
+  const long long s_lo = (long long)blockIdx.x * per, s_hi = min(part_vecs, s_lo + per);
+  uint4 *mine_in = reinterpret_cast<uint4 *>(region_in(a.peers[a.rank], a.region_bytes, parity));
+  uint4 *mine_out = reinterpret_cast<uint4 *>(region_out(a.peers[a.rank], a.region_bytes, parity));
+  // stage slice b of every part
+  for (int part = 0; part < a.size; ++part) {
+    const long long base = (long long)part * part_vecs;
+    for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x)
+      if (base + v < vecs) mine_in[base + v] = src[base + v];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < a.size) {
+    P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
+    st_release_sys(&pf->ready[a.rank][blockIdx.x], a.epoch);
+  }
+  const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
+  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, a.epoch, a.status, 2)) return;
+  // reduce my part, slice b
+  {
+    const long long base = (long long)a.rank * part_vecs;
+    for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x) {
+      if (base + v >= vecs) break;
+      float acc[Acc8<T>::N] = {};
+      for (int q = 0; q < a.size; ++q) {
+        const uint4 *pin = reinterpret_cast<const uint4 *>(region_in(a.peers[q], a.region_bytes, parity));
+        Acc8<T>::add(acc, ld_peer_16(pin + base + v));
+      }
+      const uint4 r = Acc8<T>::pack(acc);
+      mine_out[v] = r;
+      dst[base + v] = r;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < a.size) {
+    P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
+    st_release_sys(&pf->reduced[a.rank][blockIdx.x], a.epoch);
+  }
+  if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, a.epoch, a.status, 3)) return;
+  // gather the other parts
+  for (int i = 1; i < a.size; ++i) {
+    const int q = (a.rank + i) % a.size;  // start at different peers to spread the load
+    const uint4 *pout = reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity));
+    const long long base = (long long)q * part_vecs;
+    for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x)
+      if (base + v < vecs) dst[base + v] = ld_peer_16(pout + v);
+  }
+}
+
+struct AllReduceMeta {
+  uint32_t dt;
+  usz len;  // elements
+};
+
+// One contiguous run?  (ArrayLayout::merge_be over all dims, operators/src/all_reduce/args.rs:46-68)
+static int contiguous_len(const ops_layout &L, const char *name, usz *len) {
+  const usz es = dt_size(L.dt);
+  for (uint32_t i = 0; i < L.ndim; ++i)
+    if (dyn(L.shape[i]) || dyn(L.strides[i])) return fail(OPS_DYNAMIC_NOT_SUPPORT, "all_reduce: %s has dynamic shape or strides", name);
+  usz total = 1;
+  isz expect = (isz)es;
+  for (uint32_t i = L.ndim; i-- > 0;) {
+    if (L.shape[i] != 1 && L.strides[i] != expect) return fail(OPS_STRIDES_NOT_SUPPORT, "all_reduce: %s is not one contiguous run", name);
+    expect *= (isz)L.shape[i];
+    total *= L.shape[i];
+  }
+  *len = total;
+  return OPS_OK;
+}
+
+static int all_reduce_meta(const ops_all_reduce_args *a, AllReduceMeta *m) {
+  if (a->pair.dst_layout.dt != a->pair.src_layout.dt) return fail(OPS_TYPE_MISMATCH, "dst and src element types differ");
+  m->dt = a->pair.dst_layout.dt;
+  if (dt_size(m->dt) == 0) return fail(OPS_TYPE_NOT_SUPPORT, "all_reduce: unknown element type %u", m->dt);
+  usz d, s;
+  OPS_TRY(contiguous_len(a->pair.dst_layout, "dst", &d));
+  OPS_TRY(contiguous_len(a->pair.src_layout, "src", &s));
+  if (d != s) return fail(OPS_SHAPE_MISMATCH, "all_reduce: dst has %zu elements, src %zu", d, s);
+  m->len = d;
+  return OPS_OK;
+}
+
+static bool nccl_types(uint32_t dt, uint8_t op, ncclDataType_t *t, ncclRedOp_t *o) {
+  switch (dt) {
+    case OPS_DT_F16: *t = ncclHalf; break;
+    case OPS_DT_BF16: *t = ncclBfloat16; break;
+    case OPS_DT_F32: *t = ncclFloat; break;
+    case OPS_DT_F64: *t = ncclDouble; break;
+    case OPS_DT_U8: *t = ncclUint8; break;
+    case OPS_DT_I8: *t = ncclInt8; break;
+    case OPS_DT_U32: *t = ncclUint32; break;
+    case OPS_DT_I32: *t = ncclInt32; break;
+    case OPS_DT_U64: *t = ncclUint64; break;
+    case OPS_DT_I64: *t = ncclInt64; break;
+    default: return false;
+  }
+  switch (op) {  // operators/src/all_reduce/nccl.rs:66-76
+    case OPS_REDUCE_SUM: *o = ncclSum; break;
+    case OPS_REDUCE_PROD: *o = ncclProd; break;
+    case OPS_REDUCE_MIN: *o = ncclMin; break;
+    case OPS_REDUCE_MAX: *o = ncclMax; break;
+    case OPS_REDUCE_MEAN: *o = ncclAvg; break;
+    default: return false;
+  }
+  return true;
+}
+
+}  // namespace ops
+
+using namespace ops;
+
+struct ops_all_reduce {
+  ops_comm *comm;
+  int algo;
+};
+
+// ------------------------------------------------------------------------------------------------
+// communicator
+// ------------------------------------------------------------------------------------------------
+OPS_API int ops_comm_unique_id(uint8_t id_out[OPS_COMM_ID_BYTES]) {
+  NcclApi &n = nccl_api();
+  if (!n.error.empty()) return fail(OPS_EXECUTION_FAILED, "%s", n.error.c_str());
+  static_assert(sizeof(ncclUniqueId) == OPS_COMM_ID_BYTES, "ncclUniqueId size");
+  ncclUniqueId id;
+  ncclResult_t r = n.GetUniqueId(&id);
+  if (r != ncclSuccess) return fail(OPS_EXECUTION_FAILED, "ncclGetUniqueId: %s", n.GetErrorString(r));
+  memcpy(id_out, &id, sizeof(id));
+  return OPS_OK;
+}
+
+OPS_API int ops_comm_init_rank(int device, int rank, int group_size, const uint8_t id[OPS_COMM_ID_BYTES], ops_comm **out) {
+  if (!out) return fail(OPS_ARGS_NOT_SUPPORT, "null out pointer");
+  if (group_size < 1 || group_size > MAX_RANKS || rank < 0 || rank >= group_size)
+    return fail(OPS_ARGS_NOT_SUPPORT, "rank %d of %d: group size must be 1..%d", rank, group_size, MAX_RANKS);
+  OpBase base;
+  OPS_TRY(init_base(&base, device));
+  ops_comm *c = new ops_comm();
+  memset(c, 0, sizeof(*c));
+  c->device = device;
+  c->rank = rank;
+  c->size = group_size;
+  c->sm_count = base.sm_count;
+  cudaSetDevice(device);
+  if (group_size > 1) {
+    if (!id) {
+      delete c;
+      return fail(OPS_ARGS_NOT_SUPPORT, "group size %d needs a unique id", group_size);
+    }
+    NcclApi &n = nccl_api();
+    if (!n.error.empty()) {
+      delete c;
+      return fail(OPS_EXECUTION_FAILED, "%s", n.error.c_str());
+    }
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof(uid));
+    ncclResult_t r = n.CommInitRank(&c->nccl, group_size, uid, rank);
+    if (r != ncclSuccess) {
+      delete c;
+      return fail(OPS_EXECUTION_FAILED, "ncclCommInitRank: %s", n.GetErrorString(r));
+    }
+    c->has_nccl = true;
+  }
+  if (cudaMalloc(&c->status_dev, sizeof(int)) != cudaSuccess || cudaMemset(c->status_dev, 0, sizeof(int)) != cudaSuccess) {
+    delete c;
+    return fail(OPS_EXECUTION_FAILED, "all_reduce: cannot allocate the status word");
+  }
+  *out = c;
+  return OPS_OK;
+}
+
+OPS_API int ops_comm_rank(const ops_comm *c) { return c->rank; }
+OPS_API int ops_comm_group_size(const ops_comm *c) { return c->size; }
+
+OPS_API void ops_comm_destroy(ops_comm *c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->p2p_ready)
+    for (int q = 0; q < c->size; ++q)
+      if (q != c->rank && c->peers[q]) cudaIpcCloseMemHandle(c->peers[q]);
+  if (c->staging) cudaFree(c->staging);
+  if (c->status_dev) cudaFree(c->status_dev);
+  if (c->has_nccl) nccl_api().CommDestroy(c->nccl);
+  delete c;
+}
+
+OPS_API int ops_comm_p2p_export(ops_comm *c, size_t staging_bytes, uint8_t handle_out[OPS_COMM_P2P_HANDLE_BYTES]) {
+  memset(handle_out, 0, OPS_COMM_P2P_HANDLE_BYTES);
+  if (c->staging) return fail(OPS_ARGS_NOT_SUPPORT, "p2p staging already exported");
+  cudaSetDevice(c->device);
+  const size_t region = (staging_bytes + 255) / 256 * 256;
+  const size_t total = sizeof(P2PFlags) + 4 * region;
+  if (cudaMalloc(&c->staging, total) != cudaSuccess) {
+    cudaGetLastError();
+    c->staging = nullptr;
+    return fail(OPS_EXECUTION_FAILED, "p2p: cannot allocate %zu staging bytes", total);
+  }
+  cudaMemset(c->staging, 0, sizeof(P2PFlags));
+  cudaDeviceSynchronize();
+  c->staging_bytes = total;
+  c->region_bytes = region;
+  P2PHandleBlob blob;
+  memset(&blob, 0, sizeof(blob));
+  cudaError_t e = cudaIpcGetMemHandle(&blob.mem, c->staging);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(OPS_EXECUTION_FAILED, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  blob.region_bytes = region;
+  blob.rank = c->rank;
+  blob.valid = 1;
+  memcpy(handle_out, &blob, sizeof(blob));
+  return OPS_OK;
+}
+
+OPS_API int ops_comm_p2p_attach(ops_comm *c, const uint8_t *all_handles) {
+  if (!c->staging) return fail(OPS_ARGS_NOT_SUPPORT, "p2p: export before attach");
+  cudaSetDevice(c->device);
+  for (int q = 0; q < c->size; ++q) {
+    P2PHandleBlob blob;
+    memcpy(&blob, all_handles + (size_t)q * OPS_COMM_P2P_HANDLE_BYTES, sizeof(blob));
+    if (!blob.valid || blob.rank != q || blob.region_bytes != c->region_bytes)
+      return fail(OPS_ARGS_NOT_SUPPORT, "p2p: handle %d is invalid or sized differently", q);
+    if (q == c->rank) {
+      c->peers[q] = c->staging;
+      continue;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, blob.mem, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(OPS_EXECUTION_FAILED, "cudaIpcOpenMemHandle(rank %d): %s", q, cudaGetErrorString(e));
+    }
+    c->peers[q] = (char *)p;
+  }
+  c->p2p_ready = true;
+  return OPS_OK;
+}
+
+OPS_API int ops_comm_p2p_status(ops_comm *c) {
+  int v = -1;
+  cudaSetDevice(c->device);
+  if (cudaMemcpy(&v, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// operator
+// ------------------------------------------------------------------------------------------------
+OPS_API int ops_all_reduce_create(ops_comm *node, ops_all_reduce **out) {
+  if (!node || !out) return fail(OPS_ARGS_NOT_SUPPORT, "null communicator or out pointer");
+  ops_all_reduce *h = new ops_all_reduce();
+  h->comm = node;
+  h->algo = OPS_ALL_REDUCE_AUTO;
+  *out = h;
+  return OPS_OK;
+}
+
+OPS_API void ops_all_reduce_destroy(ops_all_reduce *op) { delete op; }
+
+OPS_API int ops_all_reduce_set_algo(ops_all_reduce *op, int algo) {
+  if (algo < OPS_ALL_REDUCE_AUTO || algo > OPS_ALL_REDUCE_P2P_TWO_SHOT) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: unknown algorithm %d", algo);
+  if (algo >= OPS_ALL_REDUCE_P2P_ONE_SHOT && !op->comm->p2p_ready && op->comm->size > 1)
+    return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: peer-to-peer staging is not attached");
+  op->algo = algo;
+  return OPS_OK;
+}
+
+OPS_API int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args *args, size_t max_ws, size_t *ws_out) {
+  (void)op;
+  (void)max_ws;
+  (void)args;  // the crate's operators plan nothing here (all_reduce/common_cpu.rs:35-41, nccl.rs:28-34)
+  if (ws_out) *ws_out = 0;
+  return OPS_OK;
+}
+
+template <class T>
+static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz bytes, cudaStream_t s) {
+  P2PKernelArgs a;
+  for (int q = 0; q < MAX_RANKS; ++q) a.peers[q] = q < c->size ? c->peers[q] : nullptr;
+  a.region_bytes = c->region_bytes;
+  a.rank = c->rank;
+  a.size = c->size;
+  a.epoch = ++c->epoch;
+  a.status = c->status_dev;
+  const long long vecs = (long long)(bytes / 16);
+  if (algo == OPS_ALL_REDUCE_P2P_ONE_SHOT) {
+    long long ctas = (vecs + 511) / 512;  // 8 KiB per CTA
+    if (ctas > 2 * c->sm_count) ctas = 2 * c->sm_count;
+    if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
+    if (ctas < 1) ctas = 1;
+    all_reduce_one_shot_kernel<T><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
+  } else {
+    const long long part = (vecs + c->size - 1) / c->size;
+    long long ctas = (part + 511) / 512;
+    if (ctas > c->sm_count) ctas = c->sm_count;  // every CTA must be resident: same-index CTAs of different ranks wait for each other
+    if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
+    if (ctas < 1) ctas = 1;
+    all_reduce_two_shot_kernel<T><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part);
+  }
+  return check_launch("all_reduce(p2p)");
+}
+
+OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream) {
+  (void)ws;
+  (void)ws_len;
+  ops_comm *c = op->comm;
+  cudaStream_t s = (cudaStream_t)stream;
+  AllReduceMeta m;
+  OPS_TRY(all_reduce_meta(args, &m));
+  const usz bytes = m.len * dt_size(m.dt);
+  if (bytes == 0) return OPS_OK;
+  void *dst = args->pair.dst_base;
+  const void *src = args->pair.src_base;
+  if (!dst || !src) return fail(OPS_DYNAMIC_NOT_SUPPORT, "all_reduce: null base pointer at launch");
+  cudaSetDevice(c->device);
+  if (c->size == 1) {
+    // single rank: NonAllReduce, a plain copy unless in place (operators/src/lib.rs:199-224)
+    if (dst != src) {
+      OpBase base{c->device, c->sm_count};
+      return rearrange_enqueue(base, &args->pair, s);
+    }
+    return OPS_OK;
+  }
+  int algo = op->algo;
+  const bool p2p_able = c->p2p_ready && args->op == OPS_REDUCE_SUM && (m.dt == OPS_DT_F16 || m.dt == OPS_DT_F32) && bytes % 16 == 0 &&
+                        aligned(dst, 16) && aligned(src, 16) && bytes <= c->region_bytes && 2 * c->sm_count >= 1;
+  if (algo == OPS_ALL_REDUCE_AUTO) {
+    if (!p2p_able) algo = OPS_ALL_REDUCE_NCCL;
+    else algo = bytes <= (usz)(1 << 20) ? OPS_ALL_REDUCE_P2P_ONE_SHOT : OPS_ALL_REDUCE_NCCL;
+  }
+  if (algo == OPS_ALL_REDUCE_NCCL) {
+    if (!c->has_nccl) return fail(OPS_EXECUTION_FAILED, "all_reduce: communicator has no NCCL handle");
+    ncclDataType_t t;
+    ncclRedOp_t o;
+    if (!nccl_types(m.dt, args->op, &t, &o)) return fail(OPS_TYPE_NOT_SUPPORT, "all_reduce: dtype %u / op %u not supported by NCCL", m.dt, args->op);
+    NcclApi &n = nccl_api();
+    ncclResult_t r = n.AllReduce(src, dst, m.len, t, o, c->nccl, s);
+    if (r != ncclSuccess) return fail(OPS_EXECUTION_FAILED, "ncclAllReduce: %s", n.GetErrorString(r));
+    return OPS_OK;
+  }
+  if (!p2p_able) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: the peer-to-peer path needs an attached staging buffer of >= %zu bytes, f16/f32 Sum, 16-byte aligned data", bytes);
+  if (m.dt == OPS_DT_F16) return launch_p2p<__half>(c, algo, src, dst, bytes, s);
+  return launch_p2p<float>(c, algo, src, dst, bytes, s);
+}

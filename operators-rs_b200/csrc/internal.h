@@ -1,0 +1,14 @@
+// internal.h — entry points the composite operators (attention, attention_kv_cached) call on the
+// primitive ones, bypassing the C ABI but running exactly the same code.
+#pragma once
+#include "common.h"
+
+struct ops_mat_mul;
+
+namespace ops {
+
+int rearrange_enqueue(const OpBase &base, const ops_rearrange_args *args, cudaStream_t s);
+int fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args *args, cudaStream_t s);
+int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s);
+
+}  // namespace ops

@@ -1,0 +1,577 @@
+// mat_mul.cu — C <- beta*C + alpha*A*B (rank 2 or 3, one broadcastable batch dim).
+//
+// Replaces mat_mul::common_cpu::Operator (operators/src/mat_mul/common_cpu/mod.rs:26-107); the layout
+// checks restate Args::layout and Matrix::try_from (operators/src/mat_mul/args.rs:64-192).
+//
+// f16 runs on the 5th-generation tensor cores:
+//   * one persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer (one
+//     elected lane each), warps 2-5 = epilogue (one per 32-lane quarter of tensor memory);
+//   * operands are staged in shared memory by tiled TMA loads with the 128-byte swizzle the
+//     tcgen05 shared-memory descriptors expect; an mbarrier ring (full/empty per stage) couples
+//     producer and issuer, tcgen05.commit releases a stage when its MMAs have retired;
+//   * the 128 x BN f32 accumulator lives in tensor memory, double buffered (2 x BN columns), so the
+//     epilogue of tile i overlaps the main loop of tile i+1; epilogue = tcgen05.ld -> alpha/beta in
+//     f32 -> f16 -> 128-bit global stores;
+//   * both operand majors are handled by descriptors (K-major or MN-major), so no operand is ever
+//     transposed in memory; a column-major C is computed as C^T = B^T A^T.
+// Layouts TMA cannot describe (unaligned bases or strides) and f32 take a plain tiled SIMT kernel.
+// Tensor-bound when 2mnk / bytes exceeds the ridge, HBM-bound otherwise (k = 128 attention products).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+#include "device_utils.cuh"
+#include "internal.h"
+#include "sm100_ptx.cuh"
+
+namespace ops {
+
+using namespace sm100;
+
+// ------------------------------------------------------------------------------------------------
+// device side: tcgen05 kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;                       // 64 f16 = one 128-byte swizzle row
+constexpr int GEMM_UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
+constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
+
+struct GemmKernelArgs {
+  __half *d;             // row-major output
+  long long ldd, d_bs;   // elements
+  int m, n, k, batch;
+  int tiles_m, tiles_n;
+  int a_mn_major, b_mn_major;
+  int a_batched, b_batched;  // 0: operand is shared by all batches (coordinate 0)
+  float alpha, beta;
+  int read_c;
+  int vec_store;         // rows of D are 16-byte aligned
+  int *status;
+};
+
+template <int BN> struct GemmCfg {
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two >= 32
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                            const __grid_constant__ GemmKernelArgs g) {
+  typedef GemmCfg<BN> Cfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * Cfg::STAGES + 4);
+  uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (g.k + GEMM_BK - 1) / GEMM_BK;
+  const long long tiles_per_batch = (long long)g.tiles_m * g.tiles_n;
+  const long long num_tiles = tiles_per_batch * g.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int b = (int)(t / tiles_per_batch);
+        const long long r = t - (long long)b * tiles_per_batch;
+        const int tn = (int)(r / g.tiles_m), tm = (int)(r - (long long)tn * g.tiles_m);
+        const int m0 = tm * GEMM_BM, n0 = tn * BN;
+        const int ba = g.a_batched ? b : 0, bb = g.b_batched ? b : 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, g.status, 1))) break;
+          mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES, sb = sa + GEMM_A_BYTES;
+          const int k0 = kb * GEMM_BK;
+          if (g.a_mn_major) {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c) tma_load_3d(sa + c * GEMM_CHUNK_BYTES, &tmap_a, full_bar(stage), m0 + 64 * c, k0, ba);
+          } else {
+            tma_load_3d(sa, &tmap_a, full_bar(stage), k0, m0, ba);
+          }
+          if (g.b_mn_major) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
+          } else {
+            tma_load_3d(sb, &tmap_b, full_bar(stage), k0, n0, bb);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major);
+      const uint32_t a_lbo = g.a_mn_major ? GEMM_CHUNK_BYTES : 16, b_lbo = g.b_mn_major ? GEMM_CHUNK_BYTES : 16;
+      const uint32_t a_kstep = g.a_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;  // bytes per UMMA_K
+      const uint32_t b_kstep = g.b_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!(ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, g.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, g.status, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES, sb = sa + GEMM_A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < GEMM_BK / GEMM_UMMA_K; ++ks) {
+            const uint64_t da = make_smem_desc_sw128(sa + ks * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + ks * b_kstep, b_lbo, 1024);
+            umma_f16_ss(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tmem_full_bar(acc));  // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, +32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int b = (int)(t / tiles_per_batch);
+      const long long r = t - (long long)b * tiles_per_batch;
+      const int tn = (int)(r / g.tiles_m), tm = (int)(r - (long long)tn * g.tiles_m);
+      const int row = tm * GEMM_BM + quarter * 32 + lane;
+      const int n0 = tn * BN;
+      if (!(ok = mbar_wait(tmem_full_bar(acc), acc_phase, g.status, 4))) break;
+      tc_fence_after();
+      __half *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + (uint32_t)c, v);
+        tmem_wait_ld();
+        if (row < g.m) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int col = n0 + c + q * 8;
+            if (col >= g.n) break;
+            __half *dp = drow + col;
+            if (g.vec_store && col + 8 <= g.n) {
+              Pack8 out, old;
+              if (g.read_c) old.u = ld_global_16(dp);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
+                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(old.h[e])), val);
+                out.h[e] = __float2half_rn(val);
+              }
+              st_global_16(dp, out.u);
+            } else {
+              for (int e = 0; e < 8 && col + e < g.n; ++e) {
+                float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
+                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(dp[e])), val);
+                dp[e] = __float2half_rn(val);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*reinterpret_cast<volatile int *>(g.status) != 0) __nanosleep(1000000);  // let stray copies land before the CTA goes away
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// device side: generic SIMT kernel (any strides, f16 or f32), 64x64 tile, 256 threads, 4x4 per thread
+// ------------------------------------------------------------------------------------------------
+struct SimtArgs {
+  void *c;
+  const void *a, *b;
+  long long c_rs, c_cs, c_bs, a_rs, a_cs, a_bs, b_rs, b_cs, b_bs;  // elements
+  int m, n, k, batch;
+  float alpha, beta;
+  int read_c;
+};
+
+template <class T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ SimtArgs g) {
+  __shared__ float As[16][64 + 1];
+  __shared__ float Bs[16][64 + 1];
+  const int b = blockIdx.z;
+  const T *A = (const T *)g.a + (long long)b * g.a_bs;
+  const T *B = (const T *)g.b + (long long)b * g.b_bs;
+  T *C = (T *)g.c + (long long)b * g.c_bs;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < g.k; k0 += 16) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int kk = i & 15, mm = i >> 4;
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < g.m && gk < g.k) ? to_f32(A[(long long)gm * g.a_rs + (long long)gk * g.a_cs]) : 0.f;
+      const int nn = i & 63, kb = i >> 6;
+      const int gn = n0 + nn, gk2 = k0 + kb;
+      Bs[kb][nn] = (gn < g.n && gk2 < g.k) ? to_f32(B[(long long)gk2 * g.b_rs + (long long)gn * g.b_cs]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+      if (gm < g.m && gn < g.n) {
+        T *cp = C + (long long)gm * g.c_rs + (long long)gn * g.c_cs;
+        float val = __fmul_rn(g.alpha, acc[i][j]);
+        if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, to_f32(*cp)), val);
+        *cp = from_f32<T>(val);
+      }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+struct Mat {  // element strides (operators/src/mat_mul/args.rs:124-131)
+  usz batch;
+  isz stride;
+  usz r, c;
+  isz rs, cs;
+};
+
+static int to_matrix(const ops_layout &L, const char *name, Mat *mt) {
+  for (uint32_t i = 0; i < L.ndim; ++i)
+    if (dyn(L.shape[i]) || dyn(L.strides[i])) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: %s has dynamic shape or strides", name);
+  if (L.ndim < 2) return fail(OPS_RANK_NOT_SUPPORT, "Matrix must have rank 2 or more");
+  if (L.ndim > 3) return fail(OPS_SHAPE_NOT_SUPPORT, "Higher-rank tensors not supported");
+  const isz unit = (isz)dt_size(L.dt);
+  if (unit == 0) return fail(OPS_TYPE_NOT_SUPPORT, "mat_mul: unknown element type %u", L.dt);
+  mt->batch = 1;
+  mt->stride = 0;
+  if (L.ndim == 3 && L.shape[0] != 1) {
+    mt->batch = L.shape[0];
+    mt->stride = L.strides[0] / unit;
+  }
+  mt->r = L.shape[L.ndim - 2];
+  mt->c = L.shape[L.ndim - 1];
+  mt->rs = L.strides[L.ndim - 2] / unit;
+  mt->cs = L.strides[L.ndim - 1] / unit;
+  return OPS_OK;
+}
+
+static inline void transpose(Mat &m) {
+  std::swap(m.r, m.c);
+  std::swap(m.rs, m.cs);
+}
+
+struct GemmProblem {  // D (row-major, unit column stride) = alpha * A * B + beta * D
+  uint32_t dt;
+  usz batch, m, n, k;
+  Mat a, b, d;
+  const void *a_ptr, *b_ptr;
+  void *d_ptr;
+};
+
+static int solve_layout(const ops_mat_mul_args *args, GemmProblem *p) {
+  Mat c, a, b;
+  OPS_TRY(to_matrix(args->c_layout, "c", &c));
+  OPS_TRY(to_matrix(args->a_layout, "a", &a));
+  OPS_TRY(to_matrix(args->b_layout, "b", &b));
+  if (c.r != a.r || c.c != b.c || a.c != b.r) return fail(OPS_SHAPE_MISMATCH, "Inconsistent matrix shapes");
+  const usz batch = c.batch;
+  if (!(a.batch == 1 || a.batch == batch) || !(b.batch == 1 || b.batch == batch)) return fail(OPS_SHAPE_MISMATCH, "Inconsistent batch sizes");
+  if (!(c.rs == 1 || c.cs == 1) || !(a.rs == 1 || a.cs == 1) || !(b.rs == 1 || b.cs == 1))
+    return fail(OPS_STRIDES_NOT_SUPPORT, "Matrix is not contiguous");
+  if (args->c_layout.dt != args->a_layout.dt || args->c_layout.dt != args->b_layout.dt) return fail(OPS_TYPE_MISMATCH, "mat_mul: element types differ");
+  p->dt = args->c_layout.dt;
+  p->a_ptr = args->a_base;
+  p->b_ptr = args->b_base;
+  p->d_ptr = args->c_base;
+  if (c.cs != 1) {  // column-major C: compute C^T = B^T A^T, which is row-major
+    transpose(c);
+    transpose(a);
+    transpose(b);
+    std::swap(a, b);
+    std::swap(p->a_ptr, p->b_ptr);
+  }
+  p->batch = batch;
+  p->m = c.r;
+  p->n = c.c;
+  p->k = a.c;
+  p->a = a;
+  p->b = b;
+  p->d = c;
+  return OPS_OK;
+}
+
+// cuTensorMapEncodeTiled, fetched from the driver at run time (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// One operand as a rank-3 f16 tensor map: dims (inner, outer, batch), 128-byte swizzle.
+static bool encode_operand(CUtensorMap *map, const void *ptr, usz inner, usz outer, usz batch, isz outer_stride_el, isz batch_stride_el,
+                           uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  // strides of size-1 dims are never used for addressing; give them a valid dummy
+  cuuint64_t os = outer > 1 ? (cuuint64_t)outer_stride_el * 2 : (cuuint64_t)((inner * 2 + 15) / 16 * 16);
+  cuuint64_t bs = batch > 1 ? (cuuint64_t)batch_stride_el * 2 : os * (outer ? outer : 1);
+  cuuint64_t strides[2] = {os, bs};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool tma_ok(const void *ptr, usz outer, usz batch, isz outer_stride_el, isz batch_stride_el) {
+  if (!aligned(ptr, 16)) return false;
+  if (outer > 1 && (outer_stride_el <= 0 || (outer_stride_el * 2) % 16 != 0)) return false;
+  if (batch > 1 && (batch_stride_el <= 0 || (batch_stride_el * 2) % 16 != 0)) return false;
+  return true;
+}
+
+struct GemmState {
+  int *status_dev = nullptr;
+  bool attr_set[2] = {false, false};
+};
+
+}  // namespace ops
+
+using namespace ops;
+
+struct ops_mat_mul {
+  ops::OpBase base;
+  ops::GemmState st;
+};
+
+namespace ops {
+
+template <int BN>
+static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn, bool b_mn, usz eff_batch_a, usz eff_batch_b, float alpha,
+                          float beta, cudaStream_t s) {
+  typedef GemmCfg<BN> Cfg;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (a_mn) ok = encode_operand(&ta, p.a_ptr, p.m, p.k, eff_batch_a, p.a.cs, p.a.stride, 64, GEMM_BK);
+  else ok = encode_operand(&ta, p.a_ptr, p.k, p.m, eff_batch_a, p.a.rs, p.a.stride, GEMM_BK, GEMM_BM);
+  if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for A");
+  if (b_mn) ok = encode_operand(&tb, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
+  else ok = encode_operand(&tb, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
+  if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B");
+
+  GemmKernelArgs g;
+  g.d = (__half *)p.d_ptr;
+  g.ldd = p.d.rs;
+  g.d_bs = p.d.stride;
+  g.m = (int)p.m;
+  g.n = (int)p.n;
+  g.k = (int)p.k;
+  g.batch = (int)p.batch;
+  g.tiles_m = (int)((p.m + GEMM_BM - 1) / GEMM_BM);
+  g.tiles_n = (int)((p.n + BN - 1) / BN);
+  g.a_mn_major = a_mn;
+  g.b_mn_major = b_mn;
+  g.a_batched = eff_batch_a > 1;
+  g.b_batched = eff_batch_b > 1;
+  g.alpha = alpha;
+  g.beta = beta;
+  g.read_c = beta != 0.f;
+  g.vec_store = aligned(p.d_ptr, 16) && (p.m == 1 || p.d.rs % 8 == 0) && (p.batch == 1 || p.d.stride % 8 == 0);
+  g.status = op->st.status_dev;
+  const long long tiles = (long long)g.tiles_m * g.tiles_n * g.batch;
+  const unsigned grid = (unsigned)std::min<long long>(tiles, op->base.sm_count);
+  ops_mat_mul *mop = const_cast<ops_mat_mul *>(op);
+  const int slot = BN == 256 ? 0 : 1;
+  if (!mop->st.attr_set[slot]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    mop->st.attr_set[slot] = true;
+  }
+  gemm_f16_tcgen05_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g);
+  return check_launch("mat_mul(tcgen05)");
+}
+
+int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s) {
+  GemmProblem p;
+  OPS_TRY(solve_layout(args, &p));
+  if (dyn(args->alpha) || dyn(args->beta)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: alpha and beta must be static at launch");
+  if (p.dt != OPS_DT_F16 && p.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "Unsupported element type %u", p.dt);
+  if (p.m == 0 || p.n == 0 || p.batch == 0) return OPS_OK;
+  if (p.m > 0x7fffffffu || p.n > 0x7fffffffu || p.k > 0x7fffffffu || p.batch > 65535u) return fail(OPS_SHAPE_NOT_SUPPORT, "mat_mul: shape too large");
+  if (!p.a_ptr || !p.b_ptr || !p.d_ptr) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: null base pointer at launch");
+  cudaSetDevice(op->base.device);
+  float alpha = args->alpha, beta = args->beta;
+  if (p.dt == OPS_DT_F16) {  // the CPU path rounds both scalars to the element type first (mat_mul/common_cpu/mod.rs:101)
+    alpha = __half2float(__float2half_rn(alpha));
+    beta = __half2float(__float2half_rn(beta));
+  }
+
+  if (p.dt == OPS_DT_F16 && p.k > 0) {
+    // operand majors: A is [m,k] (K-major when its column stride is 1), B is [k,n] (K-major when its row stride is 1)
+    const bool a_mn = !(p.a.cs == 1 || p.k == 1) ;
+    const bool b_mn = !(p.b.rs == 1 || p.k == 1);
+    const usz ea = (p.a.batch > 1 && p.a.stride != 0) ? p.batch : 1;
+    const usz eb = (p.b.batch > 1 && p.b.stride != 0) ? p.batch : 1;
+    const bool a_ok = a_mn ? (p.a.rs == 1 && tma_ok(p.a_ptr, p.k, ea, p.a.cs, p.a.stride)) : tma_ok(p.a_ptr, p.m, ea, p.a.rs, p.a.stride);
+    const bool b_ok = b_mn ? (p.b.cs == 1 && tma_ok(p.b_ptr, p.k, eb, p.b.rs, p.b.stride)) : tma_ok(p.b_ptr, p.n, eb, p.b.cs, p.b.stride);
+    const bool d_ok = p.d.rs >= 0 && p.d.stride >= 0;
+    if (a_ok && b_ok && d_ok && encode_tiled_fn()) {
+      if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+      return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+    }
+  }
+  SimtArgs g;
+  g.c = p.d_ptr;
+  g.a = p.a_ptr;
+  g.b = p.b_ptr;
+  g.c_rs = p.d.rs; g.c_cs = p.d.cs; g.c_bs = p.d.stride;
+  g.a_rs = p.a.rs; g.a_cs = p.a.cs; g.a_bs = p.a.stride;
+  g.b_rs = p.b.rs; g.b_cs = p.b.cs; g.b_bs = p.b.stride;
+  g.m = (int)p.m; g.n = (int)p.n; g.k = (int)p.k; g.batch = (int)p.batch;
+  g.alpha = alpha; g.beta = beta; g.read_c = beta != 0.f;
+  dim3 grid((unsigned)((p.n + 63) / 64), (unsigned)((p.m + 63) / 64), (unsigned)p.batch);
+  if (grid.y > 65535u) return fail(OPS_SHAPE_NOT_SUPPORT, "mat_mul: m too large for the generic kernel");
+  if (p.dt == OPS_DT_F16) gemm_simt_kernel<__half><<<grid, 256, 0, s>>>(g);
+  else gemm_simt_kernel<float><<<grid, 256, 0, s>>>(g);
+  return check_launch("mat_mul(simt)");
+}
+
+}  // namespace ops
+
+OPS_API int ops_mat_mul_create(int device, ops_mat_mul **out) {
+  if (!out) return fail(OPS_ARGS_NOT_SUPPORT, "null out pointer");
+  ops_mat_mul *h = new ops_mat_mul();
+  int rc = init_base(&h->base, device);
+  if (rc != OPS_OK) {
+    delete h;
+    return rc;
+  }
+  cudaSetDevice(device);
+  if (cudaMalloc(&h->st.status_dev, sizeof(int)) != cudaSuccess || cudaMemset(h->st.status_dev, 0, sizeof(int)) != cudaSuccess) {
+    delete h;
+    return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot allocate the status word");
+  }
+  *out = h;
+  return OPS_OK;
+}
+
+OPS_API void ops_mat_mul_destroy(ops_mat_mul *op) {
+  if (!op) return;
+  if (op->st.status_dev) cudaFree(op->st.status_dev);
+  delete op;
+}
+
+// Non-zero when a bounded wait inside the tensor-core kernel ran out (1 producer, 2/3 issuer, 4 epilogue).
+// Synchronises the device; meant for tests and post-mortems, not for the hot path.
+OPS_API int ops_mat_mul_status(const ops_mat_mul *op) {
+  int v = -1;
+  cudaSetDevice(op->base.device);
+  if (cudaMemcpy(&v, op->st.status_dev, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+OPS_API int ops_mat_mul_scheme(ops_mat_mul *op, const ops_mat_mul_args *args, size_t max_ws, size_t *ws_out) {
+  (void)op;
+  (void)max_ws;
+  (void)args;  // like the crate's CPU operator, scheme() plans nothing (mat_mul/common_cpu/mod.rs:18-24)
+  if (ws_out) *ws_out = 0;
+  return OPS_OK;
+}
+
+OPS_API int ops_mat_mul_launch(const ops_mat_mul *op, const ops_mat_mul_args *args, void *ws, size_t ws_len, void *stream) {
+  (void)ws;
+  (void)ws_len;
+  return mat_mul_enqueue(op, args, (cudaStream_t)stream);
+}

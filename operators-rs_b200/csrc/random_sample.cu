@@ -1,0 +1,585 @@
+// random_sample.cu — one row of logits -> one KVPair {idx, val-bits}: argmax or seeded top-k/top-p sampling.
+//
+// Replaces random_sample::common_cpu::Operator (operators/src/random_sample/common_cpu/mod.rs:41-99;
+// argmax :102-109, random :111-144; ordering operators/src/random_sample/kv_pair.rs:62-84); argument
+// checks follow Args::meta (operators/src/random_sample/args.rs:92-120).
+//
+// Both modes are bit-exact restatements of serial CPU loops:
+//   argmax  — the LAST index among equal maxima (Iterator::max_by keeps the later element on Equal, and
+//             an unordered compare counts as Equal).  A 64-bit (ordered value, index) atomicMax gives
+//             exactly that; rows holding NaN take a serial finish that replays the CPU loop.
+//   random  — all n logits are ordered by (value desc, index asc); c0 = 1, c_i = fl32(c_{i-1} +
+//             exp((x_i - x_0)/t)) serially; the answer is the first i with c_i >= seed*min(c_{k-1},
+//             c_{n-1}*top_p) and val = the logit type's rounding of c_i.  Terms below 2^-25 can never
+//             change a sum that is >= 1, so only the prefix with (x - max)/t >= -16.7 is ordered (stable
+//             4-bit LSD radix sort inside one CTA).  The serial f32 sum is reproduced exactly in
+//             parallel: while the sum stays inside one binade its ulp u is constant, so each add is the
+//             integer update S += round_half_even(e/u); a tie's outcome depends only on the parity of
+//             S, so every element is a pair (delta if S even, delta if S odd) and pairs compose
+//             associatively -> block-wide scan.  The add that crosses into the next binade is done by
+//             one hardware f32 add, then the scan restarts with the doubled ulp.
+//             exp is evaluated in double and rounded to f32 (= the correctly rounded f32 exp).
+//
+// HBM-bound on paper (rows * n * sizeof(T) bytes read); argmax splits a row over several CTAs.
+#include "common.h"
+#include "device_utils.cuh"
+
+namespace ops {
+
+struct KVPair {
+  uint32_t idx;
+  uint32_t val;
+};
+
+// Monotone map float -> u32 with -0 folded onto +0 (they compare Equal in the CPU loop).
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+  uint32_t u = __float_as_uint(v + 0.f);  // -0 + 0 = +0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+template <class T> __device__ __forceinline__ uint32_t raw_bits(T v);
+template <> __device__ __forceinline__ uint32_t raw_bits<__half>(__half v) { return (uint32_t)__half_as_ushort(v); }
+template <> __device__ __forceinline__ uint32_t raw_bits<float>(float v) { return __float_as_uint(v); }
+
+// ------------------------------------------------------------------------------------------------
+// argmax
+// ------------------------------------------------------------------------------------------------
+struct ArgmaxScratch {          // per row, zero-initialised before the launch
+  unsigned long long best;      // (ordered value << 32) | index, over non-NaN elements
+  unsigned int last_nan;        // 1 + index of the last NaN, 0 if none
+  unsigned int tickets;         // CTAs of this row that have finished
+};
+
+template <class T>
+__global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logits, long long row_stride, int n, int split,
+                                                     ArgmaxScratch *scratch, KVPair *out) {
+  __shared__ unsigned long long s_best[8];
+  __shared__ unsigned int s_nan[8];
+  const int row = blockIdx.x / split, part = blockIdx.x - row * split;
+  const T *x = byte_off(logits, (long long)row * row_stride);
+  int chunk = (n + split - 1) / split;
+  chunk = (chunk + 7) & ~7;
+  const int begin = part * chunk, end = min(n, begin + chunk);
+
+  unsigned long long best = 0;
+  unsigned int last_nan = 0;
+  auto visit = [&](float v, int i) {
+    if (v != v) last_nan = max(last_nan, (unsigned)i + 1u);
+    else best = max(best, ((unsigned long long)ordered_key(v) << 32) | (unsigned)i);
+  };
+  const bool vec_ok = (((uintptr_t)x) & 15) == 0;
+  constexpr int PER = 16 / (int)sizeof(T);
+  if (vec_ok) {
+    const int vend = begin + ((end - begin) / PER) * PER;
+    for (int i = begin + threadIdx.x * PER; i < vend; i += blockDim.x * PER) {
+      const uint4 raw = ld_stream_16(x + i);
+      const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i + j);
+    }
+    for (int i = vend + threadIdx.x; i < end; i += blockDim.x) visit(to_f32(x[i]), i);
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) visit(to_f32(x[i]), i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    last_nan = max(last_nan, __shfl_xor_sync(0xffffffffu, last_nan, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_best[threadIdx.x >> 5] = best;
+    s_nan[threadIdx.x >> 5] = last_nan;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+    best = max(best, s_best[w]);
+    last_nan = max(last_nan, s_nan[w]);
+  }
+  ArgmaxScratch *sc = scratch + row;
+  if (best) atomicMax(&sc->best, best);
+  if (last_nan) atomicMax(&sc->last_nan, last_nan);
+  __threadfence();
+  if (atomicAdd(&sc->tickets, 1u) != (unsigned)(split - 1)) return;
+  // last CTA of the row: finish
+  __threadfence();
+  const unsigned long long gbest = atomicMax(&sc->best, 0ull);
+  const unsigned int gnan = atomicMax(&sc->last_nan, 0u);
+  unsigned int idx;
+  if (gnan == 0) {
+    idx = (unsigned int)(gbest & 0xffffffffull);
+  } else {
+    // replay of the CPU loop from the last NaN on: the NaN is taken, then replaced by whatever follows
+    idx = gnan - 1;
+    for (unsigned int i = gnan; i < (unsigned)n; ++i)
+      if (!(to_f32(x[idx]) > to_f32(x[i]))) idx = i;
+  }
+  out[row].idx = idx;
+  out[row].val = raw_bits(x[idx]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// seeded sampling: one CTA of 1024 threads per row
+// ------------------------------------------------------------------------------------------------
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int SCAN_ITEMS = 4;
+constexpr float KEEP_ARG = -16.7f;  // exp(-16.7) < 2^-24: anything below can never move a sum >= 1
+
+struct Pair64 {  // increment of the integer sum if it is even (d0) / odd (d1) before this span
+  long long d0, d1;
+};
+__device__ __forceinline__ Pair64 compose(Pair64 f, Pair64 g) {  // f first, then g
+  Pair64 h;
+  h.d0 = f.d0 + ((f.d0 & 1) ? g.d1 : g.d0);
+  h.d1 = f.d1 + (((1 + f.d1) & 1) ? g.d1 : g.d0);
+  return h;
+}
+__device__ __forceinline__ Pair64 shfl_up_pair(Pair64 p, int o) {
+  Pair64 r;
+  r.d0 = __shfl_up_sync(0xffffffffu, p.d0, o);
+  r.d1 = __shfl_up_sync(0xffffffffu, p.d1, o);
+  return r;
+}
+
+struct SampleShared {
+  int warp_cnt[16][32];
+  int warp_off[16][32];
+  int digit_base[16];
+  int tile_cnt[16];
+  int hist[16];
+  int scan_i[33];
+  float red_f[33];
+  Pair64 scan_p[33];
+  int kept;
+  int i0;
+  int cross;
+  int tail_flag;
+  float s;
+};
+
+// exclusive block scan of one int per thread; returns the exclusive prefix, *total = block total
+__device__ __forceinline__ int block_excl_scan(int v, int *scratch, int *total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = scratch[lane];
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += t;
+    }
+    scratch[lane] = winc - w;
+    if (lane == 31) scratch[32] = winc;
+  }
+  __syncthreads();
+  *total = scratch[32];
+  return scratch[warp] + inc - v;
+}
+
+template <class T> struct KeyBits;
+template <> struct KeyBits<__half> { static constexpr int bits = 16; };
+template <> struct KeyBits<float> { static constexpr int bits = 32; };
+
+// sort key: ascending key = descending value.  f16 rows get 16-bit keys (4 radix passes), f32 rows 32-bit.
+template <class T> __device__ __forceinline__ uint32_t sort_key(T v);
+template <> __device__ __forceinline__ uint32_t sort_key<float>(float v) { return ~ordered_key(v); }
+template <> __device__ __forceinline__ uint32_t sort_key<__half>(__half v) {
+  uint32_t h = __half_as_ushort(v);
+  if ((h & 0x7fffu) == 0) h = 0;  // -0 -> +0
+  const uint32_t k = (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+  return (~k) & 0xffffu;
+}
+template <class T> __device__ __forceinline__ float key_value(uint32_t key);
+template <> __device__ __forceinline__ float key_value<float>(uint32_t key) { return key_to_float(~key); }
+template <> __device__ __forceinline__ float key_value<__half>(uint32_t key) {
+  const uint32_t k = (~key) & 0xffffu;
+  const uint32_t h = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+template <class T>
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restrict__ logits, long long row_stride, int n,
+                                                                float temperature, float top_p, unsigned long long top_k,
+                                                                const float *__restrict__ seeds, float seed_scalar,
+                                                                char *__restrict__ ws, long long ws_row_bytes, KVPair *out) {
+  __shared__ SampleShared sh;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;
+  const T *x = byte_off(logits, (long long)row * row_stride);
+  uint2 *buf_a = reinterpret_cast<uint2 *>(ws + (long long)row * ws_row_bytes);
+  uint2 *buf_b = buf_a + n;
+  const float seed = seeds ? seeds[row] : seed_scalar;
+
+  // ---- S1: row maximum --------------------------------------------------------------------------
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += SAMPLE_THREADS) mx = fmaxf(mx, to_f32(x[i]));
+  mx = block_max(mx, sh.red_f);
+
+  // ---- S2: keep (in index order) every element that can still move the sum ----------------------
+  if (tid == 0) sh.kept = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += SAMPLE_THREADS * 8) {
+    const int i0 = base + tid * 8;
+    uint32_t keys[8];
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j;
+      bool keep = false;
+      if (i < n) {
+        const T v = x[i];
+        const float arg = __fdiv_rn(__fsub_rn(to_f32(v), mx), temperature);
+        keep = arg >= KEEP_ARG;
+        keys[j] = sort_key(v);
+      }
+      if (!keep) keys[j] = 0xffffffffu;  // marker; real keys of kept f32 elements are never all-ones (that is -NaN)
+      cnt += keep;
+    }
+    int total;
+    int off = block_excl_scan(cnt, sh.scan_i, &total) + sh.kept;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (keys[j] != 0xffffffffu) buf_a[off++] = make_uint2(keys[j], (uint32_t)(i0 + j));
+    __syncthreads();
+    if (tid == 0) sh.kept += total;
+    __syncthreads();
+  }
+  const int M = sh.kept;
+
+  // ---- S3: stable LSD radix sort of the kept prefix, 4 bits per pass ----------------------------
+  uint2 *src = buf_a, *dst = buf_b;
+  for (int shift = 0; shift < KeyBits<T>::bits; shift += 4) {
+    if (tid < 16) sh.hist[tid] = 0;
+    __syncthreads();
+    for (int base = 0; base < M; base += SAMPLE_THREADS) {
+      const int i = base + tid;
+      const int d = i < M ? (int)((src[i].x >> shift) & 15u) : 16;
+      const unsigned m = __match_any_sync(0xffffffffu, d);
+      if (d < 16 && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&sh.hist[d], __popc(m));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int acc = 0;
+      for (int d = 0; d < 16; ++d) {
+        sh.digit_base[d] = acc;
+        acc += sh.hist[d];
+      }
+    }
+    __syncthreads();
+    for (int base = 0; base < M; base += SAMPLE_THREADS) {
+      const int i = base + tid;
+      uint2 el = make_uint2(0, 0);
+      int d = 16;
+      if (i < M) {
+        el = src[i];
+        d = (int)((el.x >> shift) & 15u);
+      }
+      const unsigned m = __match_any_sync(0xffffffffu, d);
+      const int rank = __popc(m & ((1u << lane) - 1u));
+      if (tid < 512) (&sh.warp_cnt[0][0])[tid] = 0;
+      __syncthreads();
+      if (d < 16 && rank == 0) sh.warp_cnt[d][warp] = __popc(m);
+      __syncthreads();
+      if (warp < 16) {  // warp d scans the 32 per-warp counts of digit d
+        const int v = sh.warp_cnt[warp][lane];
+        int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int t = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += t;
+        }
+        sh.warp_off[warp][lane] = inc - v;
+        if (lane == 31) sh.tile_cnt[warp] = inc;
+      }
+      __syncthreads();
+      if (d < 16) dst[sh.digit_base[d] + sh.warp_off[d][warp] + rank] = el;
+      __syncthreads();
+      if (tid < 16) sh.digit_base[tid] += sh.tile_cnt[tid];
+      __syncthreads();
+    }
+    uint2 *t = src;
+    src = dst;
+    dst = t;
+  }
+  // sorted (key, idx) pairs are in `src`; `dst` is free: first M floats = e_i, next M floats = c_i
+  float *E = reinterpret_cast<float *>(dst);
+  float *C = E + n;
+
+  // ---- S4: e_i, then the exact serial prefix sums -----------------------------------------------
+  const float x0 = key_value<T>(src[0].x);
+  for (int i = tid; i < M; i += SAMPLE_THREADS) {
+    const float arg = __fdiv_rn(__fsub_rn(key_value<T>(src[i].x), x0), temperature);
+    E[i] = (float)exp((double)arg);
+  }
+  if (tid == 0) {
+    C[0] = 1.f;
+    sh.i0 = 1;
+    sh.s = 1.f;
+  }
+  __syncthreads();
+
+  while (true) {
+    const int i0 = sh.i0;
+    if (i0 >= M) break;
+    const float s = sh.s;
+    const int ex = (int)((__float_as_uint(s) >> 23) & 0xffu) - 127;   // s in [2^ex, 2^(ex+1))
+    const float u = __uint_as_float((uint32_t)(ex - 23 + 127) << 23);  // ulp of s
+    const float u_inv = __uint_as_float((uint32_t)(23 - ex + 127) << 23);
+    long long S = (long long)(s * u_inv);  // exact integer in [2^23, 2^24)
+    bool restarted = false;
+    for (int base = i0; base < M; base += SAMPLE_THREADS * SCAN_ITEMS) {
+      __syncthreads();
+      if (tid == 0) {
+        sh.cross = 0x7fffffff;
+        sh.tail_flag = (E[base] * u_inv < 0.5f) ? 1 : 0;  // sorted descending: nothing later can contribute
+      }
+      __syncthreads();
+      if (sh.tail_flag) {
+        const float cs = (float)S * u;
+        for (int i = base + tid; i < M; i += SAMPLE_THREADS) C[i] = cs;
+        __syncthreads();
+        if (tid == 0) {
+          sh.i0 = M;
+          sh.s = cs;
+        }
+        restarted = true;
+        break;
+      }
+      // per-thread span of SCAN_ITEMS consecutive elements
+      long long q[SCAN_ITEMS];
+      bool tie[SCAN_ITEMS];
+      Pair64 mine{0, 0};
+      const int first = base + tid * SCAN_ITEMS;
+#pragma unroll
+      for (int j = 0; j < SCAN_ITEMS; ++j) {
+        const int i = first + j;
+        q[j] = 0;
+        tie[j] = false;
+        if (i < M) {
+          const float a = E[i] * u_inv;  // exact power-of-two scaling, a < 2^24
+          const float fl = floorf(a);
+          const float r = a - fl;        // exact
+          q[j] = (long long)fl + (r > 0.5f ? 1 : 0);
+          tie[j] = r == 0.5f;
+        }
+        Pair64 el;
+        if (tie[j]) {
+          el.d0 = q[j] + (q[j] & 1);
+          el.d1 = q[j] + ((q[j] & 1) ^ 1);
+        } else {
+          el.d0 = el.d1 = q[j];
+        }
+        mine = compose(mine, el);
+      }
+      // inclusive scan of `mine` across the block (compose is associative, not commutative)
+      Pair64 inc = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        Pair64 t = shfl_up_pair(inc, o);
+        if (lane >= o) inc = compose(t, inc);
+      }
+      if (lane == 31) sh.scan_p[warp] = inc;
+      __syncthreads();
+      if (warp == 0) {
+        Pair64 w = sh.scan_p[lane];
+        Pair64 winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          Pair64 t = shfl_up_pair(winc, o);
+          if (lane >= o) winc = compose(t, winc);
+        }
+        // exclusive prefix of warps: shift down by one
+        Pair64 wex = shfl_up_pair(winc, 1);
+        if (lane == 0) wex = Pair64{0, 0};
+        sh.scan_p[lane] = wex;
+        if (lane == 31) sh.scan_p[32] = winc;
+      }
+      __syncthreads();
+      Pair64 lane_ex = shfl_up_pair(inc, 1);  // exclusive within the warp
+      if (lane == 0) lane_ex = Pair64{0, 0};
+      const Pair64 before = compose(sh.scan_p[warp], lane_ex);
+      long long St = S + ((S & 1) ? before.d1 : before.d0);
+#pragma unroll
+      for (int j = 0; j < SCAN_ITEMS; ++j) {
+        const int i = first + j;
+        if (i < M) {
+          St += q[j] + ((tie[j] && ((St + q[j]) & 1)) ? 1 : 0);
+          if (St >= (1ll << 24)) atomicMin(&sh.cross, i);
+          else C[i] = (float)St * u;
+        }
+      }
+      __syncthreads();
+      if (sh.cross != 0x7fffffff) {
+        if (tid == 0) {
+          const int ic = sh.cross;
+          const float c_new = __fadd_rn(C[ic - 1], E[ic]);  // the one add that changes binade: hardware f32
+          C[ic] = c_new;
+          sh.s = c_new;
+          sh.i0 = ic + 1;
+        }
+        restarted = true;
+        break;
+      }
+      const Pair64 tot = sh.scan_p[32];
+      S += (S & 1) ? tot.d1 : tot.d0;
+    }
+    __syncthreads();
+    if (!restarted) {
+      if (tid == 0) {
+        sh.i0 = M;
+        sh.s = (float)S * u;
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+
+  // ---- S5: threshold and pick -------------------------------------------------------------------
+  const unsigned long long kk = (top_k < (unsigned long long)n ? top_k : (unsigned long long)n) - 1ull;
+  const float pk = C[kk < (unsigned long long)M ? (int)kk : M - 1];
+  const float pp = __fmul_rn(C[M - 1], top_p);
+  const float plimit = __fmul_rn(seed, fminf(pk, pp));
+  int below = 0;
+  for (int i = tid; i < M; i += SAMPLE_THREADS) below += (C[i] < plimit) ? 1 : 0;
+  int total;
+  block_excl_scan(below, sh.scan_i, &total);
+  if (tid == 0) {
+    const int j = total < M ? total : M - 1;
+    out[row].idx = src[j].y;
+    out[row].val = raw_bits(from_f32<T>(C[j]));
+  }
+}
+
+struct SampleMeta {
+  uint32_t dt;
+  usz n;
+};
+
+static int sample_meta(const ops_random_sample_args *a, SampleMeta *m) {
+  if (a->kv_pair.dt != OPS_DT_KVPAIR) return fail(OPS_TYPE_NOT_SUPPORT, "output must be KVpair");
+  m->dt = a->logits.dt;
+  if (dt_size(m->dt) > 4 || dt_size(m->dt) == 0) return fail(OPS_TYPE_NOT_SUPPORT, "element too large");
+  if (a->indices.dt != OPS_DT_U32) return fail(OPS_TYPE_NOT_SUPPORT, "indices must be u32");
+  if (a->logits.ndim != 1) return fail(OPS_RANK_NOT_SUPPORT, "logits.ndim = %u, 1 expected", a->logits.ndim);
+  if (a->indices.ndim != 1) return fail(OPS_RANK_NOT_SUPPORT, "indices.ndim = %u, 1 expected", a->indices.ndim);
+  m->n = a->logits.shape[0];
+  return OPS_OK;
+}
+
+static inline bool is_argmax(const ops_sample_args &c) { return c.temperature == 0.f || c.top_k == 1; }
+
+static usz argmax_ws(usz rows) { return rows * sizeof(ArgmaxScratch); }
+static usz sample_ws_row(usz n) { return (n * 16 + 255) / 256 * 256; }
+
+static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const void *logits, isz row_stride, void *kv_out,
+                       const ops_sample_args &cfg, const float *seeds_dev, float seed_scalar, void *ws, usz ws_len,
+                       cudaStream_t s) {
+  if (dt != OPS_DT_F16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "random_sample: f16 or f32 logits expected");
+  if (rows == 0) return OPS_OK;
+  if (n == 0) return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: empty logits");
+  if (n > 0x7fffffffu / 16 || rows > 0x7fffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: shape too large");
+  if (!logits || !kv_out) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: null base pointer at launch");
+  cudaSetDevice(base.device);
+  if (is_argmax(cfg)) {
+    const usz need = argmax_ws(rows);
+    if (ws_len < need || !ws) return need_workspace(need);
+    cudaMemsetAsync(ws, 0, need, s);
+    // split a row over several CTAs when there are few rows; keep >= 8 KiB per CTA
+    const usz row_bytes = n * dt_size(dt);
+    usz split = (2 * (usz)base.sm_count + rows - 1) / rows;
+    const usz max_split = (row_bytes + 8191) / 8192;
+    if (split > max_split) split = max_split;
+    if (split < 1) split = 1;
+    const unsigned grid = (unsigned)(rows * split);
+    if (dt == OPS_DT_F16)
+      argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half *)logits, row_stride, (int)n, (int)split, (ArgmaxScratch *)ws, (KVPair *)kv_out);
+    else
+      argmax_kernel<float><<<grid, 256, 0, s>>>((const float *)logits, row_stride, (int)n, (int)split, (ArgmaxScratch *)ws, (KVPair *)kv_out);
+    return check_launch("random_sample(argmax)");
+  }
+  if (!(cfg.temperature > 0.f)) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: temperature must be >= 0");
+  if (cfg.top_k == 0 || !(cfg.top_p > 0.f)) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: top_k and top_p must be positive");
+  const usz per_row = sample_ws_row(n);
+  const usz need = per_row * rows;
+  if (ws_len < need || !ws) return need_workspace(need);
+  if (!aligned(ws, 16)) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: workspace must be 16-byte aligned");
+  const float top_p = cfg.top_p > 1.f ? 1.f : cfg.top_p;
+  if (dt == OPS_DT_F16)
+    sample_kernel<__half><<<(unsigned)rows, SAMPLE_THREADS, 0, s>>>((const __half *)logits, row_stride, (int)n, cfg.temperature, top_p,
+                                                                    (unsigned long long)cfg.top_k, seeds_dev, seed_scalar, (char *)ws,
+                                                                    (long long)per_row, (KVPair *)kv_out);
+  else
+    sample_kernel<float><<<(unsigned)rows, SAMPLE_THREADS, 0, s>>>((const float *)logits, row_stride, (int)n, cfg.temperature, top_p,
+                                                                   (unsigned long long)cfg.top_k, seeds_dev, seed_scalar, (char *)ws,
+                                                                   (long long)per_row, (KVPair *)kv_out);
+  return check_launch("random_sample(sample)");
+}
+
+}  // namespace ops
+
+using namespace ops;
+
+OPS_DEFINE_SIMPLE_HANDLE(random_sample)
+
+OPS_API int ops_sample_args_new(float temperature, float top_p, size_t top_k, ops_sample_args *out) {
+  if (temperature < 0.f) return 1;
+  if (top_k == 0 || top_p <= 0.f) return 2;
+  out->temperature = temperature;
+  out->top_p = top_p < 1.f ? top_p : 1.f;
+  out->top_k = top_k;
+  return 0;
+}
+
+OPS_API size_t ops_random_sample_batched_workspace(uint32_t dt, size_t rows, size_t n, const ops_sample_args *config) {
+  (void)dt;
+  return is_argmax(*config) ? argmax_ws(rows) : sample_ws_row(n) * rows;
+}
+
+// Like the crate's GPU operator (operators/src/random_sample/cuda/mod.rs:58-81) the reported size
+// covers both modes when it fits, else the smaller one, else 0.
+OPS_API int ops_random_sample_scheme(ops_random_sample *op, const ops_random_sample_args *args, size_t max_ws, size_t *ws_out) {
+  (void)op;
+  SampleMeta m;
+  OPS_TRY(sample_meta(args, &m));
+  if (ws_out) {
+    *ws_out = 0;
+    if (!dyn(m.n)) {
+      const usz big = sample_ws_row(m.n), small = argmax_ws(1);
+      *ws_out = big <= max_ws ? big : (small <= max_ws ? small : 0);
+    }
+  }
+  return OPS_OK;
+}
+
+OPS_API int ops_random_sample_launch(const ops_random_sample *op, const ops_random_sample_args *a, void *ws, size_t ws_len, void *stream) {
+  SampleMeta m;
+  OPS_TRY(sample_meta(a, &m));
+  const isz st = a->logits.strides[0];
+  if (dyn(st) || st != (isz)dt_size(m.dt)) return fail(OPS_STRIDES_NOT_SUPPORT, "random_sample: logits must be contiguous");
+  if (dyn(m.n)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: n must be static at launch");
+  return launch_rows(op->base, m.dt, 1, m.n, a->logits_base, 0, a->kv_pair_base, a->config, nullptr, a->seed, ws, ws_len, (cudaStream_t)stream);
+}
+
+OPS_API int ops_random_sample_launch_batched(const ops_random_sample *op, uint32_t dt, size_t rows, size_t n, const void *logits_base,
+                                             ptrdiff_t row_stride, void *kv_pairs_base, const ops_sample_args *config,
+                                             const float *seeds_dev, void *ws, size_t ws_len, void *stream) {
+  if (!is_argmax(*config) && !seeds_dev) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: batched sampling needs one seed per row");
+  return launch_rows(op->base, dt, rows, n, logits_base, row_stride, kv_pairs_base, *config, seeds_dev, 0.f, ws, ws_len, (cudaStream_t)stream);
+}
+
+OPS_API int ops_random_sample_build_indices(size_t n, uint32_t *host_out) {
+  for (size_t i = 0; i < n; ++i) host_out[i] = (uint32_t)i;
+  return OPS_OK;
+}

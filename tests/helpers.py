@@ -1,0 +1,32 @@
+"""Shared comparison helpers for the parity tests."""
+import numpy as np
+
+F16_EPS = 9.765625e-4  # f16::EPSILON, the absolute threshold of every reference test
+
+
+def max_abs(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref.astype(np.float64)).max()) if got.size else 0.0
+
+
+def assert_close(got, ref, tol=1e-2, what=""):
+    """BASELINE tolerance: max-abs error after f32 accumulation, f16 outputs."""
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert np.isfinite(got.astype(np.float32)).all(), f"{what}: non-finite output"
+    err = max_abs(got, ref)
+    assert err <= tol, f"{what}: max-abs {err} > {tol}"
+
+
+def error_collector(got, ref64, abs_thr=F16_EPS, rel_thr=0.0):
+    """The reference's own acceptance rule (operators/src/common/mod.rs:66-112): an element is an outlier
+    when abs diff > abs_thr AND rel diff > rel_thr, rel = |a-b| / (|a|+|b|+eps); pass when outliers*1000 <= count."""
+    a = got.astype(np.float64).ravel()
+    b = ref64.astype(np.float64).ravel()
+    d = np.abs(a - b)
+    rel = d / (np.abs(a) + np.abs(b) + np.finfo(np.float64).eps)
+    outliers = int(((d > abs_thr) & (rel > rel_thr)).sum())
+    return outliers, a.size
+
+
+def assert_reference_rule(got, ref64, rel_thr, what=""):
+    out, cnt = error_collector(got, ref64, F16_EPS, rel_thr)
+    assert out * 1000 <= cnt, f"{what}: {out}/{cnt} outliers under the reference's rule (rel {rel_thr})"

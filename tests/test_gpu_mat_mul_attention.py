@@ -1,0 +1,179 @@
+"""GPU parity of mat_mul, attention and attention_kv_cached against the CPU oracle, through the C ABI.
+
+mat_mul: the reference's test shapes (batch 4, k 2048, n 5632, m in {1,7,64,255,1024}, alpha 0.5,
+beta 1; operators/src/mat_mul/cuda/mod.rs:137-254), every operand-major combination, ragged edges,
+broadcast batches and layouts the tensor-core path cannot take.  attention: the reference's shape
+(nh 32, nkvh 4, seq 7, att 127, dh 64; operators/src/attention/cuda.rs:75-159), BASELINE config 2 at
+reduced and full size.  Tolerances are written at each assert.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close, assert_reference_rule
+
+pytestmark = pytest.mark.gpu
+
+
+def to_dev(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def gemm_case(pkg, orc, synth, dev, batch, m, n, k, a_t, b_t, c_t, alpha, beta, seed=1, bcast_b=False):
+    """a_t/b_t/c_t: the matrix is stored transposed (column-major view)."""
+    bs = () if batch is None else (batch,)
+    a_store = synth.normal(seed, bs + ((k, m) if a_t else (m, k)), 1.0).astype(np.float16)
+    bsb = () if (batch is None or bcast_b) else (batch,)
+    b_store = synth.normal(seed + 1, bsb + ((n, k) if b_t else (k, n)), 1.0 / np.sqrt(max(k, 1))).astype(np.float16)
+    c_store = synth.normal(seed + 2, bs + ((n, m) if c_t else (m, n)), 1.0).astype(np.float16)
+    ad, bd, cd = to_dev(a_store, dev), to_dev(b_store, dev), to_dev(c_store, dev)
+    view = lambda t, tr: t.transpose(-1, -2) if tr else t
+    av, bv, cv = view(ad, a_t), view(bd, b_t), view(cd, c_t)
+    na = np.swapaxes(a_store, -1, -2) if a_t else a_store  # logical [.., m, k]
+    nb = np.swapaxes(b_store, -1, -2) if b_t else b_store  # logical [.., k, n]
+    nc = c_store.copy()
+    ncv = np.swapaxes(nc, -1, -2) if c_t else nc
+    if bcast_b and batch is not None:
+        bv = bv.unsqueeze(0)  # [1, k, n]: batch-1 operand broadcasts (operators/src/mat_mul/args.rs:152-156,176-178)
+        nb = nb[None]
+    mm = pkg.MatMul(0)
+    mm.launch(pkg.MatMulArgs.of(cv, beta, av, bv, alpha))
+    orc.mat_mul(ncv, beta, na, nb, alpha)
+    torch.cuda.synchronize()
+    assert mm.status() == 0, f"tensor-core kernel reported a timed-out wait: {mm.status()}"
+    got = cd.cpu().numpy()
+    # f16 output of magnitude ~1-3: one f16 ulp is up to 2e-3; 1e-2 is the BASELINE budget
+    assert_close(got, nc, 1e-2, f"mat_mul m{m} n{n} k{k}")
+    return got, nc
+
+
+@pytest.mark.parametrize("m", [1, 7, 64, 255, 1024])
+def test_mat_mul_reference_shapes(pkg, orc, synth, dev, m):
+    got, ref = gemm_case(pkg, orc, synth, dev, 4, m, 5632, 2048, False, False, False, 0.5, 1.0)
+    # reference rule against an f64 oracle, rel 5e-3
+    bs, k, n = 4, 2048, 5632
+    a = synth.normal(1, (bs, m, k), 1.0).astype(np.float16).astype(np.float64)
+    b = synth.normal(2, (bs, k, n), 1.0 / np.sqrt(k)).astype(np.float16).astype(np.float64)
+    c = synth.normal(3, (bs, m, n), 1.0).astype(np.float16).astype(np.float64)
+    assert_reference_rule(got, 1.0 * c + 0.5 * np.matmul(a, b), 5e-3, "mat_mul")
+
+
+@pytest.mark.parametrize("a_t,b_t,c_t", [(False, False, False), (False, True, False), (True, False, False), (True, True, False),
+                                         (False, False, True), (True, True, True), (False, True, True)])
+def test_mat_mul_majors(pkg, orc, synth, dev, a_t, b_t, c_t):
+    gemm_case(pkg, orc, synth, dev, None, 384, 512, 320, a_t, b_t, c_t, 1.0, 0.0, seed=10)
+    gemm_case(pkg, orc, synth, dev, 3, 200, 264, 136, a_t, b_t, c_t, 0.75, 0.5, seed=20)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (129, 257, 72), (1, 8, 8), (300, 96, 1000), (128, 128, 4096), (257, 520, 200),
+                                   (64, 5000, 128), (2000, 24, 64)])
+def test_mat_mul_edges(pkg, orc, synth, dev, m, n, k):
+    gemm_case(pkg, orc, synth, dev, None, m, n, k, False, False, False, 1.0, 0.0, seed=30)
+    gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 1.0, 1.0, seed=40)
+
+
+def test_mat_mul_broadcast_and_unaligned(pkg, orc, synth, dev):
+    gemm_case(pkg, orc, synth, dev, 5, 96, 160, 64, False, False, False, 1.0, 0.0, seed=50, bcast_b=True)
+    # k = 30 / n = 50: strides that TMA cannot describe -> generic kernel, same answers
+    gemm_case(pkg, orc, synth, dev, 2, 33, 50, 30, False, False, False, 0.5, 1.0, seed=60)
+    gemm_case(pkg, orc, synth, dev, None, 17, 9, 5, True, True, True, 1.0, 0.0, seed=70)
+
+
+def test_mat_mul_f32(pkg, orc, synth, dev):
+    a = synth.normal(1, (70, 90), 1.0)
+    b = synth.normal(2, (90, 50), 0.1)
+    c = synth.normal(3, (70, 50), 1.0)
+    cd = to_dev(c, dev)
+    pkg.MatMul(0).launch(pkg.MatMulArgs.of(cd, 0.25, to_dev(a, dev), to_dev(b, dev), 2.0))
+    ref = orc.mat_mul(c.copy(), 0.25, a, b, 2.0)
+    np.testing.assert_allclose(cd.cpu().numpy(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_mat_mul_llama_shape_sampled(pkg, orc, synth, dev):
+    # one of the config-3 GEMMs at full size on the GPU: [4096,4096] x [4096,6144]; the oracle checks 24 sampled
+    # rows (rows of a product are independent)
+    g = torch.Generator(device=dev).manual_seed(5)
+    a = torch.randn(4096, 4096, generator=g, device=dev).half()
+    w = (torch.randn(4096, 6144, generator=g, device=dev) * 0.02).half()
+    c = torch.empty(4096, 6144, dtype=torch.float16, device=dev)
+    mm = pkg.MatMul(0)
+    mm.launch(pkg.MatMulArgs.of(c, 0.0, a, w, 1.0))
+    torch.cuda.synchronize()
+    assert mm.status() == 0
+    rows = sorted(set([0, 127, 128, 4095] + list(np.random.default_rng(0).integers(0, 4096, 20))))
+    ref = orc.mat_mul(np.zeros((len(rows), 6144), np.float16), 0.0, a[rows].cpu().numpy(), w.cpu().numpy(), 1.0)
+    assert_close(c[rows].cpu().numpy(), ref, 1e-2, "QKV projection")
+
+
+# ------------------------------------------------------------------------------------------ attention
+def attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, token_major, causal=True, seed=100):
+    q = synth.normal(seed, (seq, nh, dh) if token_major else (nh, seq, dh), 1.0).astype(np.float16)
+    k = synth.normal(seed + 1, (nkvh, att, dh), 1.0).astype(np.float16)
+    v = synth.normal(seed + 2, (nkvh, att, dh), 1.0).astype(np.float16)
+    qd, kd, vd = to_dev(q, dev), to_dev(k, dev), to_dev(v, dev)
+    od = torch.zeros_like(qd)
+    qv = qd.permute(1, 0, 2) if token_major else qd
+    ov = od.permute(1, 0, 2) if token_major else od
+    op = pkg.Attention(0)
+    args = pkg.AttentionArgs.of(qv, kd, vd, ov, pkg.MASK_CAUSAL if causal else pkg.MASK_NONE)
+    need = op.scheme(args)
+    assert need == (nh * seq * dh + nh * seq * att) * 2
+    op.launch(args, torch.empty(need, dtype=torch.uint8, device=dev))
+    qn, on = q.copy(), np.zeros_like(q)
+    orc.attention(np.swapaxes(qn, 0, 1) if token_major else qn, k, v, np.swapaxes(on, 0, 1) if token_major else on, causal)
+    # outputs are convex combinations of N(0,1) values: |o| < ~4, f16 ulp <= 2e-3; BASELINE budget 1e-2
+    assert_close(od.cpu().numpy(), on, 1e-2, "attention")
+    if not token_major:  # head-major q merges (nh, seq): the crate overwrites q with the result, so do we
+        assert_close(qd.cpu().numpy(), qn, 1e-2, "attention (q clobbered)")
+    return od
+
+
+@pytest.mark.parametrize("token_major", [False, True])
+def test_attention_reference_shape(pkg, orc, synth, dev, token_major):
+    attention_case(pkg, orc, synth, dev, 32, 4, 7, 127, 64, token_major)
+
+
+@pytest.mark.parametrize("nh,nkvh,seq,att,dh", [(8, 2, 64, 64, 128), (4, 4, 130, 130, 64), (8, 1, 1, 300, 128), (6, 3, 33, 257, 32)])
+def test_attention_shapes(pkg, orc, synth, dev, nh, nkvh, seq, att, dh):
+    attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, True)
+    attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, False, causal=False)
+
+
+def test_attention_workspace_fallback(pkg, orc, synth, dev):
+    # no workspace given: launch reports the need, the host side allocates and retries (Workspace::new)
+    nh, nkvh, seq, att, dh = 4, 2, 16, 48, 64
+    q = synth.normal(1, (nh, seq, dh), 1.0).astype(np.float16)
+    k = synth.normal(2, (nkvh, att, dh), 1.0).astype(np.float16)
+    v = synth.normal(3, (nkvh, att, dh), 1.0).astype(np.float16)
+    qd, od = to_dev(q, dev), torch.zeros(nh, seq, dh, dtype=torch.float16, device=dev)
+    pkg.Attention(0).launch(pkg.AttentionArgs.of(qd, to_dev(k, dev), to_dev(v, dev), od))
+    on = np.zeros_like(q)
+    orc.attention(q.copy(), k, v, on, True)
+    assert_close(od.cpu().numpy(), on, 1e-2, "attention, internal workspace")
+
+
+def test_attention_config2_prefill(pkg, orc, synth, dev):
+    # BASELINE config 2 at full size: q [32,2048,128], k/v [8,2048,128]; the oracle runs the whole thing (a few seconds)
+    attention_case(pkg, orc, synth, dev, 32, 8, 2048, 2048, 128, False, seed=0xB2000020)
+
+
+def test_attention_kv_cached(pkg, orc, synth, dev):
+    # the reference's shape (operators/src/attention_kv_cached/cuda.rs:89-93): nh 32, nkvh 4, seq 7, pos 13, dh 64
+    nh, nkvh, seq, pos, dh, buf = 32, 4, 7, 13, 64, 40
+    q = synth.normal(1, (nh, seq, dh), 1.0).astype(np.float16)
+    k = synth.normal(2, (nkvh, seq, dh), 1.0).astype(np.float16)
+    v = synth.normal(3, (nkvh, seq, dh), 1.0).astype(np.float16)
+    kc = synth.normal(4, (nkvh, buf, dh), 1.0).astype(np.float16)
+    vc = synth.normal(5, (nkvh, buf, dh), 1.0).astype(np.float16)
+    qd, kd, vd, kcd, vcd = (to_dev(t, dev) for t in (q, k, v, kc, vc))
+    od = torch.zeros_like(qd)
+    op = pkg.AttentionKvCached(0)
+    op.launch(pkg.AttentionKvCachedArgs.of(qd, kd, vd, od, kcd, vcd, pos))
+    on = np.zeros_like(q)
+    orc.attention_kv_cached(q.copy(), k, v, on, kc, vc, pos, True)
+    np.testing.assert_array_equal(kcd.cpu().numpy().view(np.uint16), kc.view(np.uint16))  # cache writes are byte-exact
+    np.testing.assert_array_equal(vcd.cpu().numpy().view(np.uint16), vc.view(np.uint16))
+    assert_close(od.cpu().numpy(), on, 1e-2, "attention_kv_cached")
+    with pytest.raises(pkg.LaunchError) as e:
+        op.launch(pkg.AttentionKvCachedArgs.of(qd, kd, vd, od, kcd, vcd, buf - seq + 1))
+    assert e.value.kind == pkg.SHAPE_MISMATCH and "Out of cache buffer" in e.value.info
