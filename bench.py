@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""bench.py — layer tokens/s of the Llama-3-8B-shaped decoder-layer operator chain on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" = one pass of the operator chain (rms_norm, mat_mul QKV, rope, attention, mat_mul O, [all_reduce],
+rms_norm, mat_mul gate|up, swiglu, mat_mul down, [all_reduce]) over one batch of synthetic tokens:
+  N = 1 : BASELINE config 3 (4096 tokens, d 4096, 32/8 heads, dh 128, ffn 14336, f16, random init);
+  N > 1 : config 4, the same layer tensor-parallel over N GPUs with f16 sum all_reduce of the [T, 4096] partials
+          (total work fixed -> "scaling": "strong").
+`value` is device-timed (CUDA events on the launching stream, max over ranks) with the inputs resident in HBM;
+`e2e` is the same chain called through the package's public API with the step's activations in pinned HOST memory:
+host->device copy of x, the chain, device->host copy of the result, all inside the timed region.
+`roofline` describes the dominant kernel (the gate|up tensor-core GEMM launch) from CUDA events recorded around
+every operator inside the timed region; `ops` lists every operator the same way.
+`cpu_baseline` (rank 0, N = 1) times the CPU oracle — the restated common_cpu operators, the reference crate itself
+cannot be built without a Rust toolchain — on a bounded token sample of the same layer.
+`--impl reference` runs only that CPU arm and prints it in the same format.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as graft  # noqa: E402
+
+CFG = dict(d=4096, nh=32, nkvh=8, dh=128, ffn=14336, theta=5e5, eps=1e-5)
+WORKLOAD = "BASELINE config 3: Llama-3-8B-shaped decoder layer, 4096 tokens, d=4096, 32q/8kv heads, dh=128, ffn=14336, f16, random init"
+SEED = 0xB2000030
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken DURING the timed regions."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                                          "-i", str(gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.flush()
+        self.out.seek(0)
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.out.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.out.name)
+        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def make_weights(torch, device, cfg):
+    """Random-init weights of the config-3 layer: N(0, 0.02) projections, U(0.5, 1.5) norm weights; same on every rank."""
+    g = torch.Generator(device=device).manual_seed(SEED)
+    d, nh, nkvh, dh, ffn = cfg["d"], cfg["nh"], cfg["nkvh"], cfg["dh"], cfg["ffn"]
+
+    def proj(r, c):
+        return (torch.randn(r, c, generator=g, device=device, dtype=torch.float32) * 0.02).half()
+
+    def norm():
+        return (torch.rand(d, generator=g, device=device, dtype=torch.float32) + 0.5).half()
+
+    return {"w_norm1": norm(), "w_qkv": proj(d, (nh + 2 * nkvh) * dh), "w_o": proj(nh * dh, d), "w_norm2": norm(),
+            "w_gu": proj(d, 2 * ffn), "w_down": proj(ffn, d)}
+
+
+def cpu_layer_baseline(tokens, repeats, warmup):
+    """Times the CPU oracle's decoder layer on `tokens` tokens.  Returns (tokens/s, threads, seconds per pass)."""
+    import numpy as np
+    orc = graft.load_oracle()
+    orc.lib()
+    graft.load_package()
+    pkg_synth = __import__("importlib").import_module(graft.PKG_NAME + ".synth")
+    rng_seed = SEED
+    d, nh, nkvh, dh, ffn = CFG["d"], CFG["nh"], CFG["nkvh"], CFG["dh"], CFG["ffn"]
+    w = {"w_norm1": pkg_synth.uniform(rng_seed + 1, (d,), 0.5, 1.5).astype(np.float16),
+         "w_norm2": pkg_synth.uniform(rng_seed + 2, (d,), 0.5, 1.5).astype(np.float16)}
+    rng = np.random.default_rng(rng_seed)  # fast generator: the weights' values do not affect the timing
+    for name, shape in (("w_qkv", (d, (nh + 2 * nkvh) * dh)), ("w_o", (nh * dh, d)), ("w_gu", (d, 2 * ffn)), ("w_down", (ffn, d))):
+        w[name] = (rng.standard_normal(shape, dtype=np.float32) * 0.02).astype(np.float16)
+    x = rng.standard_normal((tokens, d), dtype=np.float32).astype(np.float16)
+    pos = np.arange(tokens, dtype=np.uint32)
+    times = []
+    for i in range(warmup + repeats):
+        t0 = time.perf_counter()
+        orc.decoder_layer(x, pos, [w], CFG)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return tokens / sec, orc.num_threads(), sec
+
+
+def run_reference(args, rank):
+    """--impl reference: the CPU arm alone (rank 0 only under torchrun)."""
+    if rank != 0:
+        return
+    tokens = args.ref_tokens
+    tps, threads, sec = cpu_layer_baseline(tokens, max(args.steps, 1), min(args.warmup, 1))
+    sample = f"{tokens}-token causal sequence through the full-width layer per step (same weights' shapes as config 3)"
+    line = {"impl": "reference", "metric": "layer_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic", "config": {"workload": WORKLOAD, "sample_tokens": tokens},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": sample + "; restated common_cpu operators (the Rust crate cannot be built here: no rustc/cargo)"},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--ref-tokens", type=int, default=512, help="tokens per step of the CPU arm")
+    ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the cpu_baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path (use --impl reference for the CPU arm)")
+    pkg = graft.load_package()
+    layer_mod = __import__("importlib").import_module(graft.PKG_NAME + ".layer")
+    tp = world
+    assert tp == max(args.gpus, 1) or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    comm = None
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        ids = [pkg.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = pkg.Comm(local_rank, rank, world, ids[0])
+        if args.all_reduce in ("auto", "one_shot", "two_shot"):
+            handle = comm.p2p_export(args.tokens * CFG["d"] * 2)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            comm.p2p_attach(handles)
+    algo = {"auto": pkg.ALL_REDUCE_AUTO, "nccl": pkg.ALL_REDUCE_NCCL, "one_shot": pkg.ALL_REDUCE_P2P_ONE_SHOT,
+            "two_shot": pkg.ALL_REDUCE_P2P_TWO_SHOT}[args.all_reduce]
+
+    cfg = layer_mod.LayerConfig(**CFG)
+    T = args.tokens
+    full = make_weights(torch, device, CFG)
+    shard = layer_mod.shard_weights(full, rank, tp, cfg) if tp > 1 else full
+    if tp > 1:
+        del full
+        torch.cuda.empty_cache()
+    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo)
+    g = torch.Generator(device=device).manual_seed(SEED + 7)
+    x0 = torch.randn(T, CFG["d"], generator=g, device=device, dtype=torch.float32).half()
+    x = torch.empty_like(x0)
+    pos = torch.arange(T, dtype=torch.int32, device=device).view(torch.uint32)
+    copy = pkg.Rearrange(local_rank)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(marks=None):
+        copy.launch(pkg.RearrangeArgs.of(x, x0))  # fresh residual stream (the chain updates it in place)
+        return layer.forward(x, pos, marks)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- timed region 1: device-resident inputs, events around every operator -------------------------------
+    sampler = ClockSampler(local_rank)
+    names = [n for n in layer.STEPS if tp > 1 or not n.startswith("all_reduce")]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record(stream)
+    for s in range(args.steps):
+        copy.launch(pkg.RearrangeArgs.of(x, x0))
+        ev[s][0].record(stream)
+        k = [0]
+
+        def mark(name, s=s, k=k):
+            k[0] += 1
+            ev[s][k[0]].record(stream)
+
+        layer.forward(x, pos, mark)
+    t_end.record(stream)
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+
+    # ---- timed region 2: end to end through the public API with host buffers ---------------------------------
+    xh = x0.cpu().pin_memory()
+    outh = torch.empty_like(xh).pin_memory()
+    for _ in range(2):
+        x.copy_(xh, non_blocking=True)
+        outh.copy_(layer.forward(x, pos), non_blocking=True)
+    barrier()
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_begin.record(stream)
+    for _ in range(args.steps):
+        x.copy_(xh, non_blocking=True)
+        outh.copy_(layer.forward(x, pos), non_blocking=True)
+    e_end.record(stream)
+    barrier()
+    e2e_ms = e_begin.elapsed_time(e_end)
+    clocks = sampler.stop()
+
+    if dist is not None:
+        tt = torch.tensor([total_ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = float(tt[0]), float(tt[1])
+
+    # per-operator durations (this rank), averaged over the timed steps
+    op_ms = {n: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps for i, n in enumerate(names)}
+    peaks = measured_peaks()
+    E = 2
+    d, ffn_l, nq, nkv, dh = CFG["d"], CFG["ffn"] // tp, CFG["nh"] // tp, CFG["nkvh"] // tp, CFG["dh"]
+    qkv_cols = (nq + 2 * nkv) * dh
+    causal_pairs = T * (T + 1) // 2
+    work = {  # algorithmic work per launch: ("hbm", bytes) or ("tensor", flops)
+        "rms_norm_1": ("hbm", 2 * T * d * E + d * E), "rms_norm_2": ("hbm", 2 * T * d * E + d * E),
+        "rope": ("hbm", 2 * T * (nq + nkv) * dh * E + T * 4),
+        "swiglu": ("hbm", 3 * T * ffn_l * E),
+        "mat_mul_qkv": ("tensor", 2 * T * d * qkv_cols), "mat_mul_o": ("tensor", 2 * T * nq * dh * d),
+        "mat_mul_gate_up": ("tensor", 2 * T * d * 2 * ffn_l), "mat_mul_down": ("tensor", 2 * T * ffn_l * d),
+        "attention": ("tensor", 4 * nq * dh * causal_pairs),
+        "all_reduce_1": ("nvlink", 2 * (tp - 1) / max(tp, 1) * T * d * E), "all_reduce_2": ("nvlink", 2 * (tp - 1) / max(tp, 1) * T * d * E),
+    }
+    ops = {}
+    for n in names:
+        kind, amount = work[n]
+        ms = op_ms[n]
+        if kind == "hbm":
+            ach = amount / (ms * 1e-3) / 1e9
+            ops[n] = {"ms": ms, "bound": "hbm", "achieved": ach, "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
+        elif kind == "tensor":
+            ach = amount / (ms * 1e-3) / 1e12
+            ops[n] = {"ms": ms, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tflops_sustained"]}
+        else:
+            ach = amount / (ms * 1e-3) / 1e9
+            ops[n] = {"ms": ms, "bound": "nvlink", "achieved": ach, "unit": "GB/s (bus)", "frac": ach / 770.0}
+    dom = ops["mat_mul_gate_up"]
+    roofline = {"kernel": "gemm_f16_tcgen05_kernel<256> (mat_mul gate|up launch)", "bound": "tensor", "achieved": dom["achieved"],
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": dom["frac"], "traffic": None,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (kernel timed inside a long step)",
+                "algorithmic_flops_per_launch": work["mat_mul_gate_up"][1]}
+
+    if rank != 0:
+        if comm is not None:
+            barrier()
+            dist.destroy_process_group()
+        return
+    ms_per_step = total_ms / args.steps
+    kernels_per_step = 1 + 2 + 4 + 1 + 1 + 5  # copy, rms_norm x2, mat_mul x4, rope, swiglu, attention chain (2 rearranges, 2 mat_mul, softmax)
+    if tp > 1 and args.all_reduce != "nccl":
+        kernels_per_step += 2
+    line = {
+        "metric": "layer_tokens_per_s", "value": T * args.steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD if tp == 1 else WORKLOAD.replace("config 3", "config 4") + f", tensor-parallel over {tp} GPUs",
+                   "tokens": T, "parallelism": f"tp{tp}", "all_reduce": args.all_reduce if tp > 1 else None,
+                   "l2": "inputs larger than L2: every step streams 436 MB of weights and a 1 GiB score matrix through a 126 MB L2",
+                   "attention": "operator chain (rearrange, mat_mul, fused_softmax, mat_mul, rearrange) with the score matrix in workspace"},
+        "clocks": clocks,
+        "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * d * E, "d2h_bytes_per_step": T * d * E,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": kernels_per_step * args.steps,
+        "roofline": roofline,
+        "ops": ops,
+    }
+    if tp == 1 and not args.no_cpu_baseline:
+        tps, threads, sec = cpu_layer_baseline(args.cpu_tokens, 1, 0)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": f"one pass over a {args.cpu_tokens}-token causal sequence through the full-width layer "
+                                          f"({sec:.1f} s); restated common_cpu operators (the Rust crate cannot be built here)"}
+    print(json.dumps(line), flush=True)
+    if comm is not None:
+        barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -178,8 +178,10 @@ def _vp(v):
 
 
 class _ArgsBase:
-    """Keeps the TensorLayouts alive next to the ctypes struct that points into them."""
+    """Keeps the TensorLayouts — and the tensors whose base pointers were taken — alive next to the ctypes struct
+    that points into them (a tensor that dies before launch would hand its memory back to the allocator)."""
     c = None
+    _alive = ()
 
     def byref(self):
         return ctypes.byref(self.c)
@@ -228,6 +230,7 @@ class RmsNormArgs(_ArgsBase):
     """rms_norm::Args (operators/src/rms_norm/args.rs:7-15)."""
 
     def __init__(self, y_layout, y_base, x_layout, x_base, w_layout, w_base, epsilon):
+        self._alive = (y_base, x_base, w_base,)
         self.keep = (_lay(y_layout), _lay(x_layout), _lay(w_layout))
         self.c = _RmsNormArgs(self.keep[0].c, _vp(y_base), self.keep[1].c, _vp(x_base), self.keep[2].c, _vp(w_base), epsilon)
 
@@ -240,6 +243,7 @@ class RopeArgs(_ArgsBase):
     """rope::Args (operators/src/rope/args.rs:8-18)."""
 
     def __init__(self, t_layout, t_base, p_layout, p_base, sin_layout, sin_base, cos_layout, cos_base, theta):
+        self._alive = (t_base, p_base, sin_base, cos_base,)
         self.keep = (_lay(t_layout), _lay(p_layout), _lay(sin_layout), _lay(cos_layout))
         self.c = _RopeArgs(self.keep[0].c, _vp(t_base), self.keep[1].c, _vp(p_base), self.keep[2].c, _vp(sin_base),
                            self.keep[3].c, _vp(cos_base), theta)
@@ -256,6 +260,7 @@ class FusedSoftmaxArgs(_ArgsBase):
     """fuesd_softmax::Args (operators/src/fuesd_softmax/args.rs:5-9)."""
 
     def __init__(self, att_mask, att_layout, att_base):
+        self._alive = (att_base,)
         self.keep = (_lay(att_layout),)
         self.c = _SoftmaxArgs(att_mask, self.keep[0].c, _vp(att_base))
 
@@ -268,6 +273,7 @@ class SwigluArgs(_ArgsBase):
     """swiglu::Args (operators/src/swiglu/args.rs:7-12)."""
 
     def __init__(self, gate_layout, gate_base, up_layout, up_base):
+        self._alive = (gate_base, up_base,)
         self.keep = (_lay(gate_layout), _lay(up_layout))
         self.c = _SwigluArgs(self.keep[0].c, _vp(gate_base), self.keep[1].c, _vp(up_base))
 
@@ -280,6 +286,7 @@ class RearrangeArgs(_ArgsBase):
     """rearrange::Args (operators/src/rearrange/args.rs:11-17)."""
 
     def __init__(self, dst_layout, dst_base, src_layout, src_base):
+        self._alive = (dst_base, src_base,)
         self.keep = (_lay(dst_layout), _lay(src_layout))
         self.c = _RearrangeArgs(self.keep[0].c, _vp(dst_base), self.keep[1].c, _vp(src_base))
 
@@ -292,6 +299,7 @@ class MatMulArgs(_ArgsBase):
     """mat_mul::Args (operators/src/mat_mul/args.rs:11-20): C = beta*C + alpha*A*B."""
 
     def __init__(self, c_layout, c_base, beta, a_layout, a_base, b_layout, b_base, alpha):
+        self._alive = (c_base, a_base, b_base,)
         self.keep = (_lay(c_layout), _lay(a_layout), _lay(b_layout))
         self.c = _MatMulArgs(self.keep[0].c, _vp(c_base), beta, self.keep[1].c, _vp(a_base), self.keep[2].c, _vp(b_base), alpha)
 
@@ -304,6 +312,7 @@ class AttentionArgs(_ArgsBase):
     """attention::Args (operators/src/attention/args.rs:10-24)."""
 
     def __init__(self, q_layout, q_base, k_layout, k_base, v_layout, v_base, o_layout, o_base, mask):
+        self._alive = (q_base, k_base, v_base, o_base,)
         self.keep = (_lay(q_layout), _lay(k_layout), _lay(v_layout), _lay(o_layout))
         self.c = _AttentionArgs(self.keep[0].c, _vp(q_base), self.keep[1].c, _vp(k_base), self.keep[2].c, _vp(v_base),
                                 self.keep[3].c, _vp(o_base), mask)
@@ -318,6 +327,7 @@ class AttentionKvCachedArgs(_ArgsBase):
 
     def __init__(self, q_layout, q_base, k_layout, k_base, v_layout, v_base, o_layout, o_base, k_cache_layout,
                  k_cache_base, v_cache_layout, v_cache_base, mask, pos):
+        self._alive = (q_base, k_base, v_base, o_base, k_cache_base, v_cache_base,)
         self.keep = tuple(_lay(x) for x in (q_layout, k_layout, v_layout, o_layout, k_cache_layout, v_cache_layout))
         k = self.keep
         self.c = _AttnCachedArgs(k[0].c, _vp(q_base), k[1].c, _vp(k_base), k[2].c, _vp(v_base), k[3].c, _vp(o_base),
@@ -356,6 +366,7 @@ class RandomSampleArgs(_ArgsBase):
     """random_sample::Args (operators/src/random_sample/args.rs:9-18)."""
 
     def __init__(self, kv_pair, kv_pair_base, logits, logits_base, indices, indices_base, config, seed):
+        self._alive = (kv_pair_base, logits_base, indices_base,)
         self.keep = (_lay(kv_pair), _lay(logits), _lay(indices), config)
         self.c = _RandomSampleArgs(self.keep[0].c, _vp(kv_pair_base), self.keep[1].c, _vp(logits_base), self.keep[2].c,
                                    _vp(indices_base), config.c, seed)
@@ -370,6 +381,7 @@ class AllReduceArgs(_ArgsBase):
     """all_reduce::Args { pair: rearrange::Args, op: ReduceOp } (operators/src/all_reduce/args.rs:9-12)."""
 
     def __init__(self, dst_layout, dst_base, src_layout, src_base, op=REDUCE_SUM):
+        self._alive = (dst_base, src_base,)
         self.keep = (_lay(dst_layout), _lay(src_layout))
         self.c = _AllReduceArgs(_RearrangeArgs(self.keep[0].c, _vp(dst_base), self.keep[1].c, _vp(src_base)), op)
 
@@ -432,6 +444,7 @@ class Operator:
         call repeated, as Workspace::new does in the crate (operators/src/common/workspace.rs:12-21)."""
         qa = queue_alloc or TorchQueueAlloc()
         stream = ctypes.c_void_p(qa.queue())
+        self._last_args = args  # the enqueued kernels read these buffers: keep them until the next launch
         ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
         rc = self._launch(self._h, args.byref(), ctypes.c_void_p(ws_ptr), ctypes.c_size_t(ws_len), stream)
         if rc == WORKSPACE_TOO_SMALL:

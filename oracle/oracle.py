@@ -173,3 +173,49 @@ def broadcast(bufs, root):
     ptrs = (ctypes.c_void_p * p)(*[b.ctypes.data for b in bufs])
     _chk(lib().orc_broadcast(_sz(p), _sz(bufs[0].nbytes), _sz(root), ptrs))
     return bufs
+
+
+def decoder_layer(x, pos, shards, cfg):
+    """The decoder-layer chain on the oracle operators (what a caller of the reference's common_cpu operators computes).
+
+    x [T, d] f16, pos [T] u32, shards = list of per-rank weight dicts (one entry = no tensor parallelism),
+    cfg = dict(d, nh, nkvh, dh, ffn, theta, eps).  Tensor-parallel ranks are emulated one after the other;
+    partial sums meet in all_reduce (f16 tree order of all_reduce/common_cpu.rs).  Rank 0 folds the residual with beta = 1.
+    Returns the layer output [T, d].
+    """
+    tp = len(shards)
+    T, d = x.shape
+    dh, nq, nkv, f = cfg["dh"], cfg["nh"] // tp, cfg["nkvh"] // tp, cfg["ffn"] // tp
+    xs = [x.copy() for _ in range(tp)]
+
+    def project(r, a, w_):
+        if r == 0:
+            out = xs[r]
+            mat_mul(out, 1.0, a, w_, 1.0)
+        else:
+            out = np.zeros((T, d), x.dtype)
+            mat_mul(out, 0.0, a, w_, 1.0)
+        return out
+
+    parts = []
+    for r, w in enumerate(shards):
+        h = rms_norm(np.empty_like(x), xs[r], w["w_norm1"], cfg["eps"])
+        qkv = mat_mul(np.zeros((T, (nq + 2 * nkv) * dh), x.dtype), 0.0, h, w["w_qkv"], 1.0)
+        heads = qkv.reshape(T, nq + 2 * nkv, dh)
+        rope(heads[:, : nq + nkv], pos, cfg["theta"])
+        att_out = np.zeros((T, nq * dh), x.dtype)
+        attention(heads[:, :nq].transpose(1, 0, 2), heads[:, nq:nq + nkv].transpose(1, 0, 2), heads[:, nq + nkv:].transpose(1, 0, 2),
+                  att_out.reshape(T, nq, dh).transpose(1, 0, 2), True)
+        parts.append(project(r, att_out, w["w_o"]))
+    if tp > 1:
+        all_reduce(parts)
+    xs = parts
+    parts = []
+    for r, w in enumerate(shards):
+        h = rms_norm(np.empty_like(x), xs[r], w["w_norm2"], cfg["eps"])
+        gu = mat_mul(np.zeros((T, 2 * f), x.dtype), 0.0, h, w["w_gu"], 1.0)
+        swiglu(gu[:, :f], gu[:, f:])
+        parts.append(project(r, gu[:, :f], w["w_down"]))
+    if tp > 1:
+        all_reduce(parts)
+    return parts[0]
