@@ -287,6 +287,17 @@ int ops_random_sample_launch_batched(const ops_random_sample *op, uint32_t dt, s
                                      const ops_sample_args *config, const float *seeds_dev,
                                      void *ws, size_t ws_len, void *stream);
 
+/* No counterpart in the reference.  ops_random_sample_launch for callers that cannot allocate device memory where
+ * they sample (a decode loop with the allocator locked down, a plugin that is given a stream but no allocator, a
+ * process with a fixed memory budget): it takes no workspace.  The scratch is a fixed 2 MiB array inside the
+ * library's device image, enough for one row of up to ops_random_sample_noalloc_max_logits() = 131072 logits; longer
+ * rows are refused with OPS_SHAPE_NOT_SUPPORT.  Nothing is allocated or freed, here or in any routine it calls.
+ * The first call on a device looks up the array's device address; make that first call before any stream capture.
+ * All calls on a device share the array: calls that overlap on the GPU race, so keep them on one stream or order
+ * them yourself.  Results are identical to ops_random_sample_launch. */
+size_t ops_random_sample_noalloc_max_logits(void);
+int ops_random_sample_launch_noalloc(const ops_random_sample *op, const ops_random_sample_args *args, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * all_reduce — all_reduce::Args {pair: rearrange::Args, op} (operators/src/all_reduce/args.rs:9-12);
  * replaces all_reduce::common_cpu::Operator over InprocNode (operators/src/all_reduce/common_cpu.rs:15-104)

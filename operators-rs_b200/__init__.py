@@ -534,6 +534,20 @@ class RandomSample(Operator):
         _check(lib().ops_random_sample_build_indices(ctypes.c_size_t(n), ctypes.c_void_p(out.ctypes.data)), False)
         return out
 
+    @staticmethod
+    def noalloc_max_logits():
+        f = lib().ops_random_sample_noalloc_max_logits
+        f.restype = ctypes.c_size_t
+        return f()
+
+    def launch_noalloc(self, args, queue_alloc=None):
+        """ops_random_sample_launch_noalloc: same result as launch(), no workspace and no allocation anywhere —
+        for callers that cannot allocate where they sample.  Rows longer than noalloc_max_logits() are refused;
+        overlapping calls on one device share the built-in scratch array and must be serialised by the caller."""
+        qa = queue_alloc or TorchQueueAlloc()
+        self._last_args = args
+        _check(lib().ops_random_sample_launch_noalloc(self._h, args.byref(), ctypes.c_void_p(qa.queue())), True)
+
     def launch_batched(self, logits, kv_out, config, seeds=None, workspace=None, queue_alloc=None):
         """Extension: all rows of logits [rows, n] in one launch; kv_out [rows, 2] int32/uint32 view."""
         qa = queue_alloc or TorchQueueAlloc(device=logits.device)
@@ -611,7 +625,8 @@ EXPORTS = [
       for fn in ("create", "scheme", "launch", "destroy")],
     "ops_rope_build_pos", "ops_rearrange_plan", "ops_mat_mul_status", "ops_attention_set_algo",
     "ops_attention_kv_cached_set_algo", "ops_sample_args_new", "ops_random_sample_build_indices",
-    "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched", "ops_comm_unique_id",
+    "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
+    "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
     "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo",
 ]

@@ -21,6 +21,8 @@
 //             exp is evaluated in double and rounded to f32 (= the correctly rounded f32 exp).
 //
 // HBM-bound on paper (rows * n * sizeof(T) bytes read); argmax splits a row over several CTAs.
+#include <mutex>
+
 #include "common.h"
 #include "device_utils.cuh"
 
@@ -551,7 +553,7 @@ OPS_API size_t ops_random_sample_batched_workspace(uint32_t dt, size_t rows, siz
 // covers both modes when it fits, else the smaller one, else 0.
 OPS_API int ops_random_sample_scheme(ops_random_sample *op, const ops_random_sample_args *args, size_t max_ws, size_t *ws_out) {
   (void)op;
-  SampleMeta m;
+  SampleMeta m{};
   OPS_TRY(sample_meta(args, &m));
   if (ws_out) {
     *ws_out = 0;
@@ -564,7 +566,7 @@ OPS_API int ops_random_sample_scheme(ops_random_sample *op, const ops_random_sam
 }
 
 OPS_API int ops_random_sample_launch(const ops_random_sample *op, const ops_random_sample_args *a, void *ws, size_t ws_len, void *stream) {
-  SampleMeta m;
+  SampleMeta m{};
   OPS_TRY(sample_meta(a, &m));
   const isz st = a->logits.strides[0];
   if (dyn(st) || st != (isz)dt_size(m.dt)) return fail(OPS_STRIDES_NOT_SUPPORT, "random_sample: logits must be contiguous");
@@ -582,4 +584,68 @@ OPS_API int ops_random_sample_launch_batched(const ops_random_sample *op, uint32
 OPS_API int ops_random_sample_build_indices(size_t n, uint32_t *host_out) {
   for (size_t i = 0; i < n; ++i) host_out[i] = (uint32_t)i;
   return OPS_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers cannot allocate device memory at the point where they sample: code that runs inside a
+// latency-critical decode loop with the allocator locked down, plugins that are handed a stream but
+// no allocator, processes whose memory budget is fixed at start-up.  For them the scratch that
+// ops_random_sample_launch takes from the caller's workspace lives here instead, in one fixed array
+// inside the library's device image.  Every GPU that loads the library carries the array until the
+// process exits.
+//
+// The array is shared by every call on a device and keeps whatever the previous call left in it.  The
+// argmax path clears the few bytes it needs to start from zero on the stream before its kernel; the
+// sampling path overwrites everything it later reads.  Two calls that overlap on the GPU (different
+// streams, or graphs replayed concurrently) would race on the array: serialise them.
+// ------------------------------------------------------------------------------------------------
+namespace ops {
+
+constexpr usz NOALLOC_MAX_LOGITS = 131072;                       // one row of up to 128 Ki logits
+constexpr usz NOALLOC_SCRATCH_BYTES = NOALLOC_MAX_LOGITS * 16;   // 2 MiB: what the sampling kernel needs for such a row
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static void *g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of the array on each device, resolved on first use
+static std::mutex g_noalloc_mutex;
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use:
+// the device address has to be asked for, once per device, with that device current.
+static int noalloc_scratch(int device, void **out) {
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: device %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[device]) {
+    cudaError_t e = cudaSetDevice(device);
+    void *p = nullptr;
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      return fail(OPS_EXECUTION_FAILED, "random_sample: cannot resolve the built-in scratch array on device %d: %s", device, cudaGetErrorString(e));
+    }
+    g_noalloc_ptr[device] = p;
+  }
+  *out = g_noalloc_ptr[device];
+  return OPS_OK;
+}
+
+}  // namespace ops
+
+OPS_API size_t ops_random_sample_noalloc_max_logits(void) { return NOALLOC_MAX_LOGITS; }
+
+OPS_API int ops_random_sample_launch_noalloc(const ops_random_sample *op, const ops_random_sample_args *a, void *stream) {
+  SampleMeta m{};
+  OPS_TRY(sample_meta(a, &m));
+  const isz st = a->logits.strides[0];
+  if (dyn(st) || st != (isz)dt_size(m.dt)) return fail(OPS_STRIDES_NOT_SUPPORT, "random_sample: logits must be contiguous");
+  if (dyn(m.n)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: n must be static at launch");
+  if (m.n > NOALLOC_MAX_LOGITS)
+    return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: %zu logits exceed the %zu the built-in scratch array is sized for; use ops_random_sample_launch with a workspace",
+                m.n, NOALLOC_MAX_LOGITS);
+  void *scratch = nullptr;
+  OPS_TRY(noalloc_scratch(op->base.device, &scratch));
+  return launch_rows(op->base, m.dt, 1, m.n, a->logits_base, 0, a->kv_pair_base, a->config, nullptr, a->seed, scratch, NOALLOC_SCRATCH_BYTES,
+                     (cudaStream_t)stream);
 }
