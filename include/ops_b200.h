@@ -208,7 +208,8 @@ int ops_mat_mul_status(const ops_mat_mul *op);
  * o = softmax_mask(q k^T / sqrt(dh)) v with grouped-query heads; q [nh,seq,dh], k,v [nkvh,att,dh].
  * As in the crate, q may be overwritten when its (nh, seq) dims are mergeable.
  * `algo`: 0 = the crate's own chain (rearrange, mat_mul, fused_softmax, mat_mul, rearrange) with
- * the score matrix in workspace; 1 = one fused flash-attention kernel (no score matrix).
+ * the score matrix in workspace, every intermediate rounded to f16 where the crate rounds it;
+ * 1 = one fused flash-attention kernel (no score matrix, no workspace, q left untouched).
  * ------------------------------------------------------------------------------------------- */
 typedef struct ops_attention ops_attention;
 typedef struct {
@@ -220,7 +221,8 @@ typedef struct {
 } ops_attention_args;
 enum { OPS_ATTENTION_CHAIN = 0, OPS_ATTENTION_FUSED = 1 };
 int ops_attention_create(int device, ops_attention **out);
-int ops_attention_set_algo(ops_attention *op, int algo);
+int ops_attention_set_algo(ops_attention *op, int algo); /* default OPS_ATTENTION_FUSED (falls back to the chain when a layout rules it out) */
+int ops_attention_status(const ops_attention *op);      /* 0, or the code of a bounded wait that ran out; synchronises; no counterpart in the crate */
 int ops_attention_scheme(ops_attention *op, const ops_attention_args *args, size_t max_ws, size_t *ws_out);
 int ops_attention_launch(const ops_attention *op, const ops_attention_args *args, void *ws, size_t ws_len, void *stream);
 void ops_attention_destroy(ops_attention *op);

@@ -4,6 +4,8 @@
 // operators/src/attention/args.rs:60-90) and attention_kv_cached::Operator
 // (operators/src/attention_kv_cached/operator.rs:76-183, checks attention_kv_cached/args.rs:72-115).
 //
+// Algorithm 1 (OPS_ATTENTION_FUSED, the default) runs the one-kernel flash attention of attention_fused.cu whenever the
+// layouts allow it (f16, dh 64 or 128, 16-byte aligned rows) and falls back to algorithm 0 otherwise.
 // Algorithm 0 (OPS_ATTENTION_CHAIN) is the crate's own composition, step for step, on this library's
 // kernels: [copy q to a contiguous buffer unless its (nh, seq) dims merge] -> att = alpha q k^T
 // (batched over kv heads, the q rows of one group stacked) -> causal softmax in place -> q = att v ->
@@ -17,6 +19,8 @@ struct ops_attention {
   ops::OpBase base;
   ops_mat_mul *mat_mul;
   int algo;
+  int *status_dev;      // written by the fused kernel when a bounded wait runs out
+  bool attr_set[2];
 };
 
 namespace ops {
@@ -125,6 +129,11 @@ int attention_enqueue(const ops_attention *op, const ops_attention_args *a, void
   if (m.nkvh == 0 || m.nh % m.nkvh != 0) return fail(OPS_SHAPE_MISMATCH, "attention: nh must be a multiple of nkvh");
   if (a->mask == OPS_MASK_CAUSAL && m.att < m.seq) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: causal mask needs att >= seq");
   if (m.nh == 0 || m.seq == 0 || m.dh == 0 || m.att == 0) return OPS_OK;
+  if (op->algo == OPS_ATTENTION_FUSED && a->q_base && a->k_base && a->v_base && a->o_base &&
+      attention_fused_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh)) {
+    ops_attention *mop = const_cast<ops_attention *>(op);
+    return attention_fused_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->status_dev, mop->attr_set, s);
+  }
   return attention_chain(op, a, m, ws, ws_len, s);
 }
 
@@ -134,10 +143,18 @@ OPS_API int ops_attention_create(int device, ops_attention **out) {
   if (!out) return fail(OPS_ARGS_NOT_SUPPORT, "null out pointer");
   ops_attention *h = new ops_attention();
   h->mat_mul = nullptr;
-  h->algo = OPS_ATTENTION_CHAIN;
+  h->algo = OPS_ATTENTION_FUSED;
+  h->status_dev = nullptr;
+  h->attr_set[0] = h->attr_set[1] = false;
   int rc = init_base(&h->base, device);
   if (rc == OPS_OK) rc = ops_mat_mul_create(device, &h->mat_mul);
+  if (rc == OPS_OK) {
+    cudaSetDevice(device);
+    if (cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess || cudaMemset(h->status_dev, 0, sizeof(int)) != cudaSuccess)
+      rc = fail(OPS_EXECUTION_FAILED, "attention: cannot allocate the status word");
+  }
   if (rc != OPS_OK) {
+    if (h->mat_mul) ops_mat_mul_destroy(h->mat_mul);
     delete h;
     return rc;
   }
@@ -148,13 +165,24 @@ OPS_API int ops_attention_create(int device, ops_attention **out) {
 OPS_API void ops_attention_destroy(ops_attention *op) {
   if (!op) return;
   if (op->mat_mul) ops_mat_mul_destroy(op->mat_mul);
+  if (op->status_dev) cudaFree(op->status_dev);
   delete op;
 }
 
 OPS_API int ops_attention_set_algo(ops_attention *op, int algo) {
-  if (algo != OPS_ATTENTION_CHAIN) return fail(OPS_ARGS_NOT_SUPPORT, "attention: unknown algorithm %d", algo);
+  if (algo != OPS_ATTENTION_CHAIN && algo != OPS_ATTENTION_FUSED) return fail(OPS_ARGS_NOT_SUPPORT, "attention: unknown algorithm %d", algo);
   op->algo = algo;
   return OPS_OK;
+}
+
+// 0, or which bounded wait ran out: 11/12 producer, 21-26 issuer, 31-33 softmax of the fused kernel, 1-4 of the
+// tensor-core mat_mul used by the chain.  Synchronises the device.
+OPS_API int ops_attention_status(const ops_attention *op) {
+  int v = -1;
+  cudaSetDevice(op->base.device);
+  if (cudaMemcpy(&v, op->status_dev, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v == 0) v = ops_mat_mul_status(op->mat_mul);
+  return v;
 }
 
 // attention::Operator::scheme (operators/src/attention/operator.rs:45-134): with static nh, seq, att,

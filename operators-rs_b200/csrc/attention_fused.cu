@@ -1,0 +1,419 @@
+// attention_fused.cu — one-kernel causal attention on tcgen05 tensor cores (no score matrix in HBM).
+//
+// The fast path behind attention::Args (operators/src/attention/args.rs:10-24).  The crate composes
+// attention from mat_mul, fused_softmax and rearrange with the [nh, seq, att] score matrix in workspace
+// (operators/src/attention/operator.rs:199-275); this kernel computes the same function with online
+// softmax, so HBM sees q, k, v and o once: E*(2*nh*seq*dh + 2*nkvh*att*dh) bytes for
+// 4*nh*dh*sum_k(att-seq+k+1) useful flops — tensor-bound.
+//
+// One CTA per (head, 128-row q block), 6 warps:
+//   warp 0   TMA producer: Q once, then K and V blocks of 128 keys through two-stage rings;
+//   warp 1   tcgen05.mma issuer: S_j = Q K_j^T into tensor memory (two S buffers), then
+//            PV_j = P_j V_j into a second pair of tensor-memory buffers — never accumulating across
+//            blocks, so no rescaling ever touches tensor memory;
+//   warps 2-5  softmax: thread = one q row.  tcgen05.ld S_j, running max / sum in the exp2 domain,
+//            P_j -> f16 into shared memory in the swizzled K-major layout the MMA reads, then
+//            O = O * alpha + PV_{j-1} in REGISTERS (dh f32 per thread), final 1/l and store.
+// The issue order QK_j, PV_{j-1}, QK_{j+1}, ... lets the tensor pipe work on the next block while
+// the softmax warps are busy with the current one.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "common.h"
+#include "device_utils.cuh"
+#include "internal.h"
+#include "sm100_ptx.cuh"
+
+namespace ops {
+
+using namespace sm100;
+
+constexpr int FA_BM = 128;       // q rows per CTA
+constexpr int FA_BN = 128;       // keys per block
+constexpr int FA_THREADS = 192;
+
+struct FusedAttnArgs {
+  __half *o;
+  long long o_sh, o_ss;  // element strides of o: head, row (dh contiguous)
+  int nh, group, seq, att;
+  int causal;
+  int q_blocks;
+  float scale_log2;      // alpha * log2(e)
+  int vec_store;
+  int *status;
+};
+
+template <int DH> struct FaCfg {
+  static constexpr int HALVES = DH / 64;                 // 64-element (128-byte) column groups of a dh row
+  static constexpr int Q_BYTES = FA_BM * DH * 2;
+  static constexpr int K_BYTES = FA_BN * DH * 2;
+  static constexpr int V_BYTES = FA_BN * DH * 2;
+  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * K_BYTES;      // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * V_BYTES;      // 2 buffers
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int NUM_BARS = 1 + 8 + 12;            // q_full; k/v full+empty x2; s/p/pv full+empty x2
+  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;                  // S0 S1 (128 each) | PV0 PV1 (128 each, DH used)
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                           const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FusedAttnArgs g) {
+  typedef FaCfg<DH> Cfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar0 = base + Cfg::OFF_BAR;
+  // barrier indices
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
+  auto s_empty = [&](int b) { return bar0 + 8u * (11 + b); };
+  auto p_full = [&](int b) { return bar0 + 8u * (13 + b); };
+  auto p_empty = [&](int b) { return bar0 + 8u * (15 + b); };
+  auto pv_full = [&](int b) { return bar0 + 8u * (17 + b); };
+  auto pv_empty = [&](int b) { return bar0 + 8u * (19 + b); };
+  const uint32_t tmem_slot = bar0 + 8u * Cfg::NUM_BARS;
+  uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(base_ptr + Cfg::OFF_BAR + 8 * Cfg::NUM_BARS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavy (late, long) q blocks first: they set the tail of the launch
+  const int qb = g.q_blocks - 1 - (int)(blockIdx.x % g.q_blocks);
+  const int head = (int)(blockIdx.x / g.q_blocks);
+  const int kv_head = head / g.group;
+  const int q0 = qb * FA_BM;
+  const int off = g.att - g.seq;  // causal row r sees keys <= off + r
+  int k_end = g.att;              // exclusive bound of keys this q block can see
+  if (g.causal) k_end = min(g.att, off + q0 + FA_BM);
+  const int nblk = (k_end + FA_BN - 1) / FA_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(s_empty(s), 4);
+      mbar_init(p_full(s), 4);
+      mbar_init(p_empty(s), 1);
+      mbar_init(pv_full(s), 1);
+      mbar_init(pv_empty(s), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < Cfg::HALVES; ++h) tma_load_3d(base + Cfg::OFF_Q + h * (FA_BM * 128), &tmap_q, q_full, h * 64, q0, head);
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!(ok = mbar_wait(k_empty(s), ph ^ 1u, g.status, 11))) break;
+        mbar_arrive_expect_tx(k_full(s), Cfg::K_BYTES);
+#pragma unroll
+        for (int h = 0; h < Cfg::HALVES; ++h)
+          tma_load_3d(base + Cfg::OFF_K + s * Cfg::K_BYTES + h * (FA_BN * 128), &tmap_k, k_full(s), h * 64, j * FA_BN, kv_head);
+        if (!(ok = mbar_wait(v_empty(s), ph ^ 1u, g.status, 12))) break;
+        mbar_arrive_expect_tx(v_full(s), Cfg::V_BYTES);
+#pragma unroll
+        for (int kg = 0; kg < FA_BN / 64; ++kg)
+#pragma unroll
+          for (int c = 0; c < Cfg::HALVES; ++c)
+            tma_load_3d(base + Cfg::OFF_V + s * Cfg::V_BYTES + (kg * Cfg::HALVES + c) * 8192, &tmap_v, v_full(s), c * 64, j * FA_BN + kg * 64,
+                        kv_head);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_f16(FA_BM, FA_BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc_f16(FA_BM, DH, 0, 1);
+      bool ok = mbar_wait(q_full, 0, g.status, 21);
+      auto issue_pv = [&](int i) -> bool {
+        const int b = i & 1;
+        const uint32_t ph = (uint32_t)((i >> 1) & 1);
+        if (!mbar_wait(v_full(b), ph, g.status, 22)) return false;
+        if (!mbar_wait(p_full(b), ph, g.status, 23)) return false;
+        if (!mbar_wait(pv_empty(b), ph ^ 1u, g.status, 24)) return false;
+        tc_fence_after();
+        const uint32_t pa = base + Cfg::OFF_P + b * Cfg::P_BYTES, va = base + Cfg::OFF_V + b * Cfg::V_BYTES;
+        const uint32_t d = tmem_base + 256u + (uint32_t)(b * 128);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks) {
+          const uint64_t da = make_smem_desc_sw128(pa + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(va + (ks >> 2) * (Cfg::HALVES * 8192) + (ks & 3) * 2048, 8192, 1024);
+          umma_f16_ss(d, da, db, idesc_pv, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(v_empty(b));
+        umma_commit(p_empty(b));
+        umma_commit(pv_full(b));
+        return true;
+      };
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!(ok = mbar_wait(k_full(b), ph, g.status, 25))) break;
+        if (!(ok = mbar_wait(s_empty(b), ph ^ 1u, g.status, 26))) break;
+        tc_fence_after();
+        const uint32_t qa = base + Cfg::OFF_Q, ka = base + Cfg::OFF_K + b * Cfg::K_BYTES;
+        const uint32_t d = tmem_base + (uint32_t)(b * 128);
+#pragma unroll
+        for (int ks = 0; ks < DH / 16; ++ks) {
+          const uint64_t da = make_smem_desc_sw128(qa + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(ka + (ks >> 2) * (FA_BN * 128) + (ks & 3) * 32, 16, 1024);
+          umma_f16_ss(d, da, db, idesc_qk, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(k_empty(b));
+        umma_commit(s_full(b));
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok && nblk > 0) issue_pv(nblk - 1);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output (warps 2..5)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int q_row = q0 + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int limit = g.causal ? min(g.att - 1, off + q_row) : g.att - 1;  // last key this row may see
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+    bool ok = true;
+
+    auto accumulate_pv = [&](int i, float a) -> bool {
+      const int b = i & 1;
+      if (!mbar_wait(pv_full(b), (uint32_t)((i >> 1) & 1), g.status, 31)) return false;
+      tc_fence_after();
+      const uint32_t t = tmem_base + lane_addr + 256u + (uint32_t)(b * 128);
+#pragma unroll
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t + (uint32_t)c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c + e] = fmaf(o[c + e], a, __uint_as_float(v[e]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pv_empty(b));
+      return true;
+    };
+
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      const int kv0 = j * FA_BN;
+      if (!(ok = mbar_wait(s_full(b), ph, g.status, 32))) break;
+      tc_fence_after();
+      const uint32_t t = tmem_base + lane_addr + (uint32_t)(b * 128);
+      const bool need_mask = kv0 + FA_BN - 1 > limit;
+      // pass A: row maximum of this block
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < FA_BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t + (uint32_t)c, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (kv0 + c + e <= limit) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      const float m_raw = fmaxf(m, mx * g.scale_log2);
+      const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // a row with nothing visible yet: keep the arithmetic finite
+      const float alpha = ex2_approx(m - m_new);             // 0 on the first block (m = -inf)
+      // pass B: probabilities -> shared memory (K-major, 128-byte swizzle), row sum
+      if (!(ok = mbar_wait(p_empty(b), ph ^ 1u, g.status, 33))) break;
+      uint8_t *p_row = base_ptr + Cfg::OFF_P + b * Cfg::P_BYTES + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < FA_BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t + (uint32_t)c, v);
+        tmem_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(v[e]), g.scale_log2, -m_new));
+          float p1 = ex2_approx(fmaf(__uint_as_float(v[e + 1]), g.scale_log2, -m_new));
+          if (need_mask) {
+            if (kv0 + c + e > limit) p0 = 0.f;
+            if (kv0 + c + e + 1 > limit) p1 = 0.f;
+          }
+          rowsum += p0 + p1;
+          __half2 h = __floats2half2_rn(p0, p1);
+          packed[e >> 1] = *reinterpret_cast<uint32_t *>(&h);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int unit = (c >> 3) + u;  // 16-byte unit index along the 128 keys
+          uint8_t *dst = p_row + (unit >> 3) * (FA_BM * 128) + (((unit & 7) ^ (row_in_tile & 7)) << 4);
+          *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();  // the MMA reads these shared-memory writes through the async proxy
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty(b));
+        mbar_arrive(p_full(b));
+      }
+      l = fmaf(l, alpha, rowsum);
+      if (j > 0) ok = accumulate_pv(j - 1, alpha_prev);
+      alpha_prev = alpha;
+      m = m_new;
+    }
+    if (ok && nblk > 0) ok = accumulate_pv(nblk - 1, alpha_prev);
+    if (ok && q_row < g.seq) {
+      const float inv = __frcp_rn(l);
+      __half *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss;
+      if (g.vec_store) {
+#pragma unroll
+        for (int c = 0; c < DH; c += 8) {
+          Pack8 out;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(o[c + e] * inv);
+          st_global_16(orow + c, out.u);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < DH; ++c) orow[c] = __float2half_rn(o[c] * inv);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*reinterpret_cast<volatile int *>(g.status) != 0) __nanosleep(1000000);
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (shared with mat_mul.cu's approach)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn fa_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// [heads, rows, dh] f16 tensor with dh contiguous as a rank-3 map (dh, rows, heads)
+static bool encode_hrd(CUtensorMap *map, const void *ptr, usz dh, usz rows, usz heads, isz row_stride_b, isz head_stride_b, uint32_t box_rows) {
+  EncodeTiledFn fn = fa_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {dh, rows, heads};
+  cuuint64_t rs = rows > 1 ? (cuuint64_t)row_stride_b : (cuuint64_t)(dh * 2);
+  cuuint64_t hs = heads > 1 ? (cuuint64_t)head_stride_b : rs * rows;
+  cuuint64_t strides[2] = {rs, hs};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool hrd_ok(const void *p, const isz *st, usz heads, usz rows) {
+  if (!aligned(p, 16) || st[2] != 2) return false;
+  if (rows > 1 && (st[1] <= 0 || st[1] % 16)) return false;
+  if (heads > 1 && (st[0] <= 0 || st[0] % 16)) return false;
+  return true;
+}
+
+bool attention_fused_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh) {
+  if (a->q_layout.dt != OPS_DT_F16 || (dh != 64 && dh != 128)) return false;
+  if (nh > 65535 || seq > 0x3fffffffu || att > 0x3fffffffu) return false;
+  const isz *sv = a->v_layout.strides, *so = a->o_layout.strides;
+  if (dyn(sv[0]) || dyn(sv[1]) || dyn(sv[2]) || dyn(so[0]) || dyn(so[1]) || dyn(so[2])) return false;
+  if (!hrd_ok(a->q_base, a->q_layout.strides, nh, seq) || !hrd_ok(a->k_base, a->k_layout.strides, nkvh, att) ||
+      !hrd_ok(a->v_base, sv, nkvh, att))
+    return false;
+  if (so[2] != 2 || so[0] % 2 || so[1] % 2) return false;
+  return fa_encode_fn() != nullptr;
+}
+
+template <int DH>
+static int launch_fused(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, int *status, bool *attr_set,
+                        cudaStream_t s) {
+  typedef FaCfg<DH> Cfg;
+  CUtensorMap tq, tk, tv;
+  const isz *sq = a->q_layout.strides, *sk = a->k_layout.strides, *sv = a->v_layout.strides, *so = a->o_layout.strides;
+  if (!encode_hrd(&tq, a->q_base, DH, seq, nh, sq[1], sq[0], FA_BM) || !encode_hrd(&tk, a->k_base, DH, att, nkvh, sk[1], sk[0], FA_BN) ||
+      !encode_hrd(&tv, a->v_base, DH, att, nkvh, sv[1], sv[0], 64))
+    return fail(OPS_EXECUTION_FAILED, "attention: cuTensorMapEncodeTiled failed");
+  FusedAttnArgs g;
+  g.o = (__half *)a->o_base;
+  g.o_sh = so[0] / 2;
+  g.o_ss = so[1] / 2;
+  g.nh = (int)nh;
+  g.group = (int)(nh / nkvh);
+  g.seq = (int)seq;
+  g.att = (int)att;
+  g.causal = a->mask == OPS_MASK_CAUSAL;
+  g.q_blocks = (int)((seq + FA_BM - 1) / FA_BM);
+  // the CPU path rounds alpha = 1/sqrt(dh) to f16 before the product (mat_mul/common_cpu/mod.rs:101)
+  const float alpha = __half2float(__float2half_rn(1.f / sqrtf((float)DH)));
+  g.scale_log2 = alpha * 1.4426950408889634f;
+  g.vec_store = aligned(a->o_base, 16) && so[0] % 16 == 0 && so[1] % 16 == 0;
+  g.status = status;
+  cudaSetDevice(base.device);
+  if (!*attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_fused_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    *attr_set = true;
+  }
+  const unsigned grid = (unsigned)(nh * (usz)g.q_blocks);
+  attention_fused_kernel<DH><<<grid, FA_THREADS, Cfg::SMEM_BYTES, s>>>(tq, tk, tv, g);
+  return check_launch("attention(fused)");
+}
+
+int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
+                            bool *attr_set, cudaStream_t s) {
+  if (dh == 128) return launch_fused<128>(base, a, nh, nkvh, seq, att, status, &attr_set[0], s);
+  return launch_fused<64>(base, a, nh, nkvh, seq, att, status, &attr_set[1], s);
+}
+
+}  // namespace ops

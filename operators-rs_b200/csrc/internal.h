@@ -10,5 +10,8 @@ namespace ops {
 int rearrange_enqueue(const OpBase &base, const ops_rearrange_args *args, cudaStream_t s);
 int fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args *args, cudaStream_t s);
 int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s);
+bool attention_fused_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh);
+int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
+                            bool *attr_set, cudaStream_t s);
 
 }  // namespace ops
