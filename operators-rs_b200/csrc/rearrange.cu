@@ -7,7 +7,7 @@
 //
 // HBM-bound: 2 * bytes moved.  A unit is cut into the widest accesses (16/8/4/2/1 bytes) that the
 // unit length, both base addresses and every stride allow; each thread moves four such pieces per
-// loop trip (all loads issued before the stores), grid-stride over a grid sized to the SM count.
+// CTA trip (all loads issued before the stores); index arithmetic in 32 bits with shifts wherever the sizes allow.
 #include <algorithm>
 #include <vector>
 
@@ -23,6 +23,7 @@ struct RearrangeParams {
   const char *src;
   long long total_vec;      // count * vec_per_unit
   long long vec_per_unit;   // unit / VEC
+  int vec_shift;            // log2(vec_per_unit) when that is a power of two, else -1
   int ndim;
   long long idx[REARRANGE_MAX_DIMS];  // units per step of dim i
   long long ds[REARRANGE_MAX_DIMS];
@@ -36,45 +37,46 @@ template <> struct VecType<4> { typedef uint32_t type; };
 template <> struct VecType<2> { typedef uint16_t type; };
 template <> struct VecType<1> { typedef uint8_t type; };
 
-__device__ __forceinline__ void locate(const RearrangeParams &p, long long v, long long &d, long long &s, int vec) {
-  long long u, o;
-  if (p.vec_per_unit == 1) {
-    u = v;
-    o = 0;
+// Vector index -> byte offsets in dst and src.  Idx = uint32_t whenever every count fits (the usual case: 32-bit
+// division is an order of magnitude cheaper than 64-bit), long long otherwise.
+template <class Idx>
+__device__ __forceinline__ void locate(const RearrangeParams &p, Idx v, long long &d, long long &s, int vec) {
+  Idx u, o;
+  if (p.vec_shift >= 0) {  // pieces per unit is a power of two
+    u = v >> p.vec_shift;
+    o = v & (Idx)((1ll << p.vec_shift) - 1);
   } else {
-    u = v / p.vec_per_unit;
-    o = v - u * p.vec_per_unit;
+    u = v / (Idx)p.vec_per_unit;
+    o = v - u * (Idx)p.vec_per_unit;
   }
-  d = o * vec;
-  s = o * vec;
+  d = (long long)o * vec;
+  s = d;
   for (int i = 0; i < p.ndim; ++i) {
-    const long long k = u / p.idx[i];
-    u -= k * p.idx[i];
-    d += k * p.ds[i];
-    s += k * p.ss[i];
+    const Idx k = u / (Idx)p.idx[i];
+    u -= k * (Idx)p.idx[i];
+    d += (long long)k * p.ds[i];
+    s += (long long)k * p.ss[i];
   }
 }
 
-template <int VEC>
+// One CTA moves 4 * blockDim.x consecutive pieces: all four loads of a thread are issued before its stores.
+template <int VEC, class Idx>
 __global__ void __launch_bounds__(256) rearrange_kernel(const __grid_constant__ RearrangeParams p) {
   typedef typename VecType<VEC>::type V;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  for (; v + 3 * stride < p.total_vec; v += 4 * stride) {
-    long long d[4], s[4];
-    V val[4];
+  const long long base = (long long)blockIdx.x * (4 * 256) + threadIdx.x;
+  long long d[4], s[4];
+  V val[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) locate(p, v + i * stride, d[i], s[i], VEC);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) val[i] = *reinterpret_cast<const V *>(p.src + s[i]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) *reinterpret_cast<V *>(p.dst + d[i]) = val[i];
+  for (int i = 0; i < 4; ++i) {
+    const long long v = base + i * 256;
+    if (v < p.total_vec) {
+      locate<Idx>(p, (Idx)v, d[i], s[i], VEC);
+      val[i] = *reinterpret_cast<const V *>(p.src + s[i]);
+    }
   }
-  for (; v < p.total_vec; v += stride) {
-    long long d, s;
-    locate(p, v, d, s, VEC);
-    *reinterpret_cast<V *>(p.dst + d) = *reinterpret_cast<const V *>(p.src + s);
-  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (base + i * 256 < p.total_vec) *reinterpret_cast<V *>(p.dst + d[i]) = val[i];
 }
 
 struct Dim {
@@ -172,18 +174,29 @@ int rearrange_enqueue(const OpBase &base, const ops_rearrange_args *a, cudaStrea
   p.vec_per_unit = (long long)(unit / vec);
   p.total_vec = (long long)count * p.vec_per_unit;
 
-  cudaSetDevice(base.device);
-  const long long per_block = 256 * 4;
-  long long blocks = (p.total_vec + per_block - 1) / per_block;
-  const long long cap = (long long)base.sm_count * 8;
-  const unsigned grid = (unsigned)std::max<long long>(1, std::min(blocks, cap));
-  switch (vec) {
-    case 16: rearrange_kernel<16><<<grid, 256, 0, s>>>(p); break;
-    case 8: rearrange_kernel<8><<<grid, 256, 0, s>>>(p); break;
-    case 4: rearrange_kernel<4><<<grid, 256, 0, s>>>(p); break;
-    case 2: rearrange_kernel<2><<<grid, 256, 0, s>>>(p); break;
-    default: rearrange_kernel<1><<<grid, 256, 0, s>>>(p); break;
+  p.vec_shift = -1;
+  if ((p.vec_per_unit & (p.vec_per_unit - 1)) == 0) {
+    p.vec_shift = 0;
+    while ((1ll << p.vec_shift) < p.vec_per_unit) ++p.vec_shift;
   }
+  cudaSetDevice(base.device);
+  const long long blocks = (p.total_vec + 1023) / 1024;
+  if (blocks > 0x7fffffffll) return fail(OPS_SHAPE_NOT_SUPPORT, "rearrange: tensor too large");
+  const unsigned grid = (unsigned)blocks;
+  const bool small = p.total_vec < 0x7fffffffll;  // every index (vector, unit, per-dim count) fits 32 bits
+#define REARRANGE_LAUNCH(VEC)                                              \
+  do {                                                                     \
+    if (small) rearrange_kernel<VEC, unsigned int><<<grid, 256, 0, s>>>(p); \
+    else rearrange_kernel<VEC, long long><<<grid, 256, 0, s>>>(p);          \
+  } while (0)
+  switch (vec) {
+    case 16: REARRANGE_LAUNCH(16); break;
+    case 8: REARRANGE_LAUNCH(8); break;
+    case 4: REARRANGE_LAUNCH(4); break;
+    case 2: REARRANGE_LAUNCH(2); break;
+    default: REARRANGE_LAUNCH(1); break;
+  }
+#undef REARRANGE_LAUNCH
   return check_launch("rearrange");
 }
 

@@ -3,8 +3,8 @@
 // Replaces swiglu::common_cpu::Operator (operators/src/swiglu/common_cpu/mod.rs:27-81, arithmetic
 // :109-137); argument checks follow Args::meta (operators/src/swiglu/args.rs:27-50).
 //
-// HBM-bound: 3*n*d*2 bytes.  Each thread handles 8 halves per 128-bit access, two independent
-// accesses (gate, up) in flight per iteration, persistent grid-stride loop sized to the SM count.
+// HBM-bound: 3*n*d*2 bytes.  Each thread handles 8 halves per 128-bit access (one gate and one up load in
+// flight); one CTA per (row, 2048-column chunk), so no index division and enough CTAs to cover HBM latency.
 #include "common.h"
 #include "device_utils.cuh"
 
@@ -16,21 +16,21 @@ __device__ __forceinline__ float swiglu_f32(float a, float b) {
   return __fmul_rn(__fmul_rn(a, sig), b);
 }
 
-// Fast path: f16, unit inner strides, d % 8 == 0, 16-byte aligned rows.
+// Fast path: f16, unit inner strides, d % 8 == 0, 16-byte aligned rows.  blockIdx.x = row, blockIdx.y = 2048-column
+// chunk (blockIdx.x = row * chunks + chunk): no per-element index division, one 128-bit gate load and one up load in flight per thread, thousands of CTAs.
 __global__ void __launch_bounds__(256) swiglu_vec_kernel(__half *__restrict__ gate, long long sgn, const __half *__restrict__ up,
-                                                         long long sun, int vec_per_row, long long total_vec) {
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vec; v += (long long)gridDim.x * blockDim.x) {
-    const long long row = v / vec_per_row;
-    const int col = (int)(v - row * vec_per_row) * 8;
-    __half *g = byte_off(gate, row * sgn) + col;
-    const __half *u = byte_off(up, row * sun) + col;
-    Pack8 gv, uv, out;
-    gv.u = ld_global_16(g);
-    uv.u = ld_stream_16(u);
+                                                         long long sun, int vec_per_row, int chunks) {
+  const unsigned row = blockIdx.x / (unsigned)chunks, chunk = blockIdx.x - row * (unsigned)chunks;  // one division per CTA
+  const int v = (int)chunk * (int)blockDim.x + (int)threadIdx.x;
+  if (v >= vec_per_row) return;
+  __half *g = byte_off(gate, (long long)row * sgn) + v * 8;
+  const __half *u = byte_off(up, (long long)row * sun) + v * 8;
+  Pack8 gv, uv, out;
+  gv.u = ld_global_16(g);
+  uv.u = ld_stream_16(u);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(swiglu_f32(__half2float(gv.h[e]), __half2float(uv.h[e])));
-    st_global_16(g, out.u);
-  }
+  for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(swiglu_f32(__half2float(gv.h[e]), __half2float(uv.h[e])));
+  st_global_16(g, out.u);
 }
 
 template <class T>
@@ -93,12 +93,11 @@ OPS_API int ops_swiglu_launch(const ops_swiglu *op, const ops_swiglu_args *a, vo
   const int max_blocks = op->base.sm_count * 8;
 
   const bool fast = m.dt == OPS_DT_F16 && sgd == 2 && sud == 2 && m.d % 8 == 0 && sgn % 16 == 0 && sun % 16 == 0 &&
-                    aligned(a->gate_base, 16) && aligned(a->up_base, 16) && m.d / 8 <= 0x7fffffff;
+                    aligned(a->gate_base, 16) && aligned(a->up_base, 16) && m.n * ((m.d / 8 + 255) / 256) <= 0x7fffffffu;
   if (fast) {
-    const long long total = (long long)m.n * (long long)(m.d / 8);
-    const long long blocks = (total + 255) / 256;
-    swiglu_vec_kernel<<<(unsigned)(blocks < max_blocks ? blocks : max_blocks), 256, 0, s>>>(
-        (__half *)a->gate_base, sgn, (const __half *)a->up_base, sun, (int)(m.d / 8), total);
+    const int vpr = (int)(m.d / 8);
+    const int chunks = (vpr + 255) / 256;
+    swiglu_vec_kernel<<<(unsigned)(m.n * (usz)chunks), 256, 0, s>>>((__half *)a->gate_base, sgn, (const __half *)a->up_base, sun, vpr, chunks);
   } else {
     const long long total = (long long)m.n * (long long)m.d;
     const long long blocks = (total + 255) / 256;
