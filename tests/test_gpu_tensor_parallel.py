@@ -1,7 +1,8 @@
 """Multi-GPU parity: all_reduce (NCCL and the NVLink peer-to-peer kernels) and the tensor-parallel layer, one process
 per GPU.  Skipped with fewer than 2 GPUs.  The oracle sums f16 partials in the crate's pairwise tree
 (operators/src/all_reduce/common_cpu.rs:66-145); the GPU paths accumulate in f32 and round once, so agreement is to f16
-rounding: |diff| <= 4e-3 for partials ~N(0,1)/sqrt(p) whose sum is ~N(0,1) (one f16 ulp at |x| in [2,4) is 2e-3).
+rounding: max-abs <= 1e-2 (BASELINE's budget) for partials ~N(0,1)/sqrt(p) whose sum is ~N(0,1); the peer-to-peer
+kernels are additionally checked bit for bit against their own specification (f32 sum in rank order, one rounding).
 """
 import importlib
 import os
@@ -103,7 +104,9 @@ def test_all_reduce_and_tp_layer(tmp_path, orc, synth, world):
             outs = [res[r][f"ar_{T}_{name}"] for r in range(world)]
             for o in outs[1:]:
                 np.testing.assert_array_equal(o.view(np.uint16), outs[0].view(np.uint16))  # every rank holds the same bits
-            assert float(np.abs(outs[0].astype(np.float32) - ref.astype(np.float32)).max()) <= 4e-3, (T, name)
+            # the oracle rounds to f16 after each of its log2(p) tree levels (up to 2e-3 per level at |x| in [4,8)); the GPU
+            # paths round once: BASELINE's max-abs 1e-2 budget covers three levels at p = 8
+            assert float(np.abs(outs[0].astype(np.float32) - ref.astype(np.float32)).max()) <= 1e-2, (T, name)
             if name in ("one_shot", "two_shot"):
                 np.testing.assert_array_equal(outs[0].view(np.uint16), acc.astype(np.float16).view(np.uint16))
     layer = importlib.import_module(graft.PKG_NAME + ".layer")
