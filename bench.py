@@ -131,6 +131,132 @@ def cpu_layer_baseline(tokens, repeats, warmup):
     return tokens / sec, orc.num_threads(), sec
 
 
+def extra_measurements(torch, pkg, device, peaks, comm, tp, dist):
+    """Per-operator numbers for the BASELINE configs the layer loop does not cover: config 1 (latency of the small
+    chain), config 2 (attention prefill pieces, KV-cache write), config 5 (random_sample) on one GPU; config 4's
+    all_reduce sizes under tensor parallelism.  CUDA events around back-to-back launches; inputs rotate through more
+    than an L2 worth of buffers where a single copy would fit in L2."""
+    idx = device.index or 0
+    f16 = torch.float16
+    g = torch.Generator(device=device).manual_seed(SEED + 99)
+
+    def randn(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).half()
+
+    side = torch.cuda.Stream(device)
+
+    def timeit(fn, reps, warm=3, graph=True):
+        """ms per call of fn(i).  The calls are captured once into a CUDA graph on a side stream and the graph is
+        replayed, so that host-side launch cost (ctypes, argument marshalling) does not starve the GPU between the
+        microsecond-scale kernels; collectives are timed eagerly."""
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if graph:
+            try:
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg, stream=side):
+                    for i in range(reps):
+                        fn(i)
+                cg.replay()
+                torch.cuda.synchronize()
+                a.record()
+                cg.replay()
+                cg.replay()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) / (2 * reps)
+            except Exception as e:  # fall back to eager timing
+                print(f"bench: graph capture failed ({e}); timing eagerly", file=sys.stderr)
+                torch.cuda.synchronize()
+        a.record()
+        for i in range(reps):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps  # ms
+
+    def hbm(ms, nbytes):
+        ach = nbytes / (ms * 1e-3) / 1e9
+        return {"us": ms * 1e3, "bound": "hbm", "achieved": ach, "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "bytes": nbytes}
+
+    def tensor(ms, flops):
+        ach = flops / (ms * 1e-3) / 1e12
+        return {"us": ms * 1e3, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tflops_burst"], "flops": flops}
+
+    out = {}
+    if tp > 1:
+        op = pkg.AllReduce(comm)
+        for T in (1, 64, 4096):
+            nbytes = T * 4096 * 2
+            buf = randn(T, 4096)
+            res = {}
+            for name, algo in (("nccl", pkg.ALL_REDUCE_NCCL), ("one_shot", pkg.ALL_REDUCE_P2P_ONE_SHOT), ("two_shot", pkg.ALL_REDUCE_P2P_TWO_SHOT)):
+                if name == "one_shot" and nbytes > (1 << 22):
+                    continue
+                op.set_algo(algo)
+                args = pkg.AllReduceArgs.of(buf, buf)
+                dist.barrier()
+                ms = timeit(lambda i: op.launch(args), 20, warm=3, graph=False)
+                tt = torch.tensor([ms], device=device, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                ms = float(tt[0])
+                bus = 2 * (tp - 1) / tp * nbytes / (ms * 1e-3) / 1e9
+                res[name] = {"us": ms * 1e3, "bus_GBps": bus, "frac_of_770": bus / 770.0}
+            out[f"all_reduce_T{T}"] = {"message_bytes": nbytes, **res}
+        return out
+
+    # ---- config 1: the small chain (latency; far below any roofline at 256 KiB) ----
+    x, w = randn(64, 2048), (torch.rand(2048, generator=g, device=device) + 0.5).half()
+    y = torch.empty_like(x)
+    pos = torch.arange(64, dtype=torch.int32, device=device).view(torch.uint32)
+    sc = randn(32, 64, 64, std=2.0)
+    rn, rp, sm = pkg.RmsNorm(idx), pkg.Rope(idx), pkg.FusedSoftmax(idx)
+    a1, a2, a3 = pkg.RmsNormArgs.of(y, x, w, 1e-5), pkg.RopeArgs.of(y.view(64, 32, 64), pos, 1e4), pkg.FusedSoftmaxArgs.of(sc)
+    out["config1_chain_latency_us"] = {"rms_norm": timeit(lambda i: rn.launch(a1), 50) * 1e3, "rope": timeit(lambda i: rp.launch(a2), 50) * 1e3,
+                                       "fused_softmax": timeit(lambda i: sm.launch(a3), 50) * 1e3}
+    # ---- config 2: attention prefill ----
+    nh, nkvh, seq, dh = 32, 8, 2048, 128
+    sets = [(randn(nh, seq, dh), randn(nkvh, seq, dh), randn(nkvh, seq, dh), torch.empty(nh, seq, dh, dtype=f16, device=device)) for _ in range(3)]
+    att = pkg.Attention(idx)
+    ws = torch.empty((nh * seq * dh + nh * seq * seq) * 2, dtype=torch.uint8, device=device)
+    fl = 4 * nh * dh * (seq * (seq + 1) // 2)
+    aargs = [pkg.AttentionArgs.of(q, k, v, o) for q, k, v, o in sets]
+    out["config2_attention_fused"] = tensor(timeit(lambda i: att.launch(aargs[i % 3], ws), 20), fl)
+    att.set_algo(pkg.ATTENTION_CHAIN)
+    out["config2_attention_chain"] = tensor(timeit(lambda i: att.launch(aargs[i % 3], ws), 10), fl)
+    mm = pkg.MatMul(idx)
+    scores = torch.empty(nkvh, 4 * seq, seq, dtype=f16, device=device)
+    q, k, v, o = sets[0]
+    qk = pkg.MatMulArgs.of(scores, 0.0, q.view(nkvh, 4 * seq, dh), k.transpose(1, 2), 1.0 / 128 ** 0.5)
+    nb = 2 * nkvh * (4 * seq * dh + dh * seq + 4 * seq * seq)
+    out["config2_mat_mul_qkT_unfused"] = {**hbm(timeit(lambda i: mm.launch(qk), 10), nb), "flops": 2 * nkvh * 4 * seq * seq * dh}
+    pv = pkg.MatMulArgs.of(o.view(nkvh, 4 * seq, dh), 0.0, scores, v, 1.0)
+    out["config2_mat_mul_pv_unfused"] = {**hbm(timeit(lambda i: mm.launch(pv), 10), nb), "flops": 2 * nkvh * 4 * seq * seq * dh}
+    smx = pkg.FusedSoftmaxArgs.of(scores.view(nh, seq, seq))
+    out["config2_fused_softmax"] = hbm(timeit(lambda i: sm.launch(smx), 10), nh * seq * seq * 2 + nh * 2 * (seq * (seq + 1) // 2))
+    caches = [torch.zeros(nkvh, 4096, dh, dtype=f16, device=device) for _ in range(10)]
+    rr = pkg.Rearrange(idx)
+    rargs = [pkg.RearrangeArgs.of(c[:, 2048:, :], k) for c in caches]
+    out["config2_kv_cache_write"] = hbm(timeit(lambda i: rr.launch(rargs[i % 10]), 40), 2 * nkvh * seq * dh * 2)
+    # ---- config 5: random_sample over 64 x 128256 logits ----
+    rows, n = 64, 128256
+    logits = [randn(rows, n, std=3.0) for _ in range(10)]
+    seeds = torch.rand(rows, generator=g, device=device)
+    kv = torch.zeros(rows, 2, dtype=torch.int32, device=device)
+    rs = pkg.RandomSample(idx)
+    cfg_s = pkg.SampleArgs(0.8, 0.9, 50)
+    wsr = torch.empty(16 * n * rows + 4096, dtype=torch.uint8, device=device)
+    out["config5_argmax_batched"] = hbm(timeit(lambda i: rs.launch_batched(logits[i % 10], kv, pkg.SampleArgs.arg_max(), None, wsr), 40), rows * n * 2)
+    out["config5_sample_batched"] = hbm(timeit(lambda i: rs.launch_batched(logits[i % 10], kv, cfg_s, seeds, wsr), 10), rows * n * 2)
+    one = [pkg.RandomSampleArgs.of(kv[r], logits[0][r], pkg.SampleArgs.arg_max()) for r in range(rows)]
+    ms = timeit(lambda i: [rs.launch(a, wsr) for a in one], 5)
+    out["config5_argmax_per_row_api"] = {**hbm(ms, rows * n * 2), "launches": rows}
+    return out
+
+
+
 def run_reference(args, rank):
     """--impl reference: the CPU arm alone (rank 0 only under torchrun)."""
     if rank != 0:
@@ -157,6 +283,7 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=512, help="tokens per step of the CPU arm")
     ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-operator measurements of configs 1, 2, 4 and 5")
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -330,13 +457,19 @@ def main():
                 "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (kernel timed inside a long step)",
                 "algorithmic_flops_per_launch": work["mat_mul_gate_up"][1]}
 
+    extras = None
+    if not args.no_extras:
+        del layer, shard
+        torch.cuda.empty_cache()
+        extras = extra_measurements(torch, pkg, device, peaks, comm, tp, dist)
+
     if rank != 0:
         if comm is not None:
             barrier()
             dist.destroy_process_group()
         return
     ms_per_step = total_ms / args.steps
-    kernels_per_step = 1 + 2 + 4 + 1 + 1 + 5  # copy, rms_norm x2, mat_mul x4, rope, swiglu, attention chain (2 rearranges, 2 mat_mul, softmax)
+    kernels_per_step = 1 + 2 + 4 + 1 + 1 + 1  # residual reset copy, rms_norm x2, mat_mul x4, rope, swiglu, fused attention
     if tp > 1 and args.all_reduce != "nccl":
         kernels_per_step += 2
     line = {
@@ -345,8 +478,8 @@ def main():
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": WORKLOAD if tp == 1 else WORKLOAD.replace("config 3", "config 4") + f", tensor-parallel over {tp} GPUs",
                    "tokens": T, "parallelism": f"tp{tp}", "all_reduce": args.all_reduce if tp > 1 else None,
-                   "l2": "inputs larger than L2: every step streams 436 MB of weights and a 1 GiB score matrix through a 126 MB L2",
-                   "attention": "operator chain (rearrange, mat_mul, fused_softmax, mat_mul, rearrange) with the score matrix in workspace"},
+                   "l2": "inputs larger than L2: every step streams 436 MB of weights and ~0.6 GB of activations through a 126 MB L2",
+                   "attention": "fused flash-attention kernel behind attention::Args (the crate's operator chain is measured in other_configs)"},
         "clocks": clocks,
         "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * d * E, "d2h_bytes_per_step": T * d * E,
                 "ms_per_step": e2e_ms / args.steps},
@@ -354,6 +487,8 @@ def main():
         "roofline": roofline,
         "ops": ops,
     }
+    if extras is not None:
+        line["other_configs"] = extras
     if tp == 1 and not args.no_cpu_baseline:
         tps, threads, sec = cpu_layer_baseline(args.cpu_tokens, 1, 0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",

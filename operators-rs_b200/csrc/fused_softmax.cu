@@ -6,7 +6,7 @@
 //
 // HBM-bound: every element is written (masked ones as zero) but only the unmasked prefix of a causal
 // row is read.  A row lives in registers between the max, exp/sum and scale steps, so the prefix is
-// read from HBM once.  Short rows: one warp per row; long rows: one CTA per row.  The f16 rounding
+// read from HBM once.  Rows up to 4096 columns: one warp per row; longer rows: one CTA per row.  The f16 rounding
 // sequence of the CPU path is kept: exp is rounded to f16, the sum uses the unrounded f32 exps, the
 // rounded value is re-widened, scaled by 1/sum and rounded again.
 #include "common.h"
@@ -148,20 +148,18 @@ int ops::fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args 
   const long long rows = (long long)nh * (long long)seq;
   const bool vec = dt == OPS_DT_F16 && sa == 2 && att_len % 8 == 0 && sh % 16 == 0 && ss % 16 == 0 && aligned(a->att_base, 16);
   const int nvec = (int)(att_len / 8);
-  if (vec && nvec <= 32 * 4) {
-    // one warp per row, 8 rows per CTA
+  if (vec && nvec <= 32 * 16) {
+    // one warp per row (rows up to 4096 columns live in 64 registers per lane): no block-level synchronisation,
+    // 8 rows per CTA keep enough bytes in flight even when a causal mask leaves most lanes of a row idle
     const unsigned grid = (unsigned)((rows + 7) / 8);
     if (nvec <= 32) softmax_f16_reg_kernel<1, true><<<grid, 256, 0, s>>>(p);
     else if (nvec <= 64) softmax_f16_reg_kernel<2, true><<<grid, 256, 0, s>>>(p);
-    else softmax_f16_reg_kernel<4, true><<<grid, 256, 0, s>>>(p);
+    else if (nvec <= 128) softmax_f16_reg_kernel<4, true><<<grid, 256, 0, s>>>(p);
+    else if (nvec <= 256) softmax_f16_reg_kernel<8, true><<<grid, 256, 0, s>>>(p);
+    else softmax_f16_reg_kernel<16, true><<<grid, 256, 0, s>>>(p);
   } else if (vec && nvec <= 256 * 8) {
-    // one CTA per row; threads sized so that every thread owns at most VPT vectors
-    const unsigned grid = (unsigned)rows;
-    if (nvec <= 256 * 2) {
-      const int threads = nvec <= 128 * 2 ? 128 : 256;
-      softmax_f16_reg_kernel<2, false><<<grid, threads, 0, s>>>(p);
-    } else if (nvec <= 256 * 4) softmax_f16_reg_kernel<4, false><<<grid, 256, 0, s>>>(p);
-    else softmax_f16_reg_kernel<8, false><<<grid, 256, 0, s>>>(p);
+    // one CTA per row; every thread owns at most 8 vectors
+    softmax_f16_reg_kernel<8, false><<<(unsigned)rows, 256, 0, s>>>(p);
   } else if (dt == OPS_DT_F16) {
     softmax_generic_kernel<__half><<<(unsigned)rows, 256, 0, s>>>(p);
   } else {

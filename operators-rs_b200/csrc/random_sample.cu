@@ -66,26 +66,47 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
   chunk = (chunk + 7) & ~7;
   const int begin = part * chunk, end = min(n, begin + chunk);
 
-  unsigned long long best = 0;
+  // per thread: running (value, index) with ">=" so that the later of equal values wins (+0 and -0 compare equal);
+  // NaNs are skipped here and only remembered (their last index), see the finish below
+  float best_v = -INFINITY;
+  int best_i = -1;
   unsigned int last_nan = 0;
   auto visit = [&](float v, int i) {
-    if (v != v) last_nan = max(last_nan, (unsigned)i + 1u);
-    else best = max(best, ((unsigned long long)ordered_key(v) << 32) | (unsigned)i);
+    if (v >= best_v) {
+      best_v = v;
+      best_i = i;
+    } else if (v != v) {
+      last_nan = (unsigned)i + 1u;  // indices only grow within a thread
+    }
   };
   const bool vec_ok = (((uintptr_t)x) & 15) == 0;
   constexpr int PER = 16 / (int)sizeof(T);
   if (vec_ok) {
     const int vend = begin + ((end - begin) / PER) * PER;
-    for (int i = begin + threadIdx.x * PER; i < vend; i += blockDim.x * PER) {
+    const int step = blockDim.x * PER;
+    int i = begin + threadIdx.x * PER;
+    for (; i + 3 * step < vend; i += 4 * step) {  // four independent 128-bit loads in flight per thread
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) raw[u] = ld_stream_16(x + i + u * step);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T *e = reinterpret_cast<const T *>(&raw[u]);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i + u * step + j);
+      }
+    }
+    for (; i < vend; i += step) {
       const uint4 raw = ld_stream_16(x + i);
       const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
       for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i + j);
     }
-    for (int i = vend + threadIdx.x; i < end; i += blockDim.x) visit(to_f32(x[i]), i);
+    for (int k = vend + threadIdx.x; k < end; k += blockDim.x) visit(to_f32(x[k]), k);
   } else {
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) visit(to_f32(x[i]), i);
+    for (int k = begin + threadIdx.x; k < end; k += blockDim.x) visit(to_f32(x[k]), k);
   }
+  unsigned long long best = best_i < 0 ? 0ull : (((unsigned long long)ordered_key(best_v) << 32) | (unsigned)best_i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -500,7 +521,7 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
     cudaMemsetAsync(ws, 0, need, s);
     // split a row over several CTAs when there are few rows; keep >= 8 KiB per CTA
     const usz row_bytes = n * dt_size(dt);
-    usz split = (2 * (usz)base.sm_count + rows - 1) / rows;
+    usz split = (8 * (usz)base.sm_count + rows - 1) / rows;  // ~8 CTAs per SM keep enough loads in flight
     const usz max_split = (row_bytes + 8191) / 8192;
     if (split > max_split) split = max_split;
     if (split < 1) split = 1;
