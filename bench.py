@@ -285,6 +285,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-operator measurements of configs 1, 2, 4 and 5")
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot"])
+    ap.add_argument("--overlap-chunks", type=int, default=1, help="token chunks of the row-parallel projections whose all_reduce overlaps the next chunk's GEMM")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -328,7 +329,7 @@ def main():
     if tp > 1:
         del full
         torch.cuda.empty_cache()
-    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo)
+    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks)
     g = torch.Generator(device=device).manual_seed(SEED + 7)
     x0 = torch.randn(T, CFG["d"], generator=g, device=device, dtype=torch.float32).half()
     x = torch.empty_like(x0)

@@ -78,8 +78,10 @@ class DecoderLayer:
     STEPS = ("rms_norm_1", "mat_mul_qkv", "rope", "attention", "mat_mul_o", "all_reduce_1", "rms_norm_2", "mat_mul_gate_up",
              "swiglu", "mat_mul_down", "all_reduce_2")
 
-    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO):
+    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1):
         import torch
+        self.overlap_chunks = max(1, int(overlap_chunks))
+        self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and self.overlap_chunks > 1) else None
         self.cfg, self.w, self.device, self.tp, self.rank = cfg, weights, device, tp, rank
         idx = device.index if device.index is not None else 0
         self.rms_norm, self.rope, self.swiglu = RmsNorm(idx), Rope(idx), Swiglu(idx)
@@ -130,16 +132,33 @@ class DecoderLayer:
         return x
 
     def _project_and_reduce(self, x, a, w, mm_name, ar_name, mark):
+        """Row-parallel projection + all_reduce.  With overlap_chunks > 1 the token dimension is cut into chunks: the
+        all_reduce of chunk c runs on a second stream while the tensor cores work on chunk c+1."""
+        import torch
         T = x.shape[0]
-        if self.tp == 1 or self.rank == 0:
-            out = x
-            self.mat_mul.launch(MatMulArgs.of(out, 1.0, a, w, 1.0))  # residual folded in: x <- x + a w
-        else:
-            # ranks other than 0 never read the residual: their partial goes to scratch, which holds the stream from here on
-            out = self.scratch[:T]
-            self.mat_mul.launch(MatMulArgs.of(out, 0.0, a, w, 1.0))
+        first = self.tp == 1 or self.rank == 0
+        # rank 0 (and the single-GPU case) folds the residual in: x <- x + a w.  The other ranks never read the
+        # residual: their partial goes to scratch, which holds the stream from here on.
+        out, beta = (x, 1.0) if first else (self.scratch[:T], 0.0)
+        chunks = self.overlap_chunks if (self.tp > 1 and T >= 256 * self.overlap_chunks) else 1
+        if chunks == 1:
+            self.mat_mul.launch(MatMulArgs.of(out, beta, a, w, 1.0))
+            mark(mm_name)
+            if self.tp > 1:
+                self.all_reduce.launch(AllReduceArgs.of(out, out))
+                mark(ar_name)
+            return out
+        main = torch.cuda.current_stream()
+        step = (T + chunks - 1) // chunks
+        step = (step + 127) // 128 * 128
+        for lo in range(0, T, step):
+            hi = min(T, lo + step)
+            self.mat_mul.launch(MatMulArgs.of(out[lo:hi], beta, a[lo:hi], w, 1.0))
+            ready = main.record_event()
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                self.all_reduce.launch(AllReduceArgs.of(out[lo:hi], out[lo:hi]))
         mark(mm_name)
-        if self.tp > 1:
-            self.all_reduce.launch(AllReduceArgs.of(out, out))
-            mark(ar_name)
+        main.wait_stream(self.comm_stream)
+        mark(ar_name)
         return out
