@@ -454,7 +454,10 @@ def main():
             ops[n] = {"ms": ms, "bound": "nvlink", "achieved": ach, "unit": "GB/s (bus)", "frac": ach / 770.0}
     dom = ops["mat_mul_gate_up"]
     roofline = {"kernel": "gemm_f16_tcgen05_kernel<256> (mat_mul gate|up launch)", "bound": "tensor", "achieved": dom["achieved"],
-                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": dom["frac"], "traffic": None,
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": dom["frac"],
+                # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the one-pass ncu capture summarised in
+                # profiles/layer_config3_dram_traffic.md (296.8 MB + 210.8 MB); only known for the config-3 shape
+                "traffic": 507593472 if (tp == 1 and T == 4096) else None,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (kernel timed inside a long step)",
                 "algorithmic_flops_per_launch": work["mat_mul_gate_up"][1]}
 

@@ -4,8 +4,9 @@
 // operators/src/attention/args.rs:60-90) and attention_kv_cached::Operator
 // (operators/src/attention_kv_cached/operator.rs:76-183, checks attention_kv_cached/args.rs:72-115).
 //
-// Algorithm 1 (OPS_ATTENTION_FUSED, the default) runs the one-kernel flash attention of attention_fused.cu whenever the
-// layouts allow it (f16, dh 64 or 128, 16-byte aligned rows) and falls back to algorithm 0 otherwise.
+// Algorithm 1 (OPS_ATTENTION_FUSED, the default) runs one kernel whenever the layouts allow it (f16, dh 64 or 128,
+// 16-byte aligned rows): the split-KV decode kernel of attention_decode.cu for at most 8 query rows per kv head over
+// 256 keys or more, else the tensor-core flash attention of attention_fused.cu; it falls back to algorithm 0 otherwise.
 // Algorithm 0 (OPS_ATTENTION_CHAIN) is the crate's own composition, step for step, on this library's
 // kernels: [copy q to a contiguous buffer unless its (nh, seq) dims merge] -> att = alpha q k^T
 // (batched over kv heads, the q rows of one group stacked) -> causal softmax in place -> q = att v ->
@@ -21,6 +22,8 @@ struct ops_attention {
   int algo;
   int *status_dev;      // written by the fused kernel when a bounded wait runs out
   bool attr_set[2];
+  float *decode_scratch;          // split-KV partials of the decode kernel (owned by the handle; one stream at a time)
+  unsigned int *decode_tickets;   // arrival counters, left at zero by every launch
 };
 
 namespace ops {
@@ -129,6 +132,9 @@ int attention_enqueue(const ops_attention *op, const ops_attention_args *a, void
   if (m.nkvh == 0 || m.nh % m.nkvh != 0) return fail(OPS_SHAPE_MISMATCH, "attention: nh must be a multiple of nkvh");
   if (a->mask == OPS_MASK_CAUSAL && m.att < m.seq) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: causal mask needs att >= seq");
   if (m.nh == 0 || m.seq == 0 || m.dh == 0 || m.att == 0) return OPS_OK;
+  if (op->algo == OPS_ATTENTION_FUSED && a->q_base && a->k_base && a->v_base && a->o_base && op->decode_scratch &&
+      attention_decode_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh))
+    return attention_decode_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->decode_scratch, op->decode_tickets, s);
   if (op->algo == OPS_ATTENTION_FUSED && a->q_base && a->k_base && a->v_base && a->o_base &&
       attention_fused_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh)) {
     ops_attention *mop = const_cast<ops_attention *>(op);
@@ -146,15 +152,24 @@ OPS_API int ops_attention_create(int device, ops_attention **out) {
   h->algo = OPS_ATTENTION_FUSED;
   h->status_dev = nullptr;
   h->attr_set[0] = h->attr_set[1] = false;
+  h->decode_scratch = nullptr;
+  h->decode_tickets = nullptr;
   int rc = init_base(&h->base, device);
   if (rc == OPS_OK) rc = ops_mat_mul_create(device, &h->mat_mul);
   if (rc == OPS_OK) {
     cudaSetDevice(device);
     if (cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess || cudaMemset(h->status_dev, 0, sizeof(int)) != cudaSuccess)
       rc = fail(OPS_EXECUTION_FAILED, "attention: cannot allocate the status word");
+    else if (cudaMalloc(&h->decode_scratch, attention_decode_scratch_bytes()) != cudaSuccess ||
+             cudaMalloc(&h->decode_tickets, attention_decode_ticket_bytes()) != cudaSuccess ||
+             cudaMemset(h->decode_tickets, 0, attention_decode_ticket_bytes()) != cudaSuccess)
+      rc = fail(OPS_EXECUTION_FAILED, "attention: cannot allocate the decode scratch");
   }
   if (rc != OPS_OK) {
     if (h->mat_mul) ops_mat_mul_destroy(h->mat_mul);
+    if (h->status_dev) cudaFree(h->status_dev);
+    if (h->decode_scratch) cudaFree(h->decode_scratch);
+    if (h->decode_tickets) cudaFree(h->decode_tickets);
     delete h;
     return rc;
   }
@@ -166,6 +181,8 @@ OPS_API void ops_attention_destroy(ops_attention *op) {
   if (!op) return;
   if (op->mat_mul) ops_mat_mul_destroy(op->mat_mul);
   if (op->status_dev) cudaFree(op->status_dev);
+  if (op->decode_scratch) cudaFree(op->decode_scratch);
+  if (op->decode_tickets) cudaFree(op->decode_tickets);
   delete op;
 }
 

@@ -11,9 +11,11 @@
 //   warp 1   tcgen05.mma issuer: S_j = Q K_j^T into tensor memory (two S buffers), then
 //            PV_j = P_j V_j into a second pair of tensor-memory buffers — never accumulating across
 //            blocks, so no rescaling ever touches tensor memory;
-//   warps 2-5  softmax: thread = one q row.  tcgen05.ld S_j, running max / sum in the exp2 domain,
-//            P_j -> f16 into shared memory in the swizzled K-major layout the MMA reads, then
-//            O = O * alpha + PV_{j-1} in REGISTERS (dh f32 per thread), final 1/l and store.
+//   warps 2-9  softmax: two threads per q row (two warps per scheduler hide each other's latencies).
+//            Both tcgen05.ld the whole S_j row for its maximum; each then turns HALF of the keys into
+//            P_j (exp2 domain, f16, written to shared memory in the swizzled K-major layout the MMA
+//            reads) and keeps HALF of the dh columns of O = O * alpha + PV_{j-1} in REGISTERS;
+//            partial row sums meet once at the end, then 1/l and the store.
 // The issue order QK_j, PV_{j-1}, QK_{j+1}, ... lets the tensor pipe work on the next block while
 // the softmax warps are busy with the current one.  Every mbarrier wait is bounded.
 #include <cuda.h>
@@ -29,7 +31,7 @@ using namespace sm100;
 
 constexpr int FA_BM = 128;       // q rows per CTA
 constexpr int FA_BN = 128;       // keys per block
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two per scheduler)
 
 struct FusedAttnArgs {
   __half *o;
@@ -53,11 +55,17 @@ template <int DH> struct FaCfg {
   static constexpr int OFF_V = OFF_K + 2 * K_BYTES;      // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * V_BYTES;      // 2 buffers
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-  static constexpr int NUM_BARS = 1 + 8 + 12;            // q_full; k/v full+empty x2; s/p/pv full+empty x2
-  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int NUM_BARS = 1 + 8 + 12 + 4;        // q_full; k/v full+empty x2; s/p/pv full+empty x2; row-sum exchange x4
+  static constexpr int OFF_LSUM = OFF_BAR + NUM_BARS * 8 + 16;  // [2 halves][128 rows] f32 partial row sums
+  static constexpr int SMEM_BYTES = OFF_LSUM + 2 * FA_BM * 4 + 1024;
   static constexpr int TMEM_COLS = 512;                  // S0 S1 (128 each) | PV0 PV1 (128 each, DH used)
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {  // three-input maximum (sm_100)
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -85,6 +93,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   auto p_empty = [&](int b) { return bar0 + 8u * (15 + b); };
   auto pv_full = [&](int b) { return bar0 + 8u * (17 + b); };
   auto pv_empty = [&](int b) { return bar0 + 8u * (19 + b); };
+  auto l_bar = [&](int q) { return bar0 + 8u * (21 + q); };
   const uint32_t tmem_slot = bar0 + 8u * Cfg::NUM_BARS;
   uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(base_ptr + Cfg::OFF_BAR + 8 * Cfg::NUM_BARS);
 
@@ -107,12 +116,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(s_empty(s), 4);
-      mbar_init(p_full(s), 4);
+      mbar_init(s_empty(s), 8);
+      mbar_init(p_full(s), 8);
       mbar_init(p_empty(s), 1);
       mbar_init(pv_full(s), 1);
-      mbar_init(pv_empty(s), 4);
+      mbar_init(pv_empty(s), 8);
     }
+    for (int q = 0; q < 4; ++q) mbar_init(l_bar(q), 2);
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -201,15 +211,20 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       if (ok && nblk > 0) issue_pv(nblk - 1);
     }
   } else {
-    // ------------------------------------------------------------------ softmax + output (warps 2..5)
+    // ------------------------------------------------------------------ softmax + output (warps 2..9)
+    // Two warps share each 32-row quarter of tensor memory (a warp may touch lanes 32*(warp%4)..+31 only): both scan the
+    // whole S row for its maximum (so they agree on it without talking), then each takes HALF of the key columns for
+    // exp/P and HALF of the dh columns of O.  Their partial row sums meet once, after the last block.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int DHH = DH / 2;
     const int row_in_tile = quarter * 32 + lane;
     const int q_row = q0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int limit = g.causal ? min(g.att - 1, off + q_row) : g.att - 1;  // last key this row may see
-    float o[DH];
+    float o[DHH];
 #pragma unroll
-    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    for (int i = 0; i < DHH; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
     bool ok = true;
 
@@ -217,9 +232,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       const int b = i & 1;
       if (!mbar_wait(pv_full(b), (uint32_t)((i >> 1) & 1), g.status, 31)) return false;
       tc_fence_after();
-      const uint32_t t = tmem_base + lane_addr + 256u + (uint32_t)(b * 128);
+      const uint32_t t = tmem_base + lane_addr + 256u + (uint32_t)(b * 128 + half * DHH);
 #pragma unroll
-      for (int c = 0; c < DH; c += 32) {
+      for (int c = 0; c < DHH; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(t + (uint32_t)c, v);
         tmem_wait_ld();
@@ -242,18 +257,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       const bool need_mask = kv0 + FA_BN - 1 > limit;
       // pass A: row maximum of this block
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t + (uint32_t)c, v);
+#pragma unroll
+      for (int c = 0; c < FA_BN; c += 64) {
+        uint32_t v[64];  // two 32-column loads in flight per wait
+        tmem_ld_32x32(t + (uint32_t)c, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld_32x32(t + (uint32_t)c + 32u, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
         tmem_wait_ld();
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
+          for (int e = 0; e < 64; ++e)
             if (kv0 + c + e <= limit) mx = fmaxf(mx, __uint_as_float(v[e]));
         } else {
+          float m0 = mx, m1 = -INFINITY;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+          for (int e = 0; e < 64; e += 4) {
+            m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+            m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+          }
+          mx = fmaxf(m0, m1);
         }
       }
       const float m_raw = fmaxf(m, mx * g.scale_log2);
@@ -263,8 +284,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       if (!(ok = mbar_wait(p_empty(b), ph ^ 1u, g.status, 33))) break;
       uint8_t *p_row = base_ptr + Cfg::OFF_P + b * Cfg::P_BYTES + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN; c += 32) {
+#pragma unroll
+      for (int c = half * (FA_BN / 2); c < (half + 1) * (FA_BN / 2); c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(t + (uint32_t)c, v);
         tmem_wait_ld();
@@ -301,12 +322,18 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       m = m_new;
     }
     if (ok && nblk > 0) ok = accumulate_pv(nblk - 1, alpha_prev);
+    // the two warps of a quarter add up their partial row sums
+    float *lsum = reinterpret_cast<float *>(base_ptr + Cfg::OFF_LSUM);
+    lsum[half * FA_BM + row_in_tile] = l;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(l_bar(quarter));
+    if (ok) ok = mbar_wait(l_bar(quarter), 0, g.status, 34);
     if (ok && q_row < g.seq) {
-      const float inv = __frcp_rn(l);
-      __half *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss;
+      const float inv = __frcp_rn(l + lsum[(half ^ 1) * FA_BM + row_in_tile]);
+      __half *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss + half * DHH;
       if (g.vec_store) {
 #pragma unroll
-        for (int c = 0; c < DH; c += 8) {
+        for (int c = 0; c < DHH; c += 8) {
           Pack8 out;
 #pragma unroll
           for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(o[c + e] * inv);
@@ -314,7 +341,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < DH; ++c) orow[c] = __float2half_rn(o[c] * inv);
+        for (int c = 0; c < DHH; ++c) orow[c] = __float2half_rn(o[c] * inv);
       }
     }
   }

@@ -14,4 +14,10 @@ bool attention_fused_supported(const ops_attention_args *a, usz nh, usz nkvh, us
 int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
                             bool *attr_set, cudaStream_t s);
 
+bool attention_decode_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh);
+usz attention_decode_scratch_bytes();
+usz attention_decode_ticket_bytes();
+int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, float *scratch,
+                             unsigned int *tickets, cudaStream_t s);
+
 }  // namespace ops

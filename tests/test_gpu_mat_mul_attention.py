@@ -72,6 +72,15 @@ def test_mat_mul_edges(pkg, orc, synth, dev, m, n, k):
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 1.0, 1.0, seed=40)
 
 
+@pytest.mark.parametrize("m,n,k", [(1024, 2048, 12288), (256, 512, 12288), (300, 700, 16000)])
+def test_mat_mul_split_k_remainder_wave(pkg, orc, synth, dev, m, n, k):
+    # long K and a tile count that leaves a partial last wave: the remainder tiles are cut along K over the idle CTAs
+    # (2 slices for 64 tiles, 8 slices for a handful) and the f32 partials are added in slice order; twice in a row to
+    # check that the arrival counters are left at zero
+    gemm_case(pkg, orc, synth, dev, None, m, n, k, False, False, False, 1.0, 0.0, seed=80)
+    gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 0.5, 1.0, seed=90)
+
+
 def test_mat_mul_broadcast_and_unaligned(pkg, orc, synth, dev):
     gemm_case(pkg, orc, synth, dev, 5, 96, 160, 64, False, False, False, 1.0, 0.0, seed=50, bcast_b=True)
     # k = 30 / n = 50: strides that TMA cannot describe -> generic kernel, same answers
@@ -144,6 +153,34 @@ def test_attention_reference_shape(pkg, orc, synth, dev, token_major):
 def test_attention_shapes(pkg, orc, synth, dev, nh, nkvh, seq, att, dh):
     attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, True)
     attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, False, causal=False)
+
+
+@pytest.mark.parametrize("nh,nkvh,seq,att,dh", [(32, 8, 1, 4096, 128), (32, 8, 2, 1000, 128), (16, 4, 1, 257, 64), (8, 8, 3, 640, 64), (4, 1, 2, 2049, 128)])
+def test_attention_decode_shapes(pkg, orc, synth, dev, nh, nkvh, seq, att, dh):
+    # a few query tokens against a long key range: the split-KV decode kernel (group * seq <= 8 rows per kv head)
+    attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, True, seed=300)
+    attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, False, causal=False, seed=310, algos=("fused",))
+
+
+def test_attention_kv_cached_decode_steps(pkg, orc, synth, dev):
+    # prefill 300 tokens, then three single-token decode steps through attention_kv_cached; caches byte-exact, outputs within 1e-2
+    nh, nkvh, dh, buf = 16, 4, 128, 512
+    kc, vc = np.zeros((nkvh, buf, dh), np.float16), np.zeros((nkvh, buf, dh), np.float16)
+    kcd, vcd = to_dev(kc, dev), to_dev(vc, dev)
+    op = pkg.AttentionKvCached(0)
+    pos = 0
+    for step, seq in enumerate([300, 1, 1, 1]):
+        q = synth.normal(400 + step, (nh, seq, dh), 1.0).astype(np.float16)
+        k = synth.normal(500 + step, (nkvh, seq, dh), 1.0).astype(np.float16)
+        v = synth.normal(600 + step, (nkvh, seq, dh), 1.0).astype(np.float16)
+        qd, od = to_dev(q, dev), torch.zeros(nh, seq, dh, dtype=torch.float16, device=dev)
+        op.launch(pkg.AttentionKvCachedArgs.of(qd, to_dev(k, dev), to_dev(v, dev), od, kcd, vcd, pos))
+        on = np.zeros_like(q)
+        orc.attention_kv_cached(q.copy(), k, v, on, kc, vc, pos, True)
+        np.testing.assert_array_equal(kcd.cpu().numpy().view(np.uint16), kc.view(np.uint16))
+        np.testing.assert_array_equal(vcd.cpu().numpy().view(np.uint16), vc.view(np.uint16))
+        assert_close(od.cpu().numpy(), on, 1e-2, f"attention_kv_cached step {step}")
+        pos += seq
 
 
 def test_attention_workspace_fallback(pkg, orc, synth, dev):
