@@ -338,6 +338,52 @@ int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args *args, s
 int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream);
 void ops_all_reduce_destroy(ops_all_reduce *op);
 
+/* =============================================================================================
+ * Operators on either side of the decoder layer (the crate's operators a caller chains around it).
+ * ============================================================================================= */
+
+/* add — add::Args (operators/src/add/args.rs:12-20); replaces add::common_cpu::Operator
+ * (operators/src/add/common_cpu/mod.rs:10-75).  c = a + b over N-d strided tensors of equal shape. */
+typedef struct ops_add ops_add;
+typedef struct {
+  ops_layout c_layout; void *c_base;
+  ops_layout a_layout; const void *a_base;
+  ops_layout b_layout; const void *b_base;
+} ops_add_args;
+int ops_add_create(int device, ops_add **out);
+int ops_add_scheme(ops_add *op, const ops_add_args *args, size_t max_ws, size_t *ws_out);
+int ops_add_launch(const ops_add *op, const ops_add_args *args, void *ws, size_t ws_len, void *stream);
+void ops_add_destroy(ops_add *op);
+
+/* add_rows — add_rows::Args (operators/src/add_rows/args.rs:10-17); replaces add_rows::common_cpu::Operator
+ * (operators/src/add_rows/common_cpu/mod.rs:12-148).  dst[b, m, :] += src[idx[b, m], :]; dst [batch, m, n],
+ * src [k, n], idx [batch, m] u32 or u64.  An index >= k (an assert in the crate) leaves the row untouched and
+ * sets the status word read by ops_add_rows_status (synchronises; no counterpart in the crate). */
+typedef struct ops_add_rows ops_add_rows;
+typedef struct {
+  ops_layout dst_layout; void *dst_base;
+  ops_layout src_layout; const void *src_base;
+  ops_layout idx_layout; const void *idx_base;
+} ops_add_rows_args;
+int ops_add_rows_create(int device, ops_add_rows **out);
+int ops_add_rows_scheme(ops_add_rows *op, const ops_add_rows_args *args, size_t max_ws, size_t *ws_out);
+int ops_add_rows_launch(const ops_add_rows *op, const ops_add_rows_args *args, void *ws, size_t ws_len, void *stream);
+int ops_add_rows_status(const ops_add_rows *op);
+void ops_add_rows_destroy(ops_add_rows *op);
+
+/* broadcast — broadcast::Args {pair: rearrange::Args, root} (operators/src/broadcast/args.rs:7-10); replaces
+ * broadcast::common_cpu::Operator (operators/src/broadcast/common_cpu/mod.rs:12-69) and the NCCL operator
+ * (operators/src/broadcast/nccl/mod.rs:36-60).  Every rank's dst receives root's src (bytes). */
+typedef struct ops_broadcast ops_broadcast;
+typedef struct {
+  ops_rearrange_args pair;
+  size_t root;
+} ops_broadcast_args;
+int ops_broadcast_create(ops_comm *node, ops_broadcast **out);
+int ops_broadcast_scheme(ops_broadcast *op, const ops_broadcast_args *args, size_t max_ws, size_t *ws_out);
+int ops_broadcast_launch(const ops_broadcast *op, const ops_broadcast_args *args, void *ws, size_t ws_len, void *stream);
+void ops_broadcast_destroy(ops_broadcast *op);
+
 #ifdef __cplusplus
 }
 #endif

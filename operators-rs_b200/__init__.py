@@ -220,6 +220,11 @@ _RandomSampleArgs = _struct("_RandomSampleArgs", [("kv_pair", _Layout), ("kv_pai
                                                   ("indices_base", ctypes.c_void_p), ("config", _SampleArgs),
                                                   ("seed", ctypes.c_float)])
 _AllReduceArgs = _struct("_AllReduceArgs", [("pair", _RearrangeArgs), ("op", ctypes.c_uint8)])
+_BroadcastArgs = _struct("_BroadcastArgs", [("pair", _RearrangeArgs), ("root", ctypes.c_size_t)])
+_AddArgs = _struct("_AddArgs", [("c_layout", _Layout), ("c_base", ctypes.c_void_p), ("a_layout", _Layout), ("a_base", ctypes.c_void_p),
+                                ("b_layout", _Layout), ("b_base", ctypes.c_void_p)])
+_AddRowsArgs = _struct("_AddRowsArgs", [("dst_layout", _Layout), ("dst_base", ctypes.c_void_p), ("src_layout", _Layout),
+                                        ("src_base", ctypes.c_void_p), ("idx_layout", _Layout), ("idx_base", ctypes.c_void_p)])
 
 
 def _lay(x):
@@ -388,6 +393,45 @@ class AllReduceArgs(_ArgsBase):
     @classmethod
     def of(cls, dst, src, op=REDUCE_SUM):
         return cls(dst, dst, src, src, op)
+
+
+class BroadcastArgs(_ArgsBase):
+    """broadcast::Args { pair: rearrange::Args, root } (operators/src/broadcast/args.rs:7-10)."""
+
+    def __init__(self, dst_layout, dst_base, src_layout, src_base, root):
+        self.keep = (_lay(dst_layout), _lay(src_layout))
+        self._alive = (dst_base, src_base,)
+        self.c = _BroadcastArgs(_RearrangeArgs(self.keep[0].c, _vp(dst_base), self.keep[1].c, _vp(src_base)), root)
+
+    @classmethod
+    def of(cls, dst, src, root):
+        return cls(dst, dst, src, src, root)
+
+
+class AddArgs(_ArgsBase):
+    """add::Args (operators/src/add/args.rs:12-20): c = a + b."""
+
+    def __init__(self, c_layout, c_base, a_layout, a_base, b_layout, b_base):
+        self.keep = (_lay(c_layout), _lay(a_layout), _lay(b_layout))
+        self._alive = (c_base, a_base, b_base,)
+        self.c = _AddArgs(self.keep[0].c, _vp(c_base), self.keep[1].c, _vp(a_base), self.keep[2].c, _vp(b_base))
+
+    @classmethod
+    def of(cls, c, a, b):
+        return cls(c, c, a, a, b, b)
+
+
+class AddRowsArgs(_ArgsBase):
+    """add_rows::Args (operators/src/add_rows/args.rs:10-17): dst[b, m, :] += src[idx[b, m], :]."""
+
+    def __init__(self, dst_layout, dst_base, src_layout, src_base, idx_layout, idx_base):
+        self.keep = (_lay(dst_layout), _lay(src_layout), _lay(idx_layout))
+        self._alive = (dst_base, src_base, idx_base,)
+        self.c = _AddRowsArgs(self.keep[0].c, _vp(dst_base), self.keep[1].c, _vp(src_base), self.keep[2].c, _vp(idx_base))
+
+    @classmethod
+    def of(cls, dst, src, idx):
+        return cls(dst, dst, src, src, idx, idx)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -621,15 +665,35 @@ class AllReduce(Operator):
         _check(lib().ops_all_reduce_set_algo(self._h, ctypes.c_int(algo)), False)
 
 
+class Broadcast(Operator):
+    NAME = "broadcast"
+
+    def _create(self, L, node):
+        self.comm = node
+        self.device = node.device
+        _check(L.ops_broadcast_create(node._h, ctypes.byref(self._h)), False)
+
+
+class Add(Operator):
+    NAME = "add"
+
+
+class AddRows(Operator):
+    NAME = "add_rows"
+
+    def status(self):
+        return lib().ops_add_rows_status(self._h)
+
+
 EXPORTS = [
     "ops_last_error", "ops_last_workspace_need", "ops_dtype_nbytes", "ops_device_count", "ops_build_info",
     *[f"ops_{op}_{fn}" for op in ("rms_norm", "rope", "fused_softmax", "swiglu", "rearrange", "mat_mul", "attention",
-                                  "attention_kv_cached", "random_sample", "all_reduce")
+                                  "attention_kv_cached", "random_sample", "all_reduce", "broadcast", "add", "add_rows")
       for fn in ("create", "scheme", "launch", "destroy")],
     "ops_rope_build_pos", "ops_rearrange_plan", "ops_mat_mul_status", "ops_attention_set_algo", "ops_attention_status",
     "ops_attention_kv_cached_set_algo", "ops_sample_args_new", "ops_random_sample_build_indices",
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
-    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo",
+    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo", "ops_add_rows_status",
 ]

@@ -46,6 +46,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
   std::string error;
 };
@@ -66,8 +67,9 @@ static NcclApi &nccl_api() {
     a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.lib, "ncclCommInitRank");
     a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.lib, "ncclCommDestroy");
     a.AllReduce = (decltype(a.AllReduce))dlsym(a.lib, "ncclAllReduce");
+    a.Broadcast = (decltype(a.Broadcast))dlsym(a.lib, "ncclBroadcast");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.lib, "ncclGetErrorString");
-    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.GetErrorString) a.error = "libnccl lacks a required symbol";
+    if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce || !a.Broadcast || !a.GetErrorString) a.error = "libnccl lacks a required symbol";
     return a;
   }();
   return api;
@@ -604,4 +606,59 @@ OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce
   if (!p2p_able) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: the peer-to-peer path needs an attached staging buffer of >= %zu bytes, f16/f32 Sum, 16-byte aligned data", bytes);
   if (m.dt == OPS_DT_F16) return launch_p2p<__half>(c, algo, src, dst, bytes, s);
   return launch_p2p<float>(c, algo, src, dst, bytes, s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// broadcast — broadcast::Args (operators/src/broadcast/args.rs:7-75): root's src bytes land in every rank's dst.
+// One ncclBroadcast on the caller's stream (operators/src/broadcast/nccl/mod.rs:53-58); a single rank copies.
+// ------------------------------------------------------------------------------------------------
+struct ops_broadcast {
+  ops_comm *comm;
+};
+
+OPS_API int ops_broadcast_create(ops_comm *node, ops_broadcast **out) {
+  if (!node || !out) return fail(OPS_ARGS_NOT_SUPPORT, "null communicator or out pointer");
+  ops_broadcast *h = new ops_broadcast();
+  h->comm = node;
+  *out = h;
+  return OPS_OK;
+}
+
+OPS_API void ops_broadcast_destroy(ops_broadcast *op) { delete op; }
+
+OPS_API int ops_broadcast_scheme(ops_broadcast *op, const ops_broadcast_args *args, size_t max_ws, size_t *ws_out) {
+  (void)op;
+  (void)max_ws;
+  (void)args;
+  if (ws_out) *ws_out = 0;
+  return OPS_OK;
+}
+
+OPS_API int ops_broadcast_launch(const ops_broadcast *op, const ops_broadcast_args *args, void *ws, size_t ws_len, void *stream) {
+  (void)ws;
+  (void)ws_len;
+  ops_comm *c = op->comm;
+  cudaStream_t s = (cudaStream_t)stream;
+  ops_all_reduce_args as_pair{args->pair, OPS_REDUCE_SUM};
+  AllReduceMeta m;
+  OPS_TRY(all_reduce_meta(&as_pair, &m));  // same layout rules: both sides one contiguous run of equal length
+  const usz bytes = m.len * dt_size(m.dt);
+  if (args->root >= (size_t)c->size) return fail(OPS_ARGS_NOT_SUPPORT, "broadcast: root %zu outside a group of %d", args->root, c->size);
+  if (bytes == 0) return OPS_OK;
+  void *dst = args->pair.dst_base;
+  const void *src = args->pair.src_base;
+  if (!dst || ((int)args->root == c->rank && !src)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "broadcast: null base pointer at launch");
+  cudaSetDevice(c->device);
+  if (c->size == 1) {
+    if (dst != src) {
+      OpBase base{c->device, c->sm_count};
+      return rearrange_enqueue(base, &args->pair, s);
+    }
+    return OPS_OK;
+  }
+  if (!c->has_nccl) return fail(OPS_EXECUTION_FAILED, "broadcast: communicator has no NCCL handle");
+  NcclApi &n = nccl_api();
+  ncclResult_t r = n.Broadcast(src ? src : dst, dst, bytes, ncclUint8, (int)args->root, c->nccl, s);
+  if (r != ncclSuccess) return fail(OPS_EXECUTION_FAILED, "ncclBroadcast: %s", n.GetErrorString(r));
+  return OPS_OK;
 }

@@ -660,3 +660,46 @@ ORC_API int orc_broadcast(usz p, usz bytes, usz root, void *const *bufs) {
     if (r != root) std::memcpy(bufs[r], bufs[root], bytes);
   return 0;
 }
+
+// add — add/common_cpu/mod.rs:68-75: c = a + b in the element type (f16: widened to f32, one rounding).
+// Shapes equal; strides in bytes; up to 8 dims.
+ORC_API int orc_add(uint32_t dt, usz ndim, const usz *shape, void *c, const isz *sc, const void *a, const isz *sa, const void *b,
+                    const isz *sb) {
+  usz total = 1;
+  for (usz i = 0; i < ndim; ++i) total *= shape[i];
+  for (usz lin = 0; lin < total; ++lin) {
+    usz rem = lin;
+    isz oc = 0, oa = 0, ob = 0;
+    for (usz d = ndim; d-- > 0;) {
+      const usz k = rem % shape[d];
+      rem /= shape[d];
+      oc += (isz)k * sc[d];
+      oa += (isz)k * sa[d];
+      ob += (isz)k * sb[d];
+    }
+    if (dt == OPS_DT_F16) *at((f16 *)c, oc) = (f16)((float)*at((const f16 *)a, oa) + (float)*at((const f16 *)b, ob));
+    else if (dt == OPS_DT_F32) *at((float *)c, oc) = *at((const float *)a, oa) + *at((const float *)b, ob);
+    else if (dt == OPS_DT_F64) *at((double *)c, oc) = *at((const double *)a, oa) + *at((const double *)b, ob);
+    else return OPS_TYPE_NOT_SUPPORT;
+  }
+  return 0;
+}
+
+// add_rows — add_rows/common_cpu/mod.rs:127-148: dst[b, m, :] += src[idx[b, m], :]; idx u32 or u64.
+ORC_API int orc_add_rows(uint32_t dt, uint32_t dt_idx, usz batch, usz m, usz n, usz k, void *dst, isz bsd, isz msd, isz nsd,
+                         const void *src, isz kss, isz nss, const void *idx, isz bsi, isz msi) {
+  for (usz b = 0; b < batch; ++b)
+    for (usz r = 0; r < m; ++r) {
+      const isz io = (isz)b * bsi + (isz)r * msi;
+      const usz id = dt_idx == OPS_DT_U32 ? (usz)*at((const uint32_t *)idx, io) : (usz)*at((const uint64_t *)idx, io);
+      if (id >= k) return OPS_ARGS_NOT_SUPPORT;  // the crate asserts
+      for (usz j = 0; j < n; ++j) {
+        const isz od = (isz)b * bsd + (isz)r * msd + (isz)j * nsd, os = (isz)id * kss + (isz)j * nss;
+        if (dt == OPS_DT_F16) *at((f16 *)dst, od) = (f16)((float)*at((f16 *)dst, od) + (float)*at((const f16 *)src, os));
+        else if (dt == OPS_DT_F32) *at((float *)dst, od) += *at((const float *)src, os);
+        else if (dt == OPS_DT_F64) *at((double *)dst, od) += *at((const double *)src, os);
+        else return OPS_TYPE_NOT_SUPPORT;
+      }
+    }
+  return 0;
+}

@@ -175,6 +175,20 @@ def broadcast(bufs, root):
     return bufs
 
 
+def add(c, a, b):
+    _chk(lib().orc_add(DT[c.dtype], _sz(c.ndim), _arr_sz(c.shape), _p(c), _arr_isz(c.strides), _p(a), _arr_isz(a.strides), _p(b),
+                       _arr_isz(b.strides)))
+    return c
+
+
+def add_rows(dst, src, idx):
+    batch, m, n = dst.shape
+    _chk(lib().orc_add_rows(DT[dst.dtype], DT[idx.dtype], _sz(batch), _sz(m), _sz(n), _sz(src.shape[0]), _p(dst), _isz(dst.strides[0]),
+                            _isz(dst.strides[1]), _isz(dst.strides[2]), _p(src), _isz(src.strides[0]), _isz(src.strides[1]), _p(idx),
+                            _isz(idx.strides[0]), _isz(idx.strides[1])))
+    return dst
+
+
 def decoder_layer(x, pos, shards, cfg):
     """The decoder-layer chain on the oracle operators (what a caller of the reference's common_cpu operators computes).
 

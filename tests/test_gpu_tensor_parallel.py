@@ -70,6 +70,13 @@ def _rank_main(rank, world, port, out_dir):
         results[f"ar_{T}_auto"] = dst.cpu().numpy()
         assert torch.equal(src.cpu(), torch.from_numpy(part))
     assert comm.p2p_status() == 0
+    # broadcast from the last rank (bytes), in place on the root and out of place elsewhere
+    bc = pkg.Broadcast(comm)
+    payload = torch.full((1000,), rank + 1, dtype=torch.int32, device=dev)
+    recv = torch.zeros_like(payload)
+    bc.launch(pkg.BroadcastArgs.of(recv, payload, world - 1))
+    torch.cuda.synchronize()
+    results["broadcast"] = recv.cpu().numpy()
     # tensor-parallel layer
     cfg = layer_mod.LayerConfig(**CFG)
     w = {k: torch.from_numpy(v).to(dev) for k, v in layer_mod.shard_weights(_weights(synth), rank, world, cfg).items()}
@@ -109,6 +116,8 @@ def test_all_reduce_and_tp_layer(tmp_path, orc, synth, world):
             assert float(np.abs(outs[0].astype(np.float32) - ref.astype(np.float32)).max()) <= 1e-2, (T, name)
             if name in ("one_shot", "two_shot"):
                 np.testing.assert_array_equal(outs[0].view(np.uint16), acc.astype(np.float16).view(np.uint16))
+    for r in range(world):
+        assert (res[r]["broadcast"] == world).all()
     layer = importlib.import_module(graft.PKG_NAME + ".layer")
     cfg = layer.LayerConfig(**CFG)
     x = synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)
