@@ -240,6 +240,18 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist):
     rr = pkg.Rearrange(idx)
     rargs = [pkg.RearrangeArgs.of(c[:, 2048:, :], k) for c in caches]
     out["config2_kv_cache_write"] = hbm(timeit(lambda i: rr.launch(rargs[i % 10]), 40), 2 * nkvh * seq * dh * 2)
+    # ---- decode step of attention_kv_cached: 1 new token against a 4096-token cache, 32/8 heads (split-KV kernel) ----
+    kc = [randn(nkvh, 4096, dh) for _ in range(8)]
+    vc = [randn(nkvh, 4096, dh) for _ in range(8)]
+    q1, o1 = randn(nh, 1, dh), torch.empty(nh, 1, dh, dtype=f16, device=device)
+    att.set_algo(pkg.ATTENTION_FUSED)
+    dargs = [pkg.AttentionArgs.of(q1, kc[i], vc[i], o1) for i in range(8)]
+    out["decode_attention_seq1_att4096"] = hbm(timeit(lambda i: att.launch(dargs[i % 8], ws), 32), 2 * nkvh * 4096 * dh * 2)
+    # ---- residual add over [4096, 4096] ----
+    ad = pkg.Add(idx)
+    xa, xb, xc = [randn(4096, 4096) for _ in range(4)], [randn(4096, 4096) for _ in range(4)], torch.empty(4096, 4096, dtype=f16, device=device)
+    adds = [pkg.AddArgs.of(xc, xa[i], xb[i]) for i in range(4)]
+    out["add_4096x4096"] = hbm(timeit(lambda i: ad.launch(adds[i % 4]), 20), 3 * 4096 * 4096 * 2)
     # ---- config 5: random_sample over 64 x 128256 logits ----
     rows, n = 64, 128256
     logits = [randn(rows, n, std=3.0) for _ in range(10)]

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   const int k_begin = split * a.keys_per_split, k_end = min(a.att, k_begin + a.keys_per_split);
   const __half *kbase = a.k + (long long)kvh * a.k_sh + li * 8;
   const __half *vbase = a.v + (long long)kvh * a.v_sh + li * 8;
-#pragma unroll 2
+#pragma unroll 4
   for (int kb = k_begin + warp * KPW; kb < k_end; kb += GROUPS) {  // warp-uniform trip count: the shuffles need every lane
     const int key = kb + sub;
     const bool valid = key < k_end;
@@ -159,23 +159,45 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   if (!s_last) return;
   __threadfence();
   if (threadIdx.x == 0) a.tickets[kvh] = 0;  // ready for the next launch
-  // last CTA of this kv head: merge the splits in split order
+  // last CTA of this kv head: merge the splits in split order.  First the per-split weights 2^(m_s - m) and the
+  // denominators (one thread per (row, split) then per row), then every output element as an independent dot product.
+  __shared__ float w_s[ROWS][DEC_MAX_SPLITS];
+  __shared__ float den_s[ROWS];
   const float *pall = a.partial + ((long long)kvh * a.splits) * ROWS * (DH + 2);
+  for (int i = threadIdx.x; i < ROWS * a.splits; i += DEC_THREADS) {
+    const int r = i / a.splits, sp = i - r * a.splits;
+    w_s[r][sp] = __ldcg(pall + ((long long)sp * ROWS + r) * (DH + 2));  // m of this split, turned into a weight below
+  }
+  __syncthreads();
+  if (threadIdx.x < ROWS) {
+    const int r = threadIdx.x;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < a.splits; ++sp) mm = fmaxf(mm, w_s[r][sp]);
+    float den = 0.f;
+    for (int sp = 0; sp < a.splits; ++sp) {
+      const float ms = w_s[r][sp];
+      const float w = ms == -INFINITY ? 0.f : ex2f(ms - mm);
+      w_s[r][sp] = w;
+      den = fmaf(__ldcg(pall + ((long long)sp * ROWS + r) * (DH + 2) + 1), w, den);
+    }
+    den_s[r] = den;
+  }
+  __syncthreads();
   for (int i = threadIdx.x; i < a.rows * DH; i += DEC_THREADS) {
     const int r = i / DH, c = i - r * DH;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < a.splits; ++sp) mm = fmaxf(mm, __ldcg(pall + ((long long)sp * ROWS + r) * (DH + 2)));
-    float num = 0.f, den = 0.f;
-    for (int sp = 0; sp < a.splits; ++sp) {
-      const float *pr = pall + ((long long)sp * ROWS + r) * (DH + 2);
-      const float ms = __ldcg(pr);
-      if (ms == -INFINITY) continue;
-      const float w = ex2f(ms - mm);
-      den = fmaf(__ldcg(pr + 1), w, den);
-      num = fmaf(__ldcg(pr + 2 + c), w, num);
+    const float *col = pall + (long long)r * (DH + 2) + 2 + c;
+    float num = 0.f;
+    int sp = 0;
+    for (; sp + 8 <= a.splits; sp += 8) {  // eight loads in flight
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
     }
+    for (; sp < a.splits; ++sp) num = fmaf(__ldcg(col + (long long)sp * ROWS * (DH + 2)), w_s[r][sp], num);
     const int gi = r / a.seq, si = r - gi * a.seq;
-    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + c] = __float2half_rn(num / den);
+    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + c] = __float2half_rn(num / den_s[r]);
   }
 }
 
@@ -217,9 +239,9 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.rows = g.group * g.seq;
   g.causal = a->mask == OPS_MASK_CAUSAL;
   const int row_slots = g.rows <= 4 ? 4 : 8;
-  // enough CTAs for every SM to hold a few, at least 64 keys each, and partials that fit the scratch buffer
-  usz splits = (4 * (usz)base.sm_count + nkvh - 1) / nkvh;
-  splits = std::min<usz>(splits, (att + 63) / 64);
+  // about two CTAs per SM, at least 128 keys each, and partials that fit the scratch buffer
+  usz splits = (2 * (usz)base.sm_count + nkvh - 1) / nkvh;
+  splits = std::min<usz>(splits, (att + 127) / 128);
   splits = std::min<usz>(splits, DEC_MAX_SPLITS);
   const usz per_split = nkvh * (usz)row_slots * (dh + 2) * sizeof(float);
   splits = std::min<usz>(splits, attention_decode_scratch_bytes() / per_split);
