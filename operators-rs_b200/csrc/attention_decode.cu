@@ -161,12 +161,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   if (threadIdx.x == 0) a.tickets[kvh] = 0;  // ready for the next launch
   // last CTA of this kv head: merge the splits in split order.  First the per-split weights 2^(m_s - m) and the
   // denominators (one thread per (row, split) then per row), then every output element as an independent dot product.
-  __shared__ float w_s[ROWS][DEC_MAX_SPLITS];
+  __shared__ float w_s[ROWS][DEC_MAX_SPLITS], l_s[ROWS][DEC_MAX_SPLITS];
   __shared__ float den_s[ROWS];
   const float *pall = a.partial + ((long long)kvh * a.splits) * ROWS * (DH + 2);
   for (int i = threadIdx.x; i < ROWS * a.splits; i += DEC_THREADS) {
     const int r = i / a.splits, sp = i - r * a.splits;
-    w_s[r][sp] = __ldcg(pall + ((long long)sp * ROWS + r) * (DH + 2));  // m of this split, turned into a weight below
+    const float *pr = pall + ((long long)sp * ROWS + r) * (DH + 2);
+    w_s[r][sp] = __ldcg(pr);  // m of this split, turned into a weight below
+    l_s[r][sp] = __ldcg(pr + 1);
   }
   __syncthreads();
   if (threadIdx.x < ROWS) {
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
       const float ms = w_s[r][sp];
       const float w = ms == -INFINITY ? 0.f : ex2f(ms - mm);
       w_s[r][sp] = w;
-      den = fmaf(__ldcg(pall + ((long long)sp * ROWS + r) * (DH + 2) + 1), w, den);
+      den = fmaf(l_s[r][sp], w, den);
     }
     den_s[r] = den;
   }
