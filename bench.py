@@ -296,7 +296,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-operator measurements of configs 1, 2, 4 and 5")
-    ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot"])
+    ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
     ap.add_argument("--overlap-chunks", type=int, default=1, help="token chunks of the row-parallel projections whose all_reduce overlaps the next chunk's GEMM")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -326,13 +326,13 @@ def main():
         ids = [pkg.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         comm = pkg.Comm(local_rank, rank, world, ids[0])
-        if args.all_reduce in ("auto", "one_shot", "two_shot"):
+        if args.all_reduce in ("auto", "one_shot", "two_shot", "fused"):
             handle = comm.p2p_export(args.tokens * CFG["d"] * 2)
             handles = [None] * world
             dist.all_gather_object(handles, handle)
             comm.p2p_attach(handles)
     algo = {"auto": pkg.ALL_REDUCE_AUTO, "nccl": pkg.ALL_REDUCE_NCCL, "one_shot": pkg.ALL_REDUCE_P2P_ONE_SHOT,
-            "two_shot": pkg.ALL_REDUCE_P2P_TWO_SHOT}[args.all_reduce]
+            "two_shot": pkg.ALL_REDUCE_P2P_TWO_SHOT, "fused": pkg.ALL_REDUCE_AUTO}[args.all_reduce]
 
     cfg = layer_mod.LayerConfig(**CFG)
     T = args.tokens
@@ -341,7 +341,8 @@ def main():
     if tp > 1:
         del full
         torch.cuda.empty_cache()
-    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks)
+    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks,
+                                   fused_all_reduce=args.all_reduce == "fused")
     g = torch.Generator(device=device).manual_seed(SEED + 7)
     x0 = torch.randn(T, CFG["d"], generator=g, device=device, dtype=torch.float32).half()
     x = torch.empty_like(x0)

@@ -338,6 +338,13 @@ int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args *args, s
 int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream);
 void ops_all_reduce_destroy(ops_all_reduce *op);
 
+/* No counterpart in the crate (it chains mat_mul and all_reduce as two operators): C <- beta*C + alpha*A*B followed by
+ * the f16 sum all_reduce of C over the group of `node`, as ONE kernel — finished tiles cross NVLink while the tensor
+ * cores work on the remaining ones.  Needs ops_comm_p2p_attach with a staging region of at least m*n*2 bytes, f16
+ * operands the tensor-core path accepts and a single dense row-major C.  beta applies to this rank's partial (fold the
+ * residual in on exactly one rank).  Every rank of the group must call it with the same shapes. */
+int ops_mat_mul_all_reduce_launch(const ops_mat_mul *op, ops_comm *node, const ops_mat_mul_args *args, void *stream);
+
 /* =============================================================================================
  * Operators on either side of the decoder layer (the crate's operators a caller chains around it).
  * ============================================================================================= */

@@ -550,6 +550,12 @@ class Rearrange(Operator):
 class MatMul(Operator):
     NAME = "mat_mul"
 
+    def launch_all_reduce(self, comm, args, queue_alloc=None):
+        """ops_mat_mul_all_reduce_launch: C = beta*C + alpha*A*B summed over the ranks of `comm`, one kernel."""
+        qa = queue_alloc or TorchQueueAlloc()
+        self._last_args = args
+        _check(lib().ops_mat_mul_all_reduce_launch(self._h, comm._h, args.byref(), ctypes.c_void_p(qa.queue())), True)
+
     def status(self):
         return lib().ops_mat_mul_status(self._h)
 
@@ -695,5 +701,5 @@ EXPORTS = [
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
-    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo", "ops_add_rows_status",
+    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
 ]

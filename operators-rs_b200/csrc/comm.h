@@ -1,0 +1,92 @@
+// comm.h — the topology node (`ops_comm`) and the layout of the peer-mapped staging buffer, shared by the
+// all_reduce / broadcast operators and the GEMM that reduces its own output across ranks.
+#pragma once
+#include <nccl.h>
+
+#include "common.h"
+#include "device_utils.cuh"
+
+namespace ops {
+
+constexpr int MAX_RANKS = 8;
+constexpr int P2P_MAX_CTAS = 256;
+constexpr int P2P_MAX_TILE_FLAGS = 16384;  // (tile, 32-row quarter) flags of the GEMM + all_reduce kernel: up to 4096 tiles
+constexpr unsigned long long P2P_WAIT_LIMIT_NS = 1000000000ull;  // 1 s
+
+// ------------------------------------------------------------------------------------------------
+// peer-to-peer state
+// ------------------------------------------------------------------------------------------------
+// Staging buffer of one rank: [flags | in(parity 0) | in(parity 1) | out(parity 0) | out(parity 1)]
+struct P2PFlags {
+  unsigned int ready[MAX_RANKS][P2P_MAX_CTAS];   // ready[q][b]: epoch up to which rank q's CTA b has staged its input
+  unsigned int reduced[MAX_RANKS][P2P_MAX_CTAS]; // reduced[q][b]: epoch up to which rank q's CTA b has published its reduced slice
+  // GEMM + all_reduce kernel: tile_ready[q][f] = epoch at which rank q stored its partial of (tile, quarter) f in its "in"
+  // region (written into the OWNER's copy of this struct); tile_done[f] = epoch at which the owner has pushed the reduced
+  // (tile, quarter) into this rank's "out" region
+  unsigned int tile_ready[MAX_RANKS][P2P_MAX_TILE_FLAGS];
+  unsigned int tile_done[P2P_MAX_TILE_FLAGS];
+};
+
+struct P2PHandleBlob {  // what ops_comm_p2p_export ships (<= OPS_COMM_P2P_HANDLE_BYTES)
+  cudaIpcMemHandle_t mem;
+  unsigned long long region_bytes;
+  int rank;
+  int valid;
+};
+static_assert(sizeof(P2PHandleBlob) <= OPS_COMM_P2P_HANDLE_BYTES, "handle blob too large");
+
+struct P2PKernelArgs {
+  char *peers[MAX_RANKS];  // peers[q]: base of rank q's staging buffer as mapped here (own buffer for q == rank)
+  unsigned long long region_bytes;
+  int rank, size;
+  unsigned int epoch;
+  int *status;
+};
+
+}  // namespace ops
+
+struct ops_comm {
+  int device;
+  int rank, size;
+  ncclComm_t nccl;
+  bool has_nccl;
+  // p2p
+  char *staging;               // own buffer (cudaMalloc)
+  size_t staging_bytes;        // total allocation
+  size_t region_bytes;         // bytes of each of the four data regions
+  char *peers[ops::MAX_RANKS];
+  bool p2p_ready;
+  unsigned int epoch;
+  int *status_dev;
+  int sm_count;
+};
+
+namespace ops {
+
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void *p) {  // system-scope relaxed load: never served from a stale L1 line
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long p2p_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ char *region_in(char *base, unsigned long long region, unsigned int parity) {
+  return base + sizeof(P2PFlags) + (unsigned long long)parity * region;
+}
+__device__ __forceinline__ char *region_out(char *base, unsigned long long region, unsigned int parity) {
+  return base + sizeof(P2PFlags) + (2ull + parity) * region;
+}
+
+}  // namespace ops

@@ -24,6 +24,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "comm.h"
 #include "common.h"
 #include "device_utils.cuh"
 #include "internal.h"
@@ -40,6 +41,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;                       // 64 f16 = one 128-byte swizzle row
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_FUSED_THREADS = 320;  // + 4 warps that reduce finished tiles across ranks while the GEMM goes on
 constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
 constexpr int GEMM_SPLIT_MAX_UNITS = 160;          // CTAs that may hold a K-slice partial (>= SM count)
@@ -64,6 +66,19 @@ struct GemmKernelArgs {
   int kb_per_slice;
   float *split_ws;         // [grid][128][BN] f32
   unsigned int *split_tickets;  // [split_r][4] arrivals per 32-row quarter, self-resetting
+};
+
+// GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
+// projections).  Every rank writes its partial tile into its peer-mapped "in" region and flags it at the tile's owner
+// (rank = tile mod p); four extra warps per CTA sum the owner's tiles from all ranks with ordinary NVLink loads as soon as
+// they are flagged, push the result into every rank's "out" region and flag that; finally each CTA moves its share of
+// finished tiles from "out" to the caller's C.  The NVLink traffic of a two-shot all_reduce, hidden behind the MMAs.
+struct FusedArArgs {
+  char *peers[MAX_RANKS];
+  unsigned long long region_bytes;
+  int rank, size;
+  unsigned int epoch;
+  int *status;
 };
 
 struct GemmWork {
@@ -100,10 +115,10 @@ template <int BN> struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int BN, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ GemmKernelArgs g) {
+                            const __grid_constant__ GemmKernelArgs g, const __grid_constant__ FusedArArgs fa) {
   typedef GemmCfg<BN> Cfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -223,7 +238,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, +32) belong to this warp
     int acc = 0;
@@ -240,12 +255,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       if (!(ok = mbar_wait(tmem_full_bar(acc), acc_phase, g.status, 4))) break;
       tc_fence_after();
       __half *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
+      // fused all_reduce: the partial goes to this rank's peer-visible "in" region (dense rows of n), C is only read
+      __half *wrow = drow;
+      if constexpr (FUSED) wrow = reinterpret_cast<__half *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa.epoch & 1u)) + (long long)row * g.n;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       // K-slice of a remainder tile: park the f32 partial; the last of the tile's slices to arrive (per 32-row quarter)
       // adds all of them up in slice order and takes over as if it had computed the whole tile
       bool finish = true;
       float *part_row = nullptr;
-      if (w.slice >= 0) {
+      if (!FUSED && w.slice >= 0) {
         const int tile_r = (int)(t - g.normal_tiles);
         part_row = g.split_ws + ((long long)blockIdx.x * GEMM_BM + quarter * 32 + lane) * BN;
 #pragma unroll 1
@@ -273,7 +291,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll 1
       for (int c = 0; c < BN && finish; c += 32) {
         uint32_t v[32];
-        if (w.slice < 0) {
+        if (FUSED || w.slice < 0) {
           tmem_ld_32x32(taddr + (uint32_t)c, v);
           tmem_wait_ld();
         } else {
@@ -325,7 +343,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(old.h[e])), val);
                 out.h[e] = __float2half_rn(val);
               }
-              st_global_16(dp, out.u);
+              st_global_16(wrow + col, out.u);
             } else {
               for (int e = 0; e < 8 && col + e < g.n; ++e) {
                 float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
@@ -339,9 +357,93 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if constexpr (FUSED) {  // tell the tile's owner that this rank's quarter of the partial is in place
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          P2PFlags *owner = reinterpret_cast<P2PFlags *>(fa.peers[(int)(t % fa.size)]);
+          st_release_sys(&owner->tile_ready[fa.rank][t * 4 + quarter], fa.epoch);
+        }
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
+      }
+    }
+  } else if constexpr (FUSED) {
+    // ------------------------------------------------------------------ cross-rank reduction (warps 6..9)
+    const int cq = warp & 3;  // 32-row quarter of a tile
+    const unsigned int parity = fa.epoch & 1u;
+    P2PFlags *mine = reinterpret_cast<P2PFlags *>(fa.peers[fa.rank]);
+    constexpr int VPR = BN / 8;       // 16-byte vectors per tile row
+    constexpr int RPP = 32 / VPR;     // tile rows per warp pass
+    const int sub = lane / VPR, vec = lane % VPR;
+    bool ok = true;
+    auto wait_flag = [&](const unsigned int *flag, int code) -> bool {
+      const unsigned long long t0 = p2p_now();
+      while ((int)(ld_acquire_sys(flag) - fa.epoch) < 0) {
+        if (p2p_now() - t0 > P2P_WAIT_LIMIT_NS) {
+          atomicCAS(fa.status, 0, code);
+          return false;
+        }
+      }
+      return true;
+    };
+    // phase A: the tiles this rank owns (t = rank + p * j), spread over the CTAs in the order the GEMM produces them
+    const long long owned = num_tiles > fa.rank ? (num_tiles - fa.rank + fa.size - 1) / fa.size : 0;
+    for (long long j = blockIdx.x; j < owned && ok; j += gridDim.x) {
+      const long long t = fa.rank + (long long)fa.size * j;
+      const int f = (int)(t * 4 + cq);
+      bool mine_ok = true;
+      if (lane < fa.size) mine_ok = wait_flag(&mine->tile_ready[lane][f], 40 + lane);
+      ok = __all_sync(0xffffffffu, mine_ok);
+      if (!ok) break;
+      const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
+      const int col = tn * BN + vec * 8;
+#pragma unroll 2
+      for (int i = 0; i < 32; i += RPP) {
+        const int row = tm * GEMM_BM + cq * 32 + i + sub;
+        if (row < g.m && col < g.n) {
+          const long long off = ((long long)row * g.n + col) * 2;
+          uint4 raw[MAX_RANKS];
+#pragma unroll
+          for (int q = 0; q < MAX_RANKS; ++q)
+            if (q < fa.size) raw[q] = ld_peer_16(region_in(fa.peers[q], fa.region_bytes, parity) + off);
+          float accv[8] = {};
+#pragma unroll
+          for (int q = 0; q < MAX_RANKS; ++q)
+            if (q < fa.size) {
+              const __half *h = reinterpret_cast<const __half *>(&raw[q]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) accv[e] += __half2float(h[e]);
+            }
+          Pack8 out;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(accv[e]);
+#pragma unroll
+          for (int q = 0; q < MAX_RANKS; ++q)
+            if (q < fa.size) *reinterpret_cast<uint4 *>(region_out(fa.peers[q], fa.region_bytes, parity) + off) = out.u;
+        }
+      }
+      __threadfence_system();
+      __syncwarp();
+      if (lane < fa.size) st_release_sys(&reinterpret_cast<P2PFlags *>(fa.peers[lane])->tile_done[f], fa.epoch);
+    }
+    // phase B: every rank needs every tile: move this CTA's share from the "out" region to C
+    for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int f = (int)(t * 4 + cq);
+      bool mine_ok = true;
+      if (lane == 0) mine_ok = wait_flag(&mine->tile_done[f], 60);
+      ok = __all_sync(0xffffffffu, mine_ok);
+      if (!ok) break;
+      const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
+      const int col = tn * BN + vec * 8;
+      const char *outp = region_out(fa.peers[fa.rank], fa.region_bytes, parity);
+#pragma unroll 4
+      for (int i = 0; i < 32; i += RPP) {
+        const int row = tm * GEMM_BM + cq * 32 + i + sub;
+        if (row < g.m && col < g.n)
+          st_global_16(g.d + (long long)row * g.ldd + col, ld_peer_16(outp + ((long long)row * g.n + col) * 2));
       }
     }
   }
@@ -531,7 +633,7 @@ static bool tma_ok(const void *ptr, usz outer, usz batch, isz outer_stride_el, i
 
 struct GemmState {
   int *status_dev = nullptr;
-  bool attr_set[2] = {false, false};
+  bool attr_set[4] = {false, false, false, false};
   // scratch of the remainder-wave K split, owned by the handle (launch never allocates): one 128 x 256 f32 partial per
   // CTA and the arrival counters, which every launch leaves at zero again.  One stream at a time per handle.
   float *split_ws = nullptr;
@@ -551,7 +653,7 @@ namespace ops {
 
 template <int BN>
 static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn, bool b_mn, usz eff_batch_a, usz eff_batch_b, float alpha,
-                          float beta, cudaStream_t s) {
+                          float beta, cudaStream_t s, ops_comm *comm = nullptr) {
   typedef GemmCfg<BN> Cfg;
   CUtensorMap ta, tb;
   bool ok;
@@ -616,19 +718,45 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
       }
     }
   }
-  const unsigned launch_grid = g.split_g > 1 ? (unsigned)op->base.sm_count : grid;
   ops_mat_mul *mop = const_cast<ops_mat_mul *>(op);
+  FusedArArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  if (comm) {
+    // fused all_reduce: whole tiles only (no K split), every CTA resident, flags for every (tile, quarter)
+    g.normal_tiles = tiles;
+    g.split_g = 1;
+    g.split_r = 0;
+    for (int q = 0; q < MAX_RANKS; ++q) fa.peers[q] = q < comm->size ? comm->peers[q] : nullptr;
+    fa.region_bytes = comm->region_bytes;
+    fa.rank = comm->rank;
+    fa.size = comm->size;
+    fa.epoch = ++comm->epoch;
+    fa.status = comm->status_dev;
+    const int slot = BN == 256 ? 2 : 3;
+    if (!mop->st.attr_set[slot]) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+      mop->st.attr_set[slot] = true;
+    }
+    gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
+    return check_launch("mat_mul+all_reduce(tcgen05)");
+  }
+  const unsigned launch_grid = g.split_g > 1 ? (unsigned)op->base.sm_count : grid;
   const int slot = BN == 256 ? 0 : 1;
   if (!mop->st.attr_set[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     mop->st.attr_set[slot] = true;
   }
-  gemm_f16_tcgen05_kernel<BN><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g);
+  gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
   return check_launch("mat_mul(tcgen05)");
 }
 
-int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s) {
+int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s, ops_comm *comm);
+
+int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s) { return mat_mul_enqueue_impl(op, args, s, nullptr); }
+
+int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s, ops_comm *comm) {
   GemmProblem p;
   OPS_TRY(solve_layout(args, &p));
   if (dyn(args->alpha) || dyn(args->beta)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: alpha and beta must be static at launch");
@@ -652,11 +780,22 @@ int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStr
     const bool a_ok = a_mn ? (p.a.rs == 1 && tma_ok(p.a_ptr, p.k, ea, p.a.cs, p.a.stride)) : tma_ok(p.a_ptr, p.m, ea, p.a.rs, p.a.stride);
     const bool b_ok = b_mn ? (p.b.cs == 1 && tma_ok(p.b_ptr, p.k, eb, p.b.rs, p.b.stride)) : tma_ok(p.b_ptr, p.n, eb, p.b.cs, p.b.stride);
     const bool d_ok = p.d.rs >= 0 && p.d.stride >= 0;
+    if (comm) {
+      // what the fused kernel needs on top of the tensor-core path: one matrix, dense 16-byte rows, a staging region that
+      // holds the whole partial, a flag per (tile, quarter), one CTA per SM resident
+      const long long tiles = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + (p.n > 128 ? 256 : 128) - 1) / (p.n > 128 ? 256 : 128));
+      const bool fused_ok = a_ok && b_ok && d_ok && encode_tiled_fn() && p.batch == 1 && p.n % 8 == 0 && p.d.rs % 8 == 0 && aligned(p.d_ptr, 16) &&
+                            comm->p2p_ready && p.m * p.n * 2 <= comm->region_bytes && tiles * 4 <= P2P_MAX_TILE_FLAGS && comm->device == op->base.device;
+      if (!fused_ok) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: needs f16 TMA-describable operands, one dense matrix whose partial fits the attached staging region");
+      if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
+      return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
+    }
     if (a_ok && b_ok && d_ok && encode_tiled_fn()) {
       if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
       return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
     }
   }
+  if (comm) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: f16 operands with k > 0 expected");
   SimtArgs g;
   g.c = p.d_ptr;
   g.a = p.a_ptr;
@@ -730,4 +869,13 @@ OPS_API int ops_mat_mul_launch(const ops_mat_mul *op, const ops_mat_mul_args *ar
   (void)ws;
   (void)ws_len;
   return mat_mul_enqueue(op, args, (cudaStream_t)stream);
+}
+
+// mat_mul immediately followed by all_reduce(sum) of its result over the group of `node`, as ONE kernel: the transfer of
+// finished tiles overlaps the tensor-core work on the remaining ones.  On return of the kernel C holds the reduced
+// result on every rank.  beta applies to this rank's partial only (fold a residual in on exactly one rank).
+OPS_API int ops_mat_mul_all_reduce_launch(const ops_mat_mul *op, ops_comm *node, const ops_mat_mul_args *args, void *stream) {
+  if (!node) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: null communicator");
+  if (node->size == 1) return mat_mul_enqueue(op, args, (cudaStream_t)stream);
+  return mat_mul_enqueue_impl(op, args, (cudaStream_t)stream, node);
 }

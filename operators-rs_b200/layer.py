@@ -78,9 +78,11 @@ class DecoderLayer:
     STEPS = ("rms_norm_1", "mat_mul_qkv", "rope", "attention", "mat_mul_o", "all_reduce_1", "rms_norm_2", "mat_mul_gate_up",
              "swiglu", "mat_mul_down", "all_reduce_2")
 
-    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1):
+    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1, fused_all_reduce=False):
         import torch
         self.overlap_chunks = max(1, int(overlap_chunks))
+        self.fused_all_reduce = bool(fused_all_reduce) and tp > 1  # row-parallel GEMM and its all_reduce as one kernel
+        self.comm = comm
         self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and self.overlap_chunks > 1) else None
         self.cfg, self.w, self.device, self.tp, self.rank = cfg, weights, device, tp, rank
         idx = device.index if device.index is not None else 0
@@ -141,6 +143,11 @@ class DecoderLayer:
         # residual: their partial goes to scratch, which holds the stream from here on.
         out, beta = (x, 1.0) if first else (self.scratch[:T], 0.0)
         chunks = self.overlap_chunks if (self.tp > 1 and T >= 256 * self.overlap_chunks) else 1
+        if self.fused_all_reduce:
+            self.mat_mul.launch_all_reduce(self.comm, MatMulArgs.of(out, beta, a, w, 1.0))
+            mark(mm_name)
+            mark(ar_name)
+            return out
         if chunks == 1:
             self.mat_mul.launch(MatMulArgs.of(out, beta, a, w, 1.0))
             mark(mm_name)

@@ -80,8 +80,26 @@ def _rank_main(rank, world, port, out_dir):
     # tensor-parallel layer
     cfg = layer_mod.LayerConfig(**CFG)
     w = {k: torch.from_numpy(v).to(dev) for k, v in layer_mod.shard_weights(_weights(synth), rank, world, cfg).items()}
-    for name, algo in (("nccl", pkg.ALL_REDUCE_NCCL), ("p2p", pkg.ALL_REDUCE_P2P_ONE_SHOT)):
-        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comm=comm, tp=world, rank=rank, all_reduce_algo=algo)
+    # mat_mul + all_reduce as one kernel against mat_mul followed by the one-shot kernel: same f16 partials, same f32 sum in
+    # rank order -> the same bits.  Twice (staging parity), with and without the residual folded in on rank 0.
+    mm = pkg.MatMul(rank)
+    a_part = torch.from_numpy(synth.normal(900 + rank, (320, 256), 1.0).astype(np.float16)).to(dev)
+    w_part = torch.from_numpy(synth.normal(950 + rank, (256, 1024), 0.05).astype(np.float16)).to(dev)
+    resid = torch.from_numpy(synth.normal(999, (320, 1024), 1.0).astype(np.float16)).to(dev)
+    op.set_algo(pkg.ALL_REDUCE_P2P_ONE_SHOT)
+    for rep in range(2):
+        beta = 1.0 if (rank == 0 and rep == 1) else 0.0
+        c_ref = resid.clone()
+        mm.launch(pkg.MatMulArgs.of(c_ref, beta, a_part, w_part, 1.0))
+        op.launch(pkg.AllReduceArgs.of(c_ref, c_ref))
+        c_fused = resid.clone()
+        mm.launch_all_reduce(comm, pkg.MatMulArgs.of(c_fused, beta, a_part, w_part, 1.0))
+        torch.cuda.synchronize()
+        assert mm.status() == 0 and comm.p2p_status() == 0
+        assert torch.equal(c_ref, c_fused), f"fused mat_mul+all_reduce differs (rep {rep})"
+    results["fused_gemm_ar"] = c_fused.cpu().numpy()
+    for name, algo, fused in (("nccl", pkg.ALL_REDUCE_NCCL, False), ("p2p", pkg.ALL_REDUCE_P2P_ONE_SHOT, False), ("fused", pkg.ALL_REDUCE_AUTO, True)):
+        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comm=comm, tp=world, rank=rank, all_reduce_algo=algo, fused_all_reduce=fused)
         x = torch.from_numpy(synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)).to(dev)
         pos = torch.arange(T_LAYER, dtype=torch.int32, device=dev).view(torch.uint32)
         out = lay.forward(x, pos)
@@ -122,7 +140,7 @@ def test_all_reduce_and_tp_layer(tmp_path, orc, synth, world):
     cfg = layer.LayerConfig(**CFG)
     x = synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)
     emu = orc.decoder_layer(x, np.arange(T_LAYER, dtype=np.uint32), [layer.shard_weights(_weights(synth), r, world, cfg) for r in range(world)], CFG)
-    for name in ("nccl", "p2p"):
+    for name in ("nccl", "p2p", "fused"):
         outs = [res[r][f"layer_{name}"] for r in range(world)]
         for o in outs[1:]:
             np.testing.assert_array_equal(o.view(np.uint16), outs[0].view(np.uint16))
