@@ -21,8 +21,8 @@ struct P2PFlags {
   unsigned int ready[MAX_RANKS][P2P_MAX_CTAS];   // ready[q][b]: epoch up to which rank q's CTA b has staged its input
   unsigned int reduced[MAX_RANKS][P2P_MAX_CTAS]; // reduced[q][b]: epoch up to which rank q's CTA b has published its reduced slice
   // GEMM + all_reduce kernel: tile_ready[q][f] = epoch at which rank q stored its partial of (tile, quarter) f in its "in"
-  // region (written into the OWNER's copy of this struct); tile_done[f] = epoch at which the owner has pushed the reduced
-  // (tile, quarter) into this rank's "out" region
+  // region (written into the OWNER's copy of this struct); tile_done[8 * tile + w] = epoch at which the owner has pushed rows
+  // [16w, 16w+16) of the reduced tile into this rank's "out" region
   unsigned int tile_ready[MAX_RANKS][P2P_MAX_TILE_FLAGS];
   unsigned int tile_done[P2P_MAX_TILE_FLAGS];
 };

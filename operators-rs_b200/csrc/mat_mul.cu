@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 #include <vector>
 
@@ -41,7 +42,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;                       // 64 f16 = one 128-byte swizzle row
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_FUSED_THREADS = 320;  // + 4 warps that reduce finished tiles across ranks while the GEMM goes on
+constexpr int GEMM_FUSED_THREADS = 448;  // + 8 warps that reduce finished tiles across ranks while the GEMM goes on
 constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
 constexpr int GEMM_SPLIT_MAX_UNITS = 160;          // CTAs that may hold a K-slice partial (>= SM count)
@@ -70,8 +71,8 @@ struct GemmKernelArgs {
 
 // GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
 // projections).  Every rank writes its partial tile into its peer-mapped "in" region and flags it at the tile's owner
-// (rank = tile mod p); four extra warps per CTA sum the owner's tiles from all ranks with ordinary NVLink loads as soon as
-// they are flagged, push the result into every rank's "out" region and flag that; finally each CTA moves its share of
+// (rank = tile mod p); extra warps in every CTA sum the owner's tiles from all ranks with ordinary NVLink loads as soon as
+// they are flagged (eight extra warps, 16 tile rows each), push the result into every rank's "out" region and flag that; finally each CTA moves its share of
 // finished tiles from "out" to the caller's C.  The NVLink traffic of a two-shot all_reduce, hidden behind the MMAs.
 struct FusedArArgs {
   char *peers[MAX_RANKS];
@@ -371,8 +372,10 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       }
     }
   } else if constexpr (FUSED) {
-    // ------------------------------------------------------------------ cross-rank reduction (warps 6..9)
-    const int cq = warp & 3;  // 32-row quarter of a tile
+    // ------------------------------------------------------------------ cross-rank reduction (warps 6..13)
+    // Eight warps; warp c works on rows [16c, 16c+16) of a tile, i.e. half of the 32-row quarter c/2 whose flag it watches.
+    const int cw = warp - 6;
+    const int cq = cw >> 1;  // quarter whose flags gate these rows
     const unsigned int parity = fa.epoch & 1u;
     P2PFlags *mine = reinterpret_cast<P2PFlags *>(fa.peers[fa.rank]);
     constexpr int VPR = BN / 8;       // 16-byte vectors per tile row
@@ -389,6 +392,40 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       }
       return true;
     };
+    // rows row0, row0 + RPP, ... (NR of them) of one tile column block: all ranks' copies requested before the first is used
+    auto reduce_rows = [&](auto nr_tag, auto np_tag, int row0, int col) {
+      constexpr int NR = decltype(nr_tag)::value, NP = decltype(np_tag)::value;
+      uint4 raw[NR][NP];
+      long long off[NR];
+      bool live[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int row = row0 + r * RPP;
+        live[r] = row < g.m && col < g.n;
+        off[r] = ((long long)row * g.n + col) * 2;
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+          if (live[r] && q < fa.size) raw[r][q] = ld_peer_16(region_in(fa.peers[q], fa.region_bytes, parity) + off[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        if (!live[r]) continue;
+        float accv[8] = {};
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+          if (q < fa.size) {
+            const __half *h = reinterpret_cast<const __half *>(&raw[r][q]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) accv[e] += __half2float(h[e]);
+          }
+        Pack8 out;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(accv[e]);
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+          if (q < fa.size) *reinterpret_cast<uint4 *>(region_out(fa.peers[q], fa.region_bytes, parity) + off[r]) = out.u;
+      }
+    };
     // phase A: the tiles this rank owns (t = rank + p * j), spread over the CTAs in the order the GEMM produces them
     const long long owned = num_tiles > fa.rank ? (num_tiles - fa.rank + fa.size - 1) / fa.size : 0;
     for (long long j = blockIdx.x; j < owned && ok; j += gridDim.x) {
@@ -400,50 +437,38 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       if (!ok) break;
       const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
       const int col = tn * BN + vec * 8;
-#pragma unroll 2
-      for (int i = 0; i < 32; i += RPP) {
-        const int row = tm * GEMM_BM + cq * 32 + i + sub;
-        if (row < g.m && col < g.n) {
-          const long long off = ((long long)row * g.n + col) * 2;
-          uint4 raw[MAX_RANKS];
-#pragma unroll
-          for (int q = 0; q < MAX_RANKS; ++q)
-            if (q < fa.size) raw[q] = ld_peer_16(region_in(fa.peers[q], fa.region_bytes, parity) + off);
-          float accv[8] = {};
-#pragma unroll
-          for (int q = 0; q < MAX_RANKS; ++q)
-            if (q < fa.size) {
-              const __half *h = reinterpret_cast<const __half *>(&raw[q]);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) accv[e] += __half2float(h[e]);
-            }
-          Pack8 out;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(accv[e]);
-#pragma unroll
-          for (int q = 0; q < MAX_RANKS; ++q)
-            if (q < fa.size) *reinterpret_cast<uint4 *>(region_out(fa.peers[q], fa.region_bytes, parity) + off) = out.u;
-        }
+      const int rbase = tm * GEMM_BM + cw * 16 + sub;
+      if (fa.size <= 4) {
+        for (int i = 0; i < 16; i += 4 * RPP) reduce_rows(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{}, rbase + i, col);
+      } else {
+        for (int i = 0; i < 16; i += 2 * RPP) reduce_rows(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{}, rbase + i, col);
       }
       __threadfence_system();
       __syncwarp();
-      if (lane < fa.size) st_release_sys(&reinterpret_cast<P2PFlags *>(fa.peers[lane])->tile_done[f], fa.epoch);
+      // these 16 rows of the tile are final on every rank: flag them (per tile and warp, so that the warp that moves the
+      // same rows to C in phase B depends on nothing else)
+      if (lane < fa.size) st_release_sys(&reinterpret_cast<P2PFlags *>(fa.peers[lane])->tile_done[t * 8 + cw], fa.epoch);
     }
     // phase B: every rank needs every tile: move this CTA's share from the "out" region to C
     for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int f = (int)(t * 4 + cq);
       bool mine_ok = true;
-      if (lane == 0) mine_ok = wait_flag(&mine->tile_done[f], 60);
+      if (lane == 0) mine_ok = wait_flag(&mine->tile_done[t * 8 + cw], 60);
       ok = __all_sync(0xffffffffu, mine_ok);
       if (!ok) break;
       const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
       const int col = tn * BN + vec * 8;
       const char *outp = region_out(fa.peers[fa.rank], fa.region_bytes, parity);
-#pragma unroll 4
-      for (int i = 0; i < 32; i += RPP) {
-        const int row = tm * GEMM_BM + cq * 32 + i + sub;
-        if (row < g.m && col < g.n)
-          st_global_16(g.d + (long long)row * g.ldd + col, ld_peer_16(outp + ((long long)row * g.n + col) * 2));
+      const int rbase = tm * GEMM_BM + cw * 16 + sub;
+      uint4 buf[16 / RPP];
+#pragma unroll
+      for (int i = 0; i < 16 / RPP; ++i) {
+        const int row = rbase + i * RPP;
+        if (row < g.m && col < g.n) buf[i] = ld_peer_16(outp + ((long long)row * g.n + col) * 2);
+      }
+#pragma unroll
+      for (int i = 0; i < 16 / RPP; ++i) {
+        const int row = rbase + i * RPP;
+        if (row < g.m && col < g.n) st_global_16(g.d + (long long)row * g.ldd + col, buf[i]);
       }
     }
   }
@@ -785,7 +810,7 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
       // holds the whole partial, a flag per (tile, quarter), one CTA per SM resident
       const long long tiles = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + (p.n > 128 ? 256 : 128) - 1) / (p.n > 128 ? 256 : 128));
       const bool fused_ok = a_ok && b_ok && d_ok && encode_tiled_fn() && p.batch == 1 && p.n % 8 == 0 && p.d.rs % 8 == 0 && aligned(p.d_ptr, 16) &&
-                            comm->p2p_ready && p.m * p.n * 2 <= comm->region_bytes && tiles * 4 <= P2P_MAX_TILE_FLAGS && comm->device == op->base.device;
+                            comm->p2p_ready && p.m * p.n * 2 <= comm->region_bytes && tiles * 8 <= P2P_MAX_TILE_FLAGS && comm->device == op->base.device;
       if (!fused_ok) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: needs f16 TMA-describable operands, one dense matrix whose partial fits the attached staging region");
       if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
       return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
