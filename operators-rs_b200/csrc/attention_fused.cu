@@ -228,23 +228,44 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
     bool ok = true;
 
+    // Tensor-memory loads are issued one ahead of the arithmetic that consumes them (tcgen05.wait::ld waits for every
+    // load in flight, so the pattern is: wait, issue the next load, work on the previous one).
     auto accumulate_pv = [&](int i, float a) -> bool {
       const int b = i & 1;
       if (!mbar_wait(pv_full(b), (uint32_t)((i >> 1) & 1), g.status, 31)) return false;
       tc_fence_after();
       const uint32_t t = tmem_base + lane_addr + 256u + (uint32_t)(b * 128 + half * DHH);
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(t, va);
+      tmem_wait_ld();
+      if constexpr (DHH > 32) tmem_ld_32x32(t + 32u, vb);
 #pragma unroll
-      for (int c = 0; c < DHH; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t + (uint32_t)c, v);
+      for (int e = 0; e < 32; ++e) o[e] = fmaf(o[e], a, __uint_as_float(va[e]));
+      if constexpr (DHH > 32) {
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c + e] = fmaf(o[c + e], a, __uint_as_float(v[e]));
+        for (int e = 0; e < 32; ++e) o[32 + e] = fmaf(o[32 + e], a, __uint_as_float(vb[e]));
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pv_empty(b));
       return true;
+    };
+    // maximum over 32 columns starting at key index k0 (masked beyond `limit` when the block touches the diagonal / tail)
+    auto chunk_max = [&](const uint32_t (&v)[32], int k0, bool need_mask, float mx) -> float {
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (k0 + e <= limit) mx = fmaxf(mx, __uint_as_float(v[e]));
+        return mx;
+      }
+      float m0 = mx, m1 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; e += 4) {
+        m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+        m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+      }
+      return fmaxf(m0, m1);
     };
 
     for (int j = 0; j < nblk && ok; ++j) {
@@ -255,40 +276,35 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       tc_fence_after();
       const uint32_t t = tmem_base + lane_addr + (uint32_t)(b * 128);
       const bool need_mask = kv0 + FA_BN - 1 > limit;
-      // pass A: row maximum of this block
+      // The whole S row is read once: the other warp's half only for the maximum, this warp's half (64 keys) stays in
+      // registers for the exponentials.
+      const int own = half * 64, oth = own ^ 64;
+      uint32_t k0[32], k1[32], x0[32], x1[32];
       float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < FA_BN; c += 64) {
-        uint32_t v[64];  // two 32-column loads in flight per wait
-        tmem_ld_32x32(t + (uint32_t)c, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-        tmem_ld_32x32(t + (uint32_t)c + 32u, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int e = 0; e < 64; ++e)
-            if (kv0 + c + e <= limit) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-          float m0 = mx, m1 = -INFINITY;
-#pragma unroll
-          for (int e = 0; e < 64; e += 4) {
-            m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
-            m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
-          }
-          mx = fmaxf(m0, m1);
-        }
-      }
+      tmem_ld_32x32(t + (uint32_t)oth, x0);
+      tmem_wait_ld();
+      tmem_ld_32x32(t + (uint32_t)oth + 32u, x1);
+      mx = chunk_max(x0, kv0 + oth, need_mask, mx);
+      tmem_wait_ld();
+      tmem_ld_32x32(t + (uint32_t)own, k0);
+      mx = chunk_max(x1, kv0 + oth + 32, need_mask, mx);
+      tmem_wait_ld();
+      tmem_ld_32x32(t + (uint32_t)own + 32u, k1);
+      mx = chunk_max(k0, kv0 + own, need_mask, mx);
+      tmem_wait_ld();
+      mx = chunk_max(k1, kv0 + own + 32, need_mask, mx);
+      // S is in registers: hand the buffer back to the tensor pipe before the exponentials
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(b));
       const float m_raw = fmaxf(m, mx * g.scale_log2);
       const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // a row with nothing visible yet: keep the arithmetic finite
       const float alpha = ex2_approx(m - m_new);             // 0 on the first block (m = -inf)
-      // pass B: probabilities -> shared memory (K-major, 128-byte swizzle), row sum
+      // probabilities -> shared memory (K-major, 128-byte swizzle), row sum
       if (!(ok = mbar_wait(p_empty(b), ph ^ 1u, g.status, 33))) break;
       uint8_t *p_row = base_ptr + Cfg::OFF_P + b * Cfg::P_BYTES + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
       float rowsum = 0.f;
-#pragma unroll
-      for (int c = half * (FA_BN / 2); c < (half + 1) * (FA_BN / 2); c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t + (uint32_t)c, v);
-        tmem_wait_ld();
+      auto emit = [&](const uint32_t (&v)[32], int c) {  // c = first key column (0..127) of these 32 values
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -308,14 +324,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           uint8_t *dst = p_row + (unit >> 3) * (FA_BM * 128) + (((unit & 7) ^ (row_in_tile & 7)) << 4);
           *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
         }
-      }
-      tc_fence_before();
+      };
+      emit(k0, own);
+      emit(k1, own + 32);
       fence_proxy_async();  // the MMA reads these shared-memory writes through the async proxy
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty(b));
-        mbar_arrive(p_full(b));
-      }
+      if (lane == 0) mbar_arrive(p_full(b));
       l = fmaf(l, alpha, rowsum);
       if (j > 0) ok = accumulate_pv(j - 1, alpha_prev);
       alpha_prev = alpha;
