@@ -249,8 +249,9 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist):
     out["decode_attention_seq1_att4096"] = hbm(timeit(lambda i: att.launch(dargs[i % 8], ws), 32), 2 * nkvh * 4096 * dh * 2)
     # ---- residual add over [4096, 4096] ----
     ad = pkg.Add(idx)
-    xa, xb, xc = [randn(4096, 4096) for _ in range(4)], [randn(4096, 4096) for _ in range(4)], torch.empty(4096, 4096, dtype=f16, device=device)
-    adds = [pkg.AddArgs.of(xc, xa[i], xb[i]) for i in range(4)]
+    xa, xb = [randn(4096, 4096) for _ in range(4)], [randn(4096, 4096) for _ in range(4)]
+    xc = [torch.empty(4096, 4096, dtype=f16, device=device) for _ in range(4)]
+    adds = [pkg.AddArgs.of(xc[i], xa[i], xb[i]) for i in range(4)]
     out["add_4096x4096"] = hbm(timeit(lambda i: ad.launch(adds[i % 4]), 20), 3 * 4096 * 4096 * 2)
     # ---- config 5: random_sample over 64 x 128256 logits ----
     rows, n = 64, 128256

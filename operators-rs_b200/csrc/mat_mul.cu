@@ -292,8 +292,16 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
 #pragma unroll 1
       for (int c = 0; c < BN && finish; c += 32) {
         uint32_t v[32];
+        // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
+        // (beta != 0) are requested before the tensor-memory load is waited for, four 128-bit loads in flight per lane.
+        const bool fast = g.vec_store && row < g.m && n0 + c + 32 <= g.n;
+        Pack8 oldc[4];
         if (FUSED || w.slice < 0) {
           tmem_ld_32x32(taddr + (uint32_t)c, v);
+          if (fast && g.read_c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) oldc[q].u = ld_global_16(drow + n0 + c + q * 8);
+          }
           tmem_wait_ld();
         } else {
           float sum[32];
@@ -329,7 +337,23 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(sum[e]);
         }
-        if (row < g.m) {
+        if (fast) {
+          if (!(FUSED || w.slice < 0) && g.read_c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) oldc[q].u = ld_global_16(drow + n0 + c + q * 8);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Pack8 out;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
+              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(oldc[q].h[e])), val);
+              out.h[e] = __float2half_rn(val);
+            }
+            st_global_16(wrow + n0 + c + q * 8, out.u);
+          }
+        } else if (row < g.m) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int col = n0 + c + q * 8;
