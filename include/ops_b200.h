@@ -325,6 +325,10 @@ int ops_comm_p2p_attach(ops_comm *c, const uint8_t *all_handles /* group_size * 
 /* Status word of the last P2P kernel on this rank: 0 ok, else a bounded wait ran out
  * (read after the stream is synchronised). */
 int ops_comm_p2p_status(ops_comm *c);
+/* Test aid with no counterpart in the crate: a communicator of `group_size` ranks that all map this rank's own staging
+ * buffer.  Its peers never run, so a peer-to-peer all_reduce on it ends through its bounded waits (about one second)
+ * with a non-zero ops_comm_p2p_status and an intact context: the time-out path can be exercised on one GPU. */
+int ops_comm_create_loopback(int device, int group_size, size_t staging_bytes, ops_comm **out);
 
 typedef struct ops_all_reduce ops_all_reduce;
 typedef struct {

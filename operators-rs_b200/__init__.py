@@ -628,6 +628,15 @@ class Comm:
         _check(lib().ops_comm_init_rank(ctypes.c_int(device), ctypes.c_int(rank), ctypes.c_int(group_size), idbuf, ctypes.byref(self._h)), False)
         self.device = device
 
+    @classmethod
+    def loopback(cls, device, group_size, staging_bytes):
+        """ops_comm_create_loopback: every peer is this rank's own buffer; for exercising the bounded waits on one GPU."""
+        self = cls.__new__(cls)
+        self._h = ctypes.c_void_p()
+        self.device = device
+        _check(lib().ops_comm_create_loopback(ctypes.c_int(device), ctypes.c_int(group_size), ctypes.c_size_t(staging_bytes), ctypes.byref(self._h)), False)
+        return self
+
     @staticmethod
     def unique_id():
         buf = (ctypes.c_uint8 * COMM_ID_BYTES)()
@@ -701,5 +710,5 @@ EXPORTS = [
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
-    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
+    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_comm_create_loopback", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
 ]

@@ -360,6 +360,27 @@ OPS_API int ops_comm_init_rank(int device, int rank, int group_size, const uint8
   return OPS_OK;
 }
 
+// A communicator whose `group_size` ranks all map THIS rank's staging buffer: no NCCL, no second process.  The other
+// "ranks" never run, so a peer-to-peer all_reduce on it can only end through its bounded waits — which is the point: it
+// lets one GPU exercise the time-out path (status word set, kernel returns, context intact) without a hung peer.
+OPS_API int ops_comm_create_loopback(int device, int group_size, size_t staging_bytes, ops_comm **out) {
+  if (!out || group_size < 2 || group_size > MAX_RANKS) return fail(OPS_ARGS_NOT_SUPPORT, "loopback communicator: group size 2..%d", MAX_RANKS);
+  ops_comm *c = nullptr;
+  OPS_TRY(ops_comm_init_rank(device, 0, 1, nullptr, &c));
+  c->size = group_size;
+  uint8_t handle[OPS_COMM_P2P_HANDLE_BYTES];
+  int rc = ops_comm_p2p_export(c, staging_bytes, handle);
+  if (rc != OPS_OK) {
+    ops_comm_destroy(c);
+    return rc;
+  }
+  for (int q = 0; q < group_size; ++q) c->peers[q] = c->staging;
+  c->p2p_ready = false;  // nothing to close at destroy: every entry is the own buffer
+  c->loopback = true;
+  *out = c;
+  return OPS_OK;
+}
+
 OPS_API int ops_comm_rank(const ops_comm *c) { return c->rank; }
 OPS_API int ops_comm_group_size(const ops_comm *c) { return c->size; }
 
@@ -451,7 +472,7 @@ OPS_API void ops_all_reduce_destroy(ops_all_reduce *op) { delete op; }
 
 OPS_API int ops_all_reduce_set_algo(ops_all_reduce *op, int algo) {
   if (algo < OPS_ALL_REDUCE_AUTO || algo > OPS_ALL_REDUCE_P2P_TWO_SHOT) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: unknown algorithm %d", algo);
-  if (algo >= OPS_ALL_REDUCE_P2P_ONE_SHOT && !op->comm->p2p_ready && op->comm->size > 1)
+  if (algo >= OPS_ALL_REDUCE_P2P_ONE_SHOT && !op->comm->p2p_ready && !op->comm->loopback && op->comm->size > 1)
     return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: peer-to-peer staging is not attached");
   op->algo = algo;
   return OPS_OK;
@@ -514,7 +535,7 @@ OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce
     return OPS_OK;
   }
   int algo = op->algo;
-  const bool p2p_able = c->p2p_ready && args->op == OPS_REDUCE_SUM && (m.dt == OPS_DT_F16 || m.dt == OPS_DT_F32) && bytes % 16 == 0 &&
+  const bool p2p_able = (c->p2p_ready || c->loopback) && args->op == OPS_REDUCE_SUM && (m.dt == OPS_DT_F16 || m.dt == OPS_DT_F32) && bytes % 16 == 0 &&
                         aligned(dst, 16) && aligned(src, 16) && bytes <= c->region_bytes && 2 * c->sm_count >= 1;
   if (algo == OPS_ALL_REDUCE_AUTO) {
     if (!p2p_able) algo = OPS_ALL_REDUCE_NCCL;

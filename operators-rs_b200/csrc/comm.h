@@ -56,6 +56,7 @@ struct ops_comm {
   size_t region_bytes;         // bytes of each of the four data regions
   char *peers[ops::MAX_RANKS];
   bool p2p_ready;
+  bool loopback;               // every peer entry is the own buffer (time-out tests on one GPU)
   unsigned int epoch;
   int *status_dev;
   int sm_count;

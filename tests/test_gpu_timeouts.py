@@ -1,0 +1,38 @@
+"""Bounded waits: a peer that never arrives ends the peer-to-peer all_reduce with a status code, not a hang.
+
+The failure is made on the host side — a loopback communicator whose other "ranks" do not exist — never by faulting or
+trapping the GPU: the kernel notices after its wait limit (about one second) that a flag is not coming, records where
+it gave up and returns; the context stays usable and the next launches work.
+"""
+import time
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("algo_name", ["one_shot", "two_shot"])
+def test_missing_peer_times_out_cleanly(pkg, dev, algo_name):
+    comm = pkg.Comm.loopback(0, 2, 1 << 20)
+    op = pkg.AllReduce(comm)
+    op.set_algo(pkg.ALL_REDUCE_P2P_ONE_SHOT if algo_name == "one_shot" else pkg.ALL_REDUCE_P2P_TWO_SHOT)
+    x = torch.ones(64, 4096, dtype=torch.float16, device=dev)
+    assert comm.p2p_status() == 0
+    t0 = time.time()
+    op.launch(pkg.AllReduceArgs.of(x, x))
+    torch.cuda.synchronize()  # returns: the wait is bounded
+    waited = time.time() - t0
+    assert 0.5 < waited < 10.0, waited
+    code = comm.p2p_status()
+    assert code != 0 and code % 16 in (1, 2, 3), code  # phase of the wait that ran out; code // 16 - 1 = the rank waited for
+    assert code // 16 - 1 == 1
+    # the context is intact: an ordinary operator still runs and is correct
+    y = torch.empty(8, 256, dtype=torch.float16, device=dev)
+    w = torch.ones(256, dtype=torch.float16, device=dev)
+    pkg.RmsNorm(0).launch(pkg.RmsNormArgs.of(y, torch.full((8, 256), 2.0, dtype=torch.float16, device=dev), w, 0.0))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(y.float().cpu().numpy(), 1.0, atol=1e-3)
+    del op
+    comm.destroy()
