@@ -47,6 +47,7 @@ constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
 constexpr int GEMM_SPLIT_MAX_UNITS = 160;          // CTAs that may hold a K-slice partial (>= SM count)
 constexpr int GEMM_SPLIT_MAX_SLICES = 8;
+constexpr int GEMM_EPI_LD = 36;                    // padded row length (words) of the epilogue's shared-memory pad: conflict-free both ways
 
 struct GemmKernelArgs {
   __half *d;             // row-major output
@@ -113,7 +114,9 @@ template <int BN> struct GemmCfg {
   static constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two >= 32
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES + 256;            // after the barriers
+  static constexpr int EPI_BYTES = 4 * 32 * GEMM_EPI_LD * 4;               // one 32 x 32 f32 transposition pad per epilogue warp
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 };
 
 template <int BN, bool FUSED>
@@ -294,13 +297,20 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         uint32_t v[32];
         // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
         // (beta != 0) are requested before the tensor-memory load is waited for, four 128-bit loads in flight per lane.
-        const bool fast = g.vec_store && row < g.m && n0 + c + 32 <= g.n;
+        // (warp-uniform) — it goes through a shared-memory pad that turns "one lane = one row" into "eight rows x 64
+        // contiguous bytes per instruction", so that C is read and written in full 32-byte sectors.
+        const bool fast = g.vec_store && n0 + c + 32 <= g.n;
+        const int rsub = lane >> 2, unit = lane & 3;
+        const int tile_row0 = row - lane;
         Pack8 oldc[4];
         if (FUSED || w.slice < 0) {
           tmem_ld_32x32(taddr + (uint32_t)c, v);
           if (fast && g.read_c) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) oldc[q].u = ld_global_16(drow + n0 + c + q * 8);
+            for (int it = 0; it < 4; ++it) {
+              const int grow = tile_row0 + it * 8 + rsub;
+              if (grow < g.m) oldc[it].u = ld_global_16(g.d + (long long)b * g.d_bs + (long long)grow * g.ldd + n0 + c + unit * 8);
+            }
           }
           tmem_wait_ld();
         } else {
@@ -340,19 +350,37 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         if (fast) {
           if (!(FUSED || w.slice < 0) && g.read_c) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) oldc[q].u = ld_global_16(drow + n0 + c + q * 8);
+            for (int it = 0; it < 4; ++it) {
+              const int grow = tile_row0 + it * 8 + rsub;
+              if (grow < g.m) oldc[it].u = ld_global_16(g.d + (long long)b * g.d_bs + (long long)grow * g.ldd + n0 + c + unit * 8);
+            }
           }
+          float *pad = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) + Cfg::EPI_OFF) + (warp - 2) * 32 * GEMM_EPI_LD;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4 *>(pad + lane * GEMM_EPI_LD + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + rsub, grow = tile_row0 + rr;
+            const float4 f0 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8);
+            const float4 f1 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8 + 4);
+            const float acc8[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
             Pack8 out;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
-              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(oldc[q].h[e])), val);
+              float val = __fmul_rn(g.alpha, acc8[e]);
+              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(oldc[it].h[e])), val);
               out.h[e] = __float2half_rn(val);
             }
-            st_global_16(wrow + n0 + c + q * 8, out.u);
+            if (grow < g.m) {
+              __half *wp;
+              if constexpr (FUSED) wp = reinterpret_cast<__half *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa.epoch & 1u)) + (long long)grow * g.n;
+              else wp = g.d + (long long)b * g.d_bs + (long long)grow * g.ldd;
+              st_global_16(wp + n0 + c + unit * 8, out.u);
+            }
           }
+          __syncwarp();  // the pad is rewritten by the next chunk
         } else if (row < g.m) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
