@@ -131,7 +131,7 @@ def cpu_layer_baseline(tokens, repeats, warmup):
     return tokens / sec, orc.num_threads(), sec
 
 
-def extra_measurements(torch, pkg, device, peaks, comm, tp, dist):
+def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank):
     """Per-operator numbers for the BASELINE configs the layer loop does not cover: config 1 (latency of the small
     chain), config 2 (attention prefill pieces, KV-cache write), config 5 (random_sample) on one GPU; config 4's
     all_reduce sizes under tensor parallelism.  CUDA events around back-to-back launches; inputs rotate through more
@@ -186,6 +186,24 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist):
         return {"us": ms * 1e3, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tflops_burst"], "flops": flops}
 
     out = {}
+    # ---- config 4's small batches: the whole layer at T = 1 and T = 64 tokens, replayed from a CUDA graph (host launch
+    # cost would otherwise dominate).  Under tensor parallelism the all_reduce inside the graph is NCCL's: the
+    # peer-to-peer kernels take their epoch as a launch argument and are therefore not replayable. ----
+    lat = {}
+    for T in (1, 64):
+        small = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=pkg.ALL_REDUCE_NCCL)
+        xs = randn(T, cfg.d)
+        ps = torch.arange(T, dtype=torch.int32, device=device).view(torch.uint32)
+        if dist is not None:
+            dist.barrier()
+        ms = timeit(lambda i: small.forward(xs, ps), 10, warm=3)
+        if dist is not None:
+            tt = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt[0])
+        lat[f"T{T}"] = {"us": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
+        del small
+    out["layer_latency_small_batches"] = lat
     if tp > 1:
         op = pkg.AllReduce(comm)
         for T in (1, 64, 4096):
@@ -477,9 +495,9 @@ def main():
 
     extras = None
     if not args.no_extras:
-        del layer, shard
+        del layer
         torch.cuda.empty_cache()
-        extras = extra_measurements(torch, pkg, device, peaks, comm, tp, dist)
+        extras = extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank)
 
     if rank != 0:
         if comm is not None:

@@ -275,9 +275,11 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           uint32_t v[32];
           tmem_ld_32x32(taddr + (uint32_t)c, v);
           tmem_wait_ld();
+          if (row < g.m) {  // rows outside C are never read back
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            *reinterpret_cast<uint4 *>(part_row + c + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4 *>(part_row + c + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
         }
         __threadfence();
         __syncwarp();
@@ -315,7 +317,10 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           tmem_wait_ld();
         } else {
           float sum[32];
-          if (g.split_g == 2) {  // the common case: both slices' 16 loads are in flight together
+          if (row >= g.m) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sum[e] = 0.f;
+          } else if (g.split_g == 2) {  // the common case: both slices' 16 loads are in flight together
             float4 f0[8], f1[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -781,7 +786,11 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
       // Splitting costs a fixed ~20 us (f32 partials through L2, a second pipeline fill), about 45 k-blocks of tile time;
       // it pays when the tile time it removes from the tail, (1 - 1/G) * num_kb k-blocks, is clearly larger.
       // Measured on the config-3 layer: +9 % on the K = 14336 down projection, a loss on the K = 4096 ones.
-      if (G >= 2 && (long long)(G - 1) * num_kb < 90LL * G) G = 1;
+      // A machine that is less than half full (skinny decode-time products: a few tiles, each streaming a whole weight
+      // panel) is a different case: there the split is what puts every SM on the HBM stream, and the partials are small
+      // (rows beyond m are neither written nor read).
+      const bool underfilled = tiles * 2 <= sms && p.m <= 64;
+      if (G >= 2 && !underfilled && (long long)(G - 1) * num_kb < 90LL * G) G = 1;
       if (G >= 2) {
         const int per = (num_kb + G - 1) / G;
         G = (num_kb + per - 1) / per;  // drop empty slices
@@ -868,7 +877,11 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
       return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
     }
     if (a_ok && b_ok && d_ok && encode_tiled_fn()) {
-      if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+      // 128 x 256 tiles unless the product is skinny and would leave three quarters of the SMs without a tile: then
+      // narrower tiles (and the K split above them) spread the weight stream over the machine
+      const long long tiles256 = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + 255) / 256) * (long long)p.batch;
+      const bool narrow = p.n <= 128 || (p.m <= 64 && tiles256 * 4 <= op->base.sm_count);
+      if (!narrow) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
       return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
     }
   }

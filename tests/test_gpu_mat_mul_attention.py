@@ -72,10 +72,11 @@ def test_mat_mul_edges(pkg, orc, synth, dev, m, n, k):
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 1.0, 1.0, seed=40)
 
 
-@pytest.mark.parametrize("m,n,k", [(1024, 2048, 12288), (256, 512, 12288), (300, 700, 16000)])
+@pytest.mark.parametrize("m,n,k", [(1024, 2048, 12288), (256, 512, 12288), (300, 700, 16000), (1, 4096, 4096), (64, 6144, 4096), (7, 4096, 14336)])
 def test_mat_mul_split_k_remainder_wave(pkg, orc, synth, dev, m, n, k):
     # long K and a tile count that leaves a partial last wave: the remainder tiles are cut along K over the idle CTAs
-    # (2 slices for 64 tiles, 8 slices for a handful) and the f32 partials are added in slice order; twice in a row to
+    # (2 slices for 64 tiles, 8 slices for a handful; skinny decode-time products are split to put every SM on the weight
+    # stream) and the f32 partials are added in slice order; twice in a row to
     # check that the arrival counters are left at zero
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, False, False, 1.0, 0.0, seed=80)
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 0.5, 1.0, seed=90)
