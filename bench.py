@@ -4,19 +4,27 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" = one pass of the operator chain (rms_norm, mat_mul QKV, rope, attention, mat_mul O, [all_reduce],
-rms_norm, mat_mul gate|up, swiglu, mat_mul down, [all_reduce]) over one batch of synthetic tokens:
+One "step" = one pass of the operator chain (rms_norm, mat_mul QKV, rope, attention, mat_mul O, [exchange],
+rms_norm, mat_mul gate|up, swiglu, mat_mul down, [exchange]) over one batch of synthetic tokens:
   N = 1 : BASELINE config 3 (4096 tokens, d 4096, 32/8 heads, dh 128, ffn 14336, f16, random init);
-  N > 1 : config 4, the same layer tensor-parallel over N GPUs with f16 sum all_reduce of the [T, 4096] partials
+  N > 1 : config 4, the same layer tensor-parallel over N GPUs with an f16 sum all_reduce of the [T, 4096] partials
           (total work fixed -> "scaling": "strong").
-`value` is device-timed (CUDA events on the launching stream, max over ranks) with the inputs resident in HBM;
-`e2e` is the same chain called through the package's public API with the step's activations in pinned HOST memory:
-host->device copy of x, the chain, device->host copy of the result, all inside the timed region.
-`roofline` describes the dominant kernel (the gate|up tensor-core GEMM launch) from CUDA events recorded around
-every operator inside the timed region; `ops` lists every operator the same way.
-`cpu_baseline` (rank 0, N = 1) times the CPU oracle — the restated common_cpu operators, the reference crate itself
-cannot be built without a Rust toolchain — on a bounded token sample of the same layer.
-`--impl reference` runs only that CPU arm and prints it in the same format.
+`value`    device-timed (CUDA events on the launching stream, max over ranks), inputs resident in HBM.
+`ops`      the same chain run once more with an event after every operator (under tensor parallelism this pass is
+           unpipelined so that an event sees one operator): per-operator time, achieved GB/s or TFLOP/s, fraction of the
+           measured peak.  `roofline` describes the dominant kernel (the gate|up tensor-core GEMM launch) from those events,
+           plus a sustained leg: that launch back to back for seconds, with the clocks sampled, against the sustained peak.
+`e2e`      the chain through the package's public API with the step's activations in pinned HOST memory: host->device
+           copy, the chain, device->host read of the result, all inside the timed region, pipelined over three streams.
+           Under tensor parallelism every rank uploads its 1/N of the rows, the ranks exchange them over NVLink, and rank 0
+           (all ranks hold the same bits) reads the result back.
+`parity`   after the timed regions: the layer on a 512-token input, every rank's output gathered and compared bit for bit,
+           rank 0's compared with the CPU oracle's chain on the same shards.
+`cpu_baseline` (rank 0, N = 1) and `--impl reference`: the CPU oracle — the restated common_cpu operators; the reference
+           crate itself cannot be built without a Rust toolchain — on the SAME 4096-token layer, all host threads.
+`other_configs` per-operator numbers of BASELINE configs 1, 2, 5 (and 4's all_reduce sizes), stand-alone launches, beside
+           the library calls the reference's GPU backend makes for them (cuBLAS through torch.matmul, CUB's radix sort
+           through torch.sort) timed the same way.
 """
 import argparse
 import json
@@ -34,6 +42,22 @@ import __graft_entry__ as graft  # noqa: E402
 CFG = dict(d=4096, nh=32, nkvh=8, dh=128, ffn=14336, theta=5e5, eps=1e-5)
 WORKLOAD = "BASELINE config 3: Llama-3-8B-shaped decoder layer, 4096 tokens, d=4096, 32q/8kv heads, dh=128, ffn=14336, f16, random init"
 SEED = 0xB2000030
+PARITY_TOKENS = 512
+NOMINAL_F16_TFLOPS = 2250.0  # dense fp16 tensor peak of one B200 at clocks.max.sm
+
+
+def config_for(tp, tokens):
+    """The `config` object of the JSON line: the same for this arm and the CPU arm at a given N."""
+    return {"workload": WORKLOAD if tp == 1 else WORKLOAD.replace("config 3", "config 4") + f", tensor-parallel over {tp} GPUs",
+            "tokens": tokens, "parallelism": f"tp{tp}",
+            "l2": "inputs larger than L2: every step streams 436 MB of weights and ~0.6 GB of activations through a 126 MB L2"}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def measured_peaks():
@@ -41,8 +65,19 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"],
+                "sm_max_mhz": p.get("sm_max_mhz", 1965.0), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+
+
+def measured_traffic():
+    """DRAM bytes per launch of the dominant kernel from the last ncu capture of this build (a small data file beside the
+    package, written by hand from that capture: kernel, shape, bytes, the commit it was taken on)."""
+    path = os.path.join(graft.PKG_DIR, "measured_traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return None
 
 
 class ClockSampler:
@@ -105,44 +140,39 @@ def make_weights(torch, device, cfg):
             "w_gu": proj(d, 2 * ffn), "w_down": proj(ffn, d)}
 
 
-def cpu_layer_baseline(tokens, repeats, warmup):
-    """Times the CPU oracle's decoder layer on `tokens` tokens.  Returns (tokens/s, threads, seconds per pass)."""
+def cpu_layer_baseline(tokens, repeats, warmup, tp=1):
+    """Times the CPU oracle's decoder layer (tensor-parallel ranks emulated one after the other, partials meeting in the
+    crate's f16 tree all_reduce) on `tokens` tokens with every host thread.  Returns (tokens/s, threads, seconds per pass)."""
+    import importlib
     import numpy as np
     orc = graft.load_oracle()
     orc.lib()
+    threads = host_threads()
+    orc.set_num_threads(threads)  # explicit: launchers like torchrun export OMP_NUM_THREADS=1
     graft.load_package()
-    pkg_synth = __import__("importlib").import_module(graft.PKG_NAME + ".synth")
-    rng_seed = SEED
+    pkg_synth = importlib.import_module(graft.PKG_NAME + ".synth")
+    layer_mod = importlib.import_module(graft.PKG_NAME + ".layer")
     d, nh, nkvh, dh, ffn = CFG["d"], CFG["nh"], CFG["nkvh"], CFG["dh"], CFG["ffn"]
-    w = {"w_norm1": pkg_synth.uniform(rng_seed + 1, (d,), 0.5, 1.5).astype(np.float16),
-         "w_norm2": pkg_synth.uniform(rng_seed + 2, (d,), 0.5, 1.5).astype(np.float16)}
-    rng = np.random.default_rng(rng_seed)  # fast generator: the weights' values do not affect the timing
+    w = {"w_norm1": pkg_synth.uniform(SEED + 1, (d,), 0.5, 1.5).astype(np.float16),
+         "w_norm2": pkg_synth.uniform(SEED + 2, (d,), 0.5, 1.5).astype(np.float16)}
+    rng = np.random.default_rng(SEED)  # fast generator: the weights' values do not affect the timing
     for name, shape in (("w_qkv", (d, (nh + 2 * nkvh) * dh)), ("w_o", (nh * dh, d)), ("w_gu", (d, 2 * ffn)), ("w_down", (ffn, d))):
         w[name] = (rng.standard_normal(shape, dtype=np.float32) * 0.02).astype(np.float16)
+    cfg = layer_mod.LayerConfig(**CFG)
+    shards = [layer_mod.shard_weights(w, r, tp, cfg) for r in range(tp)]
     x = rng.standard_normal((tokens, d), dtype=np.float32).astype(np.float16)
     pos = np.arange(tokens, dtype=np.uint32)
     times = []
     for i in range(warmup + repeats):
         t0 = time.perf_counter()
-        orc.decoder_layer(x, pos, [w], CFG)
+        orc.decoder_layer(x, pos, shards, CFG)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
     return tokens / sec, orc.num_threads(), sec
 
 
-def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank):
-    """Per-operator numbers for the BASELINE configs the layer loop does not cover: config 1 (latency of the small
-    chain), config 2 (attention prefill pieces, KV-cache write), config 5 (random_sample) on one GPU; config 4's
-    all_reduce sizes under tensor parallelism.  CUDA events around back-to-back launches; inputs rotate through more
-    than an L2 worth of buffers where a single copy would fit in L2."""
-    idx = device.index or 0
-    f16 = torch.float16
-    g = torch.Generator(device=device).manual_seed(SEED + 99)
-
-    def randn(*shape, std=1.0):
-        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).half()
-
+def make_timeit(torch, device):
     side = torch.cuda.Stream(device)
 
     def timeit(fn, reps, warm=3, graph=True):
@@ -177,6 +207,48 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps  # ms
 
+    return timeit
+
+
+def sustained_leg(torch, local_rank, fn, flops, seconds, peaks):
+    """`fn()` back to back for about `seconds` with the clocks sampled: TFLOP/s against the sustained peak."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn()
+    b.record()
+    torch.cuda.synchronize()
+    per = max(a.elapsed_time(b), 1e-3)
+    reps = max(10, int(seconds * 1e3 / per))
+    sampler = ClockSampler(local_rank)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    clocks = sampler.stop()
+    ach = flops * reps / (ms * 1e-3) / 1e12
+    return {"achieved": ach, "unit": "TFLOP/s", "peak": peaks["tflops_sustained"], "frac": ach / peaks["tflops_sustained"], "seconds": ms * 1e-3,
+            "launches": reps, "sm_mhz_median": clocks.get("sm_mhz"), "power_w_max": clocks.get("power_w_max"), "reasons": clocks.get("reasons")}
+
+
+def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank, lane_comms):
+    """Per-operator numbers for the BASELINE configs the layer loop does not cover: config 1 (latency of the small
+    chain), config 2 (attention prefill pieces, KV-cache write), config 3's memory-bound operators stand-alone, config 5
+    (random_sample) on one GPU; config 4's all_reduce sizes and small batches under tensor parallelism.  CUDA events around
+    back-to-back launches; inputs rotate through more than an L2 worth of buffers where a single copy would fit in L2."""
+    idx = device.index or 0
+    f16 = torch.float16
+    g = torch.Generator(device=device).manual_seed(SEED + 99)
+
+    def randn(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).half()
+
+    timeit = make_timeit(torch, device)
+
     def hbm(ms, nbytes):
         ach = nbytes / (ms * 1e-3) / 1e9
         return {"us": ms * 1e3, "bound": "hbm", "achieved": ach, "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "bytes": nbytes}
@@ -187,11 +259,10 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
 
     out = {}
     # ---- config 4's small batches: the whole layer at T = 1 and T = 64 tokens, replayed from a CUDA graph (host launch
-    # cost would otherwise dominate).  Under tensor parallelism the all_reduce inside the graph is NCCL's: the
-    # peer-to-peer kernels take their epoch as a launch argument and are therefore not replayable. ----
+    # cost would otherwise dominate).  The peer-to-peer kernels keep their launch counter on the device, so they replay. ----
     lat = {}
     for T in (1, 64):
-        small = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=pkg.ALL_REDUCE_NCCL)
+        small = layer_mod.DecoderLayer(cfg, shard, T, device, comms=lane_comms[:1] if tp > 1 else None, tp=tp, rank=rank, all_reduce_algo=pkg.ALL_REDUCE_AUTO)
         xs = randn(T, cfg.d)
         ps = torch.arange(T, dtype=torch.int32, device=device).view(torch.uint32)
         if dist is not None:
@@ -206,23 +277,32 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
     out["layer_latency_small_batches"] = lat
     if tp > 1:
         op = pkg.AllReduce(comm)
-        for T in (1, 64, 4096):
+        for T in (1, 64, 512, 4096):
             nbytes = T * 4096 * 2
             buf = randn(T, 4096)
             res = {}
-            for name, algo in (("nccl", pkg.ALL_REDUCE_NCCL), ("one_shot", pkg.ALL_REDUCE_P2P_ONE_SHOT), ("two_shot", pkg.ALL_REDUCE_P2P_TWO_SHOT)):
+            for name, algo in (("nccl", pkg.ALL_REDUCE_NCCL), ("one_shot", pkg.ALL_REDUCE_P2P_ONE_SHOT), ("two_shot", pkg.ALL_REDUCE_P2P_TWO_SHOT),
+                               ("two_shot_direct_add", None)):
                 if name == "one_shot" and nbytes > (1 << 22):
                     continue
-                op.set_algo(algo)
-                args = pkg.AllReduceArgs.of(buf, buf)
+                if algo is not None:
+                    op.set_algo(algo)
+                    args = pkg.AllReduceArgs.of(buf, buf)
+                    call = lambda i: op.launch(args)
+                else:
+                    part = comm.p2p_direct(f16)[: T * 4096].view(T, 4096)
+                    part.copy_(buf)
+                    args = pkg.AllReduceArgs.of(buf, part)
+                    call = lambda i: op.launch_add(args)
                 dist.barrier()
-                ms = timeit(lambda i: op.launch(args), 20, warm=3, graph=False)
+                ms = timeit(call, 20, warm=3, graph=False)
                 tt = torch.tensor([ms], device=device, dtype=torch.float64)
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 ms = float(tt[0])
                 bus = 2 * (tp - 1) / tp * nbytes / (ms * 1e-3) / 1e9
                 res[name] = {"us": ms * 1e3, "bus_GBps": bus, "frac_of_770": bus / 770.0}
             out[f"all_reduce_T{T}"] = {"message_bytes": nbytes, **res}
+        op.set_algo(pkg.ALL_REDUCE_AUTO)
         return out
 
     # ---- config 1: the small chain (latency; far below any roofline at 256 KiB) ----
@@ -234,6 +314,41 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
     a1, a2, a3 = pkg.RmsNormArgs.of(y, x, w, 1e-5), pkg.RopeArgs.of(y.view(64, 32, 64), pos, 1e4), pkg.FusedSoftmaxArgs.of(sc)
     out["config1_chain_latency_us"] = {"rms_norm": timeit(lambda i: rn.launch(a1), 50) * 1e3, "rope": timeit(lambda i: rp.launch(a2), 50) * 1e3,
                                        "fused_softmax": timeit(lambda i: sm.launch(a3), 50) * 1e3}
+    # ---- config 3's memory-bound operators on their own (no neighbours, no events in between): 4 rotating buffer sets ----
+    T, d, ffn = 4096, 4096, 14336
+    xs3 = [randn(T, d) for _ in range(4)]
+    ys3 = [torch.empty(T, d, dtype=f16, device=device) for _ in range(4)]
+    w3 = (torch.rand(d, generator=g, device=device) + 0.5).half()
+    n3 = [pkg.RmsNormArgs.of(ys3[i], xs3[i], w3, 1e-5) for i in range(4)]
+    out["config3_rms_norm_alone"] = hbm(timeit(lambda i: rn.launch(n3[i % 4]), 20), 2 * T * d * 2 + d * 2)
+    r3 = [pkg.RmsNormAddArgs.of(ys3[i], xs3[i], w3, 1e-5, ys3[(i + 1) % 4]) for i in range(4)]
+    out["config3_rms_norm_with_residual_add_alone"] = hbm(timeit(lambda i: rn.launch_add(r3[i % 4]), 20), 4 * T * d * 2 + d * 2)
+    qk3 = [randn(T, 48, 128) for _ in range(4)]
+    pos3 = torch.arange(T, dtype=torch.int32, device=device).view(torch.uint32)
+    p3 = [pkg.RopeArgs.of(qk3[i][:, :40], pos3, 5e5) for i in range(4)]
+    out["config3_rope_alone"] = hbm(timeit(lambda i: rp.launch(p3[i % 4]), 20), 2 * T * 40 * 128 * 2 + T * 4)
+    del qk3
+    gu3 = [randn(T, 2 * ffn) for _ in range(2)]
+    sw = pkg.Swiglu(idx)
+    s3 = [pkg.SwigluArgs.of(gu3[i][:, :ffn], gu3[i][:, ffn:]) for i in range(2)]
+    out["config3_swiglu_alone"] = hbm(timeit(lambda i: sw.launch(s3[i % 2]), 10), 3 * T * ffn * 2)
+    del gu3, s3
+    # ---- the library bar for mat_mul: cuBLAS (torch.matmul, f16) on the four config-3 products and on their 8-way shards ----
+    mm = pkg.MatMul(idx)
+    bars = {}
+    shapes = {"qkv": (T, 6144, d), "o": (T, d, d), "gate_up": (T, 2 * ffn, d), "down": (T, d, ffn),
+              "tp8_qkv": (T, 768, d), "tp8_o": (T, d, 512), "tp8_gate_up": (T, 3584, d), "tp8_down": (T, d, 1792)}
+    for name, (m_, n_, k_) in shapes.items():
+        a_ = randn(m_, k_)
+        b_ = randn(k_, n_, std=0.02)
+        c_ = torch.empty(m_, n_, dtype=f16, device=device)
+        ours = timeit(lambda i: mm.launch(pkg.MatMulArgs.of(c_, 0.0, a_, b_, 1.0)), 10)
+        lib_ms = timeit(lambda i: torch.matmul(a_, b_, out=c_), 10)
+        fl = 2 * m_ * n_ * k_
+        bars[name] = {"shape_mnk": [m_, n_, k_], "ours_us": ours * 1e3, "ours_tflops": fl / (ours * 1e-3) / 1e12, "cublas_us": lib_ms * 1e3,
+                      "cublas_tflops": fl / (lib_ms * 1e-3) / 1e12, "vs_cublas": lib_ms / ours}
+        del a_, b_, c_
+    out["mat_mul_vs_cublas_f16"] = bars
     # ---- config 2: attention prefill ----
     nh, nkvh, seq, dh = 32, 8, 2048, 128
     sets = [(randn(nh, seq, dh), randn(nkvh, seq, dh), randn(nkvh, seq, dh), torch.empty(nh, seq, dh, dtype=f16, device=device)) for _ in range(3)]
@@ -242,9 +357,15 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
     fl = 4 * nh * dh * (seq * (seq + 1) // 2)
     aargs = [pkg.AttentionArgs.of(q, k, v, o) for q, k, v, o in sets]
     out["config2_attention_fused"] = tensor(timeit(lambda i: att.launch(aargs[i % 3], ws), 20), fl)
+    try:  # the library bar for attention: torch's fused scaled-dot-product attention on the same tensors
+        import torch.nn.functional as F
+        qb, kb, vb = sets[0][0][None], sets[0][1][None], sets[0][2][None]
+        ms = timeit(lambda i: F.scaled_dot_product_attention(qb, kb, vb, is_causal=True, enable_gqa=True), 10)
+        out["config2_attention_torch_sdpa"] = tensor(ms, fl)
+    except Exception as e:  # noqa: BLE001
+        out["config2_attention_torch_sdpa"] = {"unavailable": str(e)[:200]}
     att.set_algo(pkg.ATTENTION_CHAIN)
     out["config2_attention_chain"] = tensor(timeit(lambda i: att.launch(aargs[i % 3], ws), 10), fl)
-    mm = pkg.MatMul(idx)
     scores = torch.empty(nkvh, 4 * seq, seq, dtype=f16, device=device)
     q, k, v, o = sets[0]
     qk = pkg.MatMulArgs.of(scores, 0.0, q.view(nkvh, 4 * seq, dh), k.transpose(1, 2), 1.0 / 128 ** 0.5)
@@ -284,22 +405,27 @@ def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg
     one = [pkg.RandomSampleArgs.of(kv[r], logits[0][r], pkg.SampleArgs.arg_max()) for r in range(rows)]
     ms = timeit(lambda i: [rs.launch(a, wsr) for a in one], 5)
     out["config5_argmax_per_row_api"] = {**hbm(ms, rows * n * 2), "launches": rows}
+    # the library bar for sampling: the reference's GPU backend orders every row with CUB's radix sort first
+    ms = timeit(lambda i: torch.sort(logits[i % 10], dim=-1, descending=True), 5)
+    out["config5_cub_sort_torch_sort"] = {**hbm(ms, rows * n * 2), "note": "sort only; the reference then scans and searches"}
+    ms = timeit(lambda i: torch.argmax(logits[i % 10], dim=-1), 20)
+    out["config5_torch_argmax"] = hbm(ms, rows * n * 2)
     return out
 
 
-
-def run_reference(args, rank):
-    """--impl reference: the CPU arm alone (rank 0 only under torchrun)."""
+def run_reference(args, rank, world):
+    """--impl reference: the CPU arm alone (rank 0 only under torchrun), on the same layer and token count."""
     if rank != 0:
         return
-    tokens = args.ref_tokens
-    tps, threads, sec = cpu_layer_baseline(tokens, max(args.steps, 1), min(args.warmup, 1))
-    sample = f"{tokens}-token causal sequence through the full-width layer per step (same weights' shapes as config 3)"
+    tp = max(world, 1)
+    tps, threads, sec = cpu_layer_baseline(args.tokens, max(args.steps, 1), max(args.warmup, 0), tp=tp)
+    sample = (f"every step is the whole {args.tokens}-token causal sequence through the full-width layer"
+              + (f", its {tp} tensor-parallel shards emulated one after the other with the crate's f16 tree all_reduce" if tp > 1 else "")
+              + "; restated common_cpu operators (the Rust crate cannot be built here: no rustc/cargo)")
     line = {"impl": "reference", "metric": "layer_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic", "config": {"workload": WORKLOAD, "sample_tokens": tokens},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                             "sample": sample + "; restated common_cpu operators (the Rust crate cannot be built here: no rustc/cargo)"},
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic", "config": config_for(tp, args.tokens),
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -307,26 +433,30 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--ref-tokens", type=int, default=512, help="tokens per step of the CPU arm")
-    ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-operator measurements of configs 1, 2, 4 and 5")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long sustained legs")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--sustain-seconds", type=float, default=2.0)
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
+    ap.add_argument("--no-direct", action="store_true", help="tensor parallel: stage the partials instead of the zero-copy exchange with the residual folded in")
+    ap.add_argument("--pipeline", type=int, default=2, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
     ap.add_argument("--overlap-chunks", type=int, default=1, help="token chunks of the row-parallel projections whose all_reduce overlaps the next chunk's GEMM")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
     if args.warmup < 3:
         args.warmup = 3
 
+    import numpy as np
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path (use --impl reference for the CPU arm)")
@@ -336,20 +466,24 @@ def main():
     assert tp == max(args.gpus, 1) or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    comm = None
+    comms = []
     dist = None
+    pipeline = max(1, args.pipeline) if (tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct and args.overlap_chunks == 1) else 1
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-        ids = [pkg.Comm.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        comm = pkg.Comm(local_rank, rank, world, ids[0])
-        if args.all_reduce in ("auto", "one_shot", "two_shot", "fused"):
-            handle = comm.p2p_export(args.tokens * CFG["d"] * 2)
-            handles = [None] * world
-            dist.all_gather_object(handles, handle)
-            comm.p2p_attach(handles)
+        for lane in range(pipeline):  # one communicator per stream of the pipelined tail
+            ids = [pkg.Comm.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            c = pkg.Comm(local_rank, rank, world, ids[0])
+            if args.all_reduce != "nccl":
+                handle = c.p2p_export(args.tokens * CFG["d"] * 2)
+                handles = [None] * world
+                dist.all_gather_object(handles, handle)
+                c.p2p_attach(handles)
+            comms.append(c)
+    comm = comms[0] if comms else None
     algo = {"auto": pkg.ALL_REDUCE_AUTO, "nccl": pkg.ALL_REDUCE_NCCL, "one_shot": pkg.ALL_REDUCE_P2P_ONE_SHOT,
             "two_shot": pkg.ALL_REDUCE_P2P_TWO_SHOT, "fused": pkg.ALL_REDUCE_AUTO}[args.all_reduce]
 
@@ -357,11 +491,9 @@ def main():
     T = args.tokens
     full = make_weights(torch, device, CFG)
     shard = layer_mod.shard_weights(full, rank, tp, cfg) if tp > 1 else full
-    if tp > 1:
-        del full
-        torch.cuda.empty_cache()
-    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks,
-                                   fused_all_reduce=args.all_reduce == "fused")
+    direct = tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct
+    layer = layer_mod.DecoderLayer(cfg, shard, T, device, comms=comms or None, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks,
+                                   fused_all_reduce=args.all_reduce == "fused", direct=direct, pipeline=pipeline)
     g = torch.Generator(device=device).manual_seed(SEED + 7)
     x0 = torch.randn(T, CFG["d"], generator=g, device=device, dtype=torch.float32).half()
     x = torch.empty_like(x0)
@@ -382,13 +514,23 @@ def main():
         step()
     barrier()
 
-    # ---- timed region 1: device-resident inputs, events around every operator -------------------------------
+    # ---- timed region 1: device-resident inputs, the chain as a caller runs it ---------------------------------
     sampler = ClockSampler(local_rank)
-    names = [n for n in layer.STEPS if tp > 1 or not n.startswith("all_reduce")]
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_begin.record(stream)
+    for s in range(args.steps):
+        step()
+    t_end.record(stream)
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+
+    # ---- timed region 1b: the same steps with an event after every operator (per-operator table) ----------------
+    names = [n for n in layer.STEPS if tp > 1 or not n.startswith("all_reduce")]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
+    m_begin, m_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    m_begin.record(stream)
     for s in range(args.steps):
         copy.launch(pkg.RearrangeArgs.of(x, x0))
         ev[s][0].record(stream)
@@ -399,42 +541,43 @@ def main():
             ev[s][k[0]].record(stream)
 
         layer.forward(x, pos, mark)
-    t_end.record(stream)
+    m_end.record(stream)
     barrier()
-    total_ms = t_begin.elapsed_time(t_end)
+    marked_ms = m_begin.elapsed_time(m_end)
 
     # ---- timed region 2: end to end through the public API with host buffers ---------------------------------
-    # Every step copies its activations from pinned host memory and returns its result to pinned host memory.  With
-    # one GPU the three legs run on three streams over two device buffers, so the copy of step i+1 and the read-back
-    # of step i-1 overlap the chain of step i (what a caller streaming batches through the layer does); under tensor
-    # parallelism the legs stay in one stream.
-    xh = x0.cpu().pin_memory()
-    outh = [torch.empty_like(xh).pin_memory() for _ in range(2)]
+    # Every step brings its activations from pinned host memory and returns its result to pinned host memory.  Three
+    # streams over two device buffers: the upload of step i+1 and the read-back of step i-1 overlap the chain of step
+    # i (what a caller streaming batches through the layer does).  With N ranks each rank uploads the 1/N of the rows
+    # it is given, the ranks exchange them over NVLink (one all-gather on the chain's stream), and rank 0 alone reads
+    # the result back: every rank ends with the same bits.
+    rows_lo, rows_hi = (T * rank) // tp, (T * (rank + 1)) // tp
+    xh = x0[rows_lo:rows_hi].cpu().pin_memory()
+    outh = [torch.empty(T, CFG["d"], dtype=torch.float16).pin_memory() for _ in range(2)] if rank == 0 else None
     xs = [x, torch.empty_like(x)]
+    slices = [torch.empty(rows_hi - rows_lo, CFG["d"], dtype=torch.float16, device=device) for _ in range(2)] if tp > 1 else None
     s_in, s_run, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device)
 
     def e2e_pass(nsteps):
-        if tp > 1:
-            for i in range(nsteps):
-                xs[0].copy_(xh, non_blocking=True)
-                outh[0].copy_(layer.forward(xs[0], pos), non_blocking=True)
-            return
         copied, ran, read = {}, {}, {}
         for i in range(nsteps):
             b = i & 1
             with torch.cuda.stream(s_in):
                 if i >= 2:
-                    s_in.wait_event(read[i - 2])  # the buffer is free once step i-2 has been read back
-                xs[b].copy_(xh, non_blocking=True)
+                    s_in.wait_event(ran[i - 2] if rank != 0 else read[i - 2])  # the buffer is free once step i-2 is done with it
+                (slices[b] if tp > 1 else xs[b]).copy_(xh, non_blocking=True)
                 copied[i] = s_in.record_event()
             with torch.cuda.stream(s_run):
                 s_run.wait_event(copied[i])
+                if tp > 1:
+                    dist.all_gather_into_tensor(xs[b], slices[b])
                 out = layer.forward(xs[b], pos)
                 ran[i] = s_run.record_event()
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ran[i])
-                outh[b].copy_(out, non_blocking=True)
-                read[i] = s_out.record_event()
+            if rank == 0:
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ran[i])
+                    outh[b].copy_(out, non_blocking=True)
+                    read[i] = s_out.record_event()
         for st in (s_in, s_run, s_out):
             stream.wait_stream(st)
 
@@ -451,13 +594,41 @@ def main():
     clocks = sampler.stop()
 
     if dist is not None:
-        tt = torch.tensor([total_ms, e2e_ms], device=device, dtype=torch.float64)
+        tt = torch.tensor([total_ms, e2e_ms, marked_ms], device=device, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = float(tt[0]), float(tt[1])
+        total_ms, e2e_ms, marked_ms = float(tt[0]), float(tt[1]), float(tt[2])
 
-    # per-operator durations (this rank), averaged over the timed steps
+    # ---- parity: the layer as timed (same handles, same exchange) on a 512-token input, against the CPU oracle ------
+    parity = None
+    if not args.no_parity:
+        Tp = min(PARITY_TOKENS, T)
+        gp = torch.Generator(device=device).manual_seed(SEED + 11)
+        xp = torch.randn(Tp, CFG["d"], generator=gp, device=device, dtype=torch.float32).half()
+        xp_host = xp.cpu().numpy().copy()
+        outp = layer.forward(xp, pos[:Tp]).clone()
+        torch.cuda.synchronize()
+        identical = True
+        if dist is not None:
+            gathered = [torch.empty_like(outp) for _ in range(tp)]
+            dist.all_gather(gathered, outp)
+            identical = all(bool(torch.equal(gathered[0], t_)) for t_ in gathered[1:])
+        status = {"mat_mul": layer.mat_mul.status(), "attention": layer.attention.status(), "p2p": comm.p2p_status() if (comm and args.all_reduce != "nccl") else 0}
+        if rank == 0:
+            orc = graft.load_oracle()
+            orc.lib()
+            orc.set_num_threads(host_threads())
+            wn = {k_: v_.cpu().numpy() for k_, v_ in full.items()}
+            shards_np = [layer_mod.shard_weights(wn, r, tp, cfg) for r in range(tp)]
+            ref = orc.decoder_layer(xp_host, np.arange(Tp, dtype=np.uint32), shards_np, CFG)
+            max_abs = float(np.abs(outp.cpu().numpy().astype(np.float32) - ref.astype(np.float32)).max())
+            parity = {"tokens": Tp, "max_abs": max_abs, "tolerance": 1e-2, "ok": bool(max_abs <= 1e-2 and identical), "ranks_identical": identical,
+                      "against": "CPU oracle chain (restated common_cpu operators) on the same shards", "kernel_status": status}
+    del full
+
+    # per-operator durations (this rank), averaged over the marked steps
     op_ms = {n: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps for i, n in enumerate(names)}
     peaks = measured_peaks()
+    clock_scale = (clocks.get("sm_mhz") or peaks["sm_max_mhz"]) / peaks["sm_max_mhz"]
     E = 2
     d, ffn_l, nq, nkv, dh = CFG["d"], CFG["ffn"] // tp, CFG["nh"] // tp, CFG["nkvh"] // tp, CFG["dh"]
     qkv_cols = (nq + 2 * nkv) * dh
@@ -480,24 +651,37 @@ def main():
             ops[n] = {"ms": ms, "bound": "hbm", "achieved": ach, "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
         elif kind == "tensor":
             ach = amount / (ms * 1e-3) / 1e12
-            ops[n] = {"ms": ms, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tflops_sustained"]}
+            # one denominator for every tensor-bound operator: the measured burst peak (the timed region lasts tens of
+            # milliseconds); beside it the nominal dense f16 peak scaled to the SM clock sampled during the run
+            ops[n] = {"ms": ms, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tflops_burst"],
+                      "frac_of_nominal_at_sampled_clock": ach / (NOMINAL_F16_TFLOPS * clock_scale)}
         else:
             ach = amount / (ms * 1e-3) / 1e9
             ops[n] = {"ms": ms, "bound": "nvlink", "achieved": ach, "unit": "GB/s (bus)", "frac": ach / 770.0}
     dom = ops["mat_mul_gate_up"]
+    traffic = measured_traffic()
+    traffic_bytes = None
+    if traffic and tp == 1 and T == 4096 and traffic.get("tokens") == 4096:
+        traffic_bytes = traffic.get("dram_bytes_per_launch")
     roofline = {"kernel": "gemm_f16_tcgen05_kernel<256> (mat_mul gate|up launch)", "bound": "tensor", "achieved": dom["achieved"],
-                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": dom["frac"],
-                # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the one-pass ncu capture summarised in
-                # profiles/layer_config3_dram_traffic.md (296.8 MB + 210.8 MB); only known for the config-3 shape
-                "traffic": 507593472 if (tp == 1 and T == 4096) else None,
-                "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (kernel timed inside a long step)",
+                "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": dom["frac"], "traffic": traffic_bytes,
+                "traffic_source": traffic, "peak_source": f"{peaks['source']} cuBLAS bf16 burst (the timed region lasts tens of milliseconds)",
                 "algorithmic_flops_per_launch": work["mat_mul_gate_up"][1]}
+    if not args.no_sustained:
+        hs, gus = layer.h[:T], layer.gu[:T]
+        ga = pkg.MatMulArgs.of(gus, 0.0, hs, shard["w_gu"], 1.0)
+        roofline["sustained"] = sustained_leg(torch, local_rank, lambda: layer.mat_mul.launch(ga), work["mat_mul_gate_up"][1], args.sustain_seconds, peaks)
+        heads = layer.qkv[:T].view(T, nq + 2 * nkv, dh)
+        aa = pkg.AttentionArgs.of(heads[:, :nq].permute(1, 0, 2), heads[:, nq:nq + nkv].permute(1, 0, 2), heads[:, nq + nkv:].permute(1, 0, 2),
+                                  layer.att_out[:T].view(T, nq, dh).permute(1, 0, 2), pkg.MASK_CAUSAL)
+        roofline["attention_sustained"] = sustained_leg(torch, local_rank, lambda: layer.attention.launch(aa, layer.ws), work["attention"][1],
+                                                        args.sustain_seconds, peaks)
 
     extras = None
     if not args.no_extras:
         del layer
         torch.cuda.empty_cache()
-        extras = extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank)
+        extras = extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank, comms)
 
     if rank != 0:
         if comm is not None:
@@ -505,30 +689,37 @@ def main():
             dist.destroy_process_group()
         return
     ms_per_step = total_ms / args.steps
-    kernels_per_step = 1 + 2 + 4 + 1 + 1 + 1  # residual reset copy, rms_norm x2, mat_mul x4, rope, swiglu, fused attention
-    if tp > 1 and args.all_reduce != "nccl":
-        kernels_per_step += 2
+    # kernels of this library per step: residual reset copy, rms_norm x2, mat_mul x4, rope, swiglu, fused attention, and
+    # under tensor parallelism the two exchange kernels (none of ours when NCCL does the all_reduce); the pipelined tail
+    # runs its seven launches once per row chunk
+    tail = 5 + (2 if (tp > 1 and args.all_reduce != "nccl") else 0)
+    kernels_per_step = 1 + 4 + tail * (pipeline if tp > 1 else 1)
+    config = config_for(tp, T)
     line = {
         "metric": "layer_tokens_per_s", "value": T * args.steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD if tp == 1 else WORKLOAD.replace("config 3", "config 4") + f", tensor-parallel over {tp} GPUs",
-                   "tokens": T, "parallelism": f"tp{tp}", "all_reduce": args.all_reduce if tp > 1 else None,
-                   "l2": "inputs larger than L2: every step streams 436 MB of weights and ~0.6 GB of activations through a 126 MB L2",
-                   "attention": "fused flash-attention kernel behind attention::Args (the crate's operator chain is measured in other_configs)"},
+        "dtype": "f16", "data": "synthetic", "config": config,
+        "run": {"all_reduce": args.all_reduce if tp > 1 else None, "exchange": ("zero-copy partials + residual folded into the all_reduce kernel" if direct else "staged") if tp > 1 else None,
+                "pipeline_chunks": pipeline if tp > 1 else None,
+                "attention": "fused flash-attention kernel behind attention::Args (the crate's operator chain is measured in other_configs)",
+                "ms_per_step_with_per_operator_events": marked_ms / args.steps},
         "clocks": clocks,
         "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * d * E, "d2h_bytes_per_step": T * d * E,
-                "ms_per_step": e2e_ms / args.steps},
+                "ms_per_step": e2e_ms / args.steps,
+                "how": "pinned host buffers; upload, chain and read-back pipelined over three streams"
+                       + (f"; each of the {tp} ranks uploads its 1/{tp} of the rows, one NVLink all-gather, rank 0 reads the result back" if tp > 1 else "")},
         "gpu_launches": kernels_per_step * args.steps,
         "roofline": roofline,
         "ops": ops,
     }
+    if parity is not None:
+        line["parity"] = parity
     if extras is not None:
         line["other_configs"] = extras
     if tp == 1 and not args.no_cpu_baseline:
-        tps, threads, sec = cpu_layer_baseline(args.cpu_tokens, 1, 0)
+        tps, threads, sec = cpu_layer_baseline(T, 1, 0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                "sample": f"one pass over a {args.cpu_tokens}-token causal sequence through the full-width layer "
+                                "sample": f"one pass over the same {T}-token causal sequence through the full-width layer "
                                           f"({sec:.1f} s); restated common_cpu operators (the Rust crate cannot be built here)"}
     print(json.dumps(line), flush=True)
     if comm is not None:

@@ -95,7 +95,7 @@ const char *ops_build_info(void);          /* "sm_100a ..." */
 /* ---------------------------------------------------------------------------------------------
  * rms_norm — rms_norm::Args (operators/src/rms_norm/args.rs:7-15); replaces
  * rms_norm::common_cpu::Operator (operators/src/rms_norm/common_cpu/mod.rs:10-93).
- * y[i,j] = x[i,j] * w[j] / sqrt(mean_j(x[i,:]^2) + epsilon); y,x f16 or f32, w f16 or f32.
+ * y[i,j] = x[i,j] * w[j] / sqrt(mean_j(x[i,:]^2) + epsilon); y,x f16, bf16 or f32, w of the same type or f32.
  * ------------------------------------------------------------------------------------------- */
 typedef struct ops_rms_norm ops_rms_norm;
 typedef struct {
@@ -108,6 +108,15 @@ int ops_rms_norm_create(int device, ops_rms_norm **out);
 int ops_rms_norm_scheme(ops_rms_norm *op, const ops_rms_norm_args *args, size_t max_ws, size_t *ws_out);
 int ops_rms_norm_launch(const ops_rms_norm *op, const ops_rms_norm_args *args, void *ws, size_t ws_len, void *stream);
 void ops_rms_norm_destroy(ops_rms_norm *op);
+/* Extension with no counterpart in the crate, which chains add (operators/src/add/common_cpu/mod.rs:29-75) and rms_norm as
+ * two operators: x <- x + r in place (rounded to the element type as add rounds), then y <- rms_norm(x), in one pass over
+ * every row.  f16 or bf16 rows with unit inner stride, 16-byte aligned, d a multiple of 8 up to 32768; other layouts are
+ * answered with OPS_ARGS_NOT_SUPPORT (chain ops_add_launch and ops_rms_norm_launch then). */
+typedef struct {
+  ops_rms_norm_args norm;               /* y, x (read and written), w, epsilon */
+  ops_layout r_layout; const void *r_base; /* what is added to x first: same shape and type as x */
+} ops_rms_norm_add_args;
+int ops_rms_norm_add_launch(const ops_rms_norm *op, const ops_rms_norm_add_args *args, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * rope — rope::Args (operators/src/rope/args.rs:8-18); replaces rope::common_cpu::Operator
@@ -294,7 +303,8 @@ int ops_random_sample_launch_batched(const ops_random_sample *op, uint32_t dt, s
  * process with a fixed memory budget): it takes no workspace.  The scratch is a fixed 2 MiB array inside the
  * library's device image, enough for one row of up to ops_random_sample_noalloc_max_logits() = 131072 logits; longer
  * rows are refused with OPS_SHAPE_NOT_SUPPORT.  Nothing is allocated or freed, here or in any routine it calls.
- * The first call on a device looks up the array's device address; make that first call before any stream capture.
+ * The array's device address is looked up when a random_sample handle is created on the device (if that failed, by
+ * the first call, which should then come before any stream capture).
  * All calls on a device share the array: calls that overlap on the GPU race, so keep them on one stream or order
  * them yourself.  Results are identical to ops_random_sample_launch. */
 size_t ops_random_sample_noalloc_max_logits(void);
@@ -316,15 +326,27 @@ int ops_comm_rank(const ops_comm *c);
 int ops_comm_group_size(const ops_comm *c);
 void ops_comm_destroy(ops_comm *c);
 /* Peer-to-peer (NVLink) path: each rank allocates a symmetric staging buffer inside the library,
- * exports an IPC handle (64 bytes) per rank, the caller all-gathers the handles (group_size*64
- * bytes, rank order) and hands them back.  After _p2p_attach the all_reduce operator may use the
- * one-shot / two-shot kernels; before it, NCCL only. */
+ * exports one handle of OPS_COMM_P2P_HANDLE_BYTES bytes, the caller all-gathers the handles
+ * (group_size * OPS_COMM_P2P_HANDLE_BYTES bytes, rank order) and hands them back.  After _p2p_attach
+ * the all_reduce operator may use the one-shot / two-shot kernels; before it, NCCL only.
+ * `staging_bytes` is the largest message the peer-to-peer kernels will be given; the library holds
+ * five regions of that size (double-buffered input and output staging, and the zero-copy input region).
+ * The launch counter that tells the ranks' launches apart lives on the device and is advanced by the
+ * kernels, so a launch recorded in a CUDA graph stays correct when the graph is replayed, provided
+ * every rank replays the same sequence. */
 #define OPS_COMM_P2P_HANDLE_BYTES 128
 int ops_comm_p2p_export(ops_comm *c, size_t staging_bytes, uint8_t handle_out[OPS_COMM_P2P_HANDLE_BYTES]);
 int ops_comm_p2p_attach(ops_comm *c, const uint8_t *all_handles /* group_size * OPS_COMM_P2P_HANDLE_BYTES */);
-/* Status word of the last P2P kernel on this rank: 0 ok, else a bounded wait ran out
- * (read after the stream is synchronised). */
+/* Status word of the P2P kernels on this rank: 0 ok, else a bounded wait ran out (read after the
+ * stream is synchronised); the first failure sticks.  The output of a launch that set it is undefined. */
 int ops_comm_p2p_status(ops_comm *c);
+/* Start over after a time-out: once every rank's streams are idle and the ranks have met at a
+ * host-side barrier, each rank calls this; status word, launch counter and all flags return to zero. */
+int ops_comm_p2p_reset(ops_comm *c);
+/* The zero-copy input region of this rank (staging_bytes long).  A kernel that writes its partial
+ * there — the same offset on every rank — lets ops_all_reduce_launch / ops_all_reduce_add_launch read
+ * it in place when given that pointer as src: no copy-in.  No counterpart in the crate. */
+int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out);
 /* Test aid with no counterpart in the crate: a communicator of `group_size` ranks that all map this rank's own staging
  * buffer.  Its peers never run, so a peer-to-peer all_reduce on it ends through its bounded waits (about one second)
  * with a non-zero ops_comm_p2p_status and an intact context: the time-out path can be exercised on one GPU. */
@@ -341,6 +363,11 @@ int ops_all_reduce_set_algo(ops_all_reduce *op, int algo);
 int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args *args, size_t max_ws, size_t *ws_out);
 int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream);
 void ops_all_reduce_destroy(ops_all_reduce *op);
+/* Extension with no counterpart in the crate, which chains all_reduce and add (operators/src/add/common_cpu/mod.rs:29-75):
+ * dst <- dst + sum over ranks of src in one kernel.  dst must hold the same values on every rank (a replicated residual
+ * stream) and differ from src; f16/bf16/f32, peer-to-peer staging attached, >= 2 ranks; OPS_ARGS_NOT_SUPPORT otherwise
+ * (chain ops_all_reduce_launch and ops_add_launch then).  The old dst enters the f32 sum first, then the ranks in order. */
+int ops_all_reduce_add_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *stream);
 
 /* No counterpart in the crate (it chains mat_mul and all_reduce as two operators): C <- beta*C + alpha*A*B followed by
  * the f16 sum all_reduce of C over the group of `node`, as ONE kernel — finished tiles cross NVLink while the tensor

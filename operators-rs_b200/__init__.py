@@ -221,6 +221,7 @@ _RandomSampleArgs = _struct("_RandomSampleArgs", [("kv_pair", _Layout), ("kv_pai
                                                   ("seed", ctypes.c_float)])
 _AllReduceArgs = _struct("_AllReduceArgs", [("pair", _RearrangeArgs), ("op", ctypes.c_uint8)])
 _BroadcastArgs = _struct("_BroadcastArgs", [("pair", _RearrangeArgs), ("root", ctypes.c_size_t)])
+_RmsNormAddArgs = _struct("_RmsNormAddArgs", [("norm", _RmsNormArgs), ("r_layout", _Layout), ("r_base", ctypes.c_void_p)])
 _AddArgs = _struct("_AddArgs", [("c_layout", _Layout), ("c_base", ctypes.c_void_p), ("a_layout", _Layout), ("a_base", ctypes.c_void_p),
                                 ("b_layout", _Layout), ("b_base", ctypes.c_void_p)])
 _AddRowsArgs = _struct("_AddRowsArgs", [("dst_layout", _Layout), ("dst_base", ctypes.c_void_p), ("src_layout", _Layout),
@@ -242,6 +243,20 @@ class RmsNormArgs(_ArgsBase):
     @classmethod
     def of(cls, y, x, w, epsilon):
         return cls(y, y, x, x, w, w, epsilon)
+
+
+class RmsNormAddArgs(_ArgsBase):
+    """Arguments of the extension ops_rms_norm_add_launch: x <- x + r in place, then y <- rms_norm(x)."""
+
+    def __init__(self, y, x, w, epsilon, r):
+        self.norm = RmsNormArgs.of(y, x, w, epsilon)
+        self._alive = (r,)
+        self.keep = (_lay(r),)
+        self.c = _RmsNormAddArgs(self.norm.c, self.keep[0].c, _vp(r))
+
+    @classmethod
+    def of(cls, y, x, w, epsilon, r):
+        return cls(y, x, w, epsilon, r)
 
 
 class RopeArgs(_ArgsBase):
@@ -510,6 +525,12 @@ class Operator:
 class RmsNorm(Operator):
     NAME = "rms_norm"
 
+    def launch_add(self, args, queue_alloc=None):
+        """ops_rms_norm_add_launch: the residual add in front of the norm folded into it (one pass over every row)."""
+        qa = queue_alloc or TorchQueueAlloc()
+        self._last_args = args
+        _check(lib().ops_rms_norm_add_launch(self._h, args.byref(), ctypes.c_void_p(qa.queue())), True)
+
 
 class Rope(Operator):
     NAME = "rope"
@@ -662,6 +683,24 @@ class Comm:
     def p2p_status(self):
         return lib().ops_comm_p2p_status(self._h)
 
+    def p2p_reset(self):
+        """ops_comm_p2p_reset: start over after a time-out (every rank, streams idle, after a host-side barrier)."""
+        _check(lib().ops_comm_p2p_reset(self._h), False)
+
+    def p2p_direct(self, dtype=None):
+        """The zero-copy input region of this rank as a torch tensor (uint8, or `dtype`) that aliases it: a kernel that
+        writes its partial there lets all_reduce read it in place (ops_comm_p2p_direct)."""
+        import torch
+        ptr, size = ctypes.c_void_p(), ctypes.c_size_t()
+        _check(lib().ops_comm_p2p_direct(self._h, ctypes.byref(ptr), ctypes.byref(size)), False)
+
+        class _Region:  # the CUDA array interface is how torch is told about memory it did not allocate
+            __cuda_array_interface__ = {"shape": (size.value,), "typestr": "|u1", "data": (ptr.value, False), "version": 2}
+
+        t = torch.as_tensor(_Region(), device=torch.device("cuda", self.device))
+        self._direct_owner = t
+        return t if dtype is None else t.view(dtype)
+
     def destroy(self):
         h, self._h = self._h, None
         if h and h.value:
@@ -678,6 +717,12 @@ class AllReduce(Operator):
 
     def set_algo(self, algo):
         _check(lib().ops_all_reduce_set_algo(self._h, ctypes.c_int(algo)), False)
+
+    def launch_add(self, args, queue_alloc=None):
+        """ops_all_reduce_add_launch: dst <- dst + sum over ranks of src, one kernel (dst replicated, dst is not src)."""
+        qa = queue_alloc or TorchQueueAlloc()
+        self._last_args = args
+        _check(lib().ops_all_reduce_add_launch(self._h, args.byref(), ctypes.c_void_p(qa.queue())), True)
 
 
 class Broadcast(Operator):
@@ -710,5 +755,6 @@ EXPORTS = [
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
-    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_comm_create_loopback", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
+    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_comm_p2p_reset", "ops_comm_p2p_direct", "ops_all_reduce_add_launch",
+    "ops_rms_norm_add_launch", "ops_comm_create_loopback", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
 ]

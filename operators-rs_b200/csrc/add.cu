@@ -6,6 +6,7 @@
 // add_rows::common_cpu::Operator (operators/src/add_rows/common_cpu/mod.rs:35-148, checks add_rows/args.rs:46-81).
 // Both HBM-bound (3 resp. 3 element streams); rows with a contiguous last dim move as 128-bit vectors.
 #include <algorithm>
+#include <type_traits>
 #include <vector>
 
 #include "common.h"
@@ -40,17 +41,18 @@ __device__ __forceinline__ void add_locate(const AddParams &p, unsigned long lon
   }
 }
 
+template <class E>
 __global__ void __launch_bounds__(256) add_vec_kernel(const __grid_constant__ AddParams p) {
   const unsigned long long i = blockIdx.x * 256ull + threadIdx.x;
   if (i >= p.total) return;
   long long oc, oa, ob;
   unsigned int in;
   add_locate(p, i, oc, oa, ob, in);
-  Pack8 x, y, z;
+  Vec8<E> x, y, z;
   x.u = ld_global_16(p.a + oa + 16ll * in);
   y.u = ld_global_16(p.b + ob + 16ll * in);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) z.h[e] = __float2half_rn(__fadd_rn(__half2float(x.h[e]), __half2float(y.h[e])));
+  for (int e = 0; e < 8; ++e) z.h[e] = from_f32<E>(__fadd_rn(to_f32(x.h[e]), to_f32(y.h[e])));
   st_global_16(p.c + oc + 16ll * in, z.u);
 }
 
@@ -80,12 +82,13 @@ __global__ void __launch_bounds__(256) add_rows_kernel(T *dst, long long bsd, lo
   const T *s = byte_off(src, (long long)id * kss);
   if (vec) {
     for (unsigned int v = blockIdx.y * 256u + threadIdx.x; v < n / 8; v += gridDim.y * 256u) {
-      Pack8 x, y;
-      x.u = ld_global_16(reinterpret_cast<const __half *>(d) + v * 8);
-      y.u = ld_global_16(reinterpret_cast<const __half *>(s) + v * 8);
+      typedef typename std::conditional<sizeof(T) == 2, T, __half>::type E;  // the vector path is only taken by 16-bit types
+      Vec8<E> x, y;
+      x.u = ld_global_16(reinterpret_cast<const E *>(d) + v * 8);
+      y.u = ld_global_16(reinterpret_cast<const E *>(s) + v * 8);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x.h[e] = __float2half_rn(__fadd_rn(__half2float(x.h[e]), __half2float(y.h[e])));
-      st_global_16(reinterpret_cast<__half *>(d) + v * 8, x.u);
+      for (int e = 0; e < 8; ++e) x.h[e] = from_f32<E>(__fadd_rn(to_f32(x.h[e]), to_f32(y.h[e])));
+      st_global_16(reinterpret_cast<E *>(d) + v * 8, x.u);
     }
   } else {
     for (unsigned int j = blockIdx.y * 256u + threadIdx.x; j < n; j += gridDim.y * 256u) {
@@ -120,7 +123,7 @@ OPS_API int ops_add_launch(const ops_add *op, const ops_add_args *a, void *ws, s
   (void)ws_len;
   OPS_TRY(add_check(a));
   const uint32_t dt = a->c_layout.dt;
-  if (dt != OPS_DT_F16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "add: f16 or f32 expected");
+  if (dt != OPS_DT_F16 && dt != OPS_DT_BF16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "add: f16, bf16 or f32 expected");
   const isz es = (isz)dt_size(dt);
   struct Dim {
     usz d;
@@ -157,7 +160,7 @@ OPS_API int ops_add_launch(const ops_add *op, const ops_add_args *a, void *ws, s
   dims.pop_back();
   p.ndim = (int)dims.size();
   unsigned long long outer = 1;
-  bool vec = dt == OPS_DT_F16 && in.c == es && in.a == es && in.b == es && in.d % 8 == 0 && aligned(p.c, 16) && aligned(p.a, 16) && aligned(p.b, 16);
+  bool vec = (dt == OPS_DT_F16 || dt == OPS_DT_BF16) && in.c == es && in.a == es && in.b == es && in.d % 8 == 0 && aligned(p.c, 16) && aligned(p.a, 16) && aligned(p.b, 16);
   for (int i = 0; i < p.ndim; ++i) {
     if (dims[i].d > 0xffffffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "add: dim too long");
     p.len[i] = (unsigned int)dims[i].d;
@@ -177,8 +180,10 @@ OPS_API int ops_add_launch(const ops_add *op, const ops_add_args *a, void *ws, s
   if (blocks > 0x7fffffffull) return fail(OPS_SHAPE_NOT_SUPPORT, "add: tensor too large");
   cudaStream_t s = (cudaStream_t)stream;
   cudaSetDevice(op->base.device);
-  if (vec) add_vec_kernel<<<(unsigned)blocks, 256, 0, s>>>(p);
+  if (vec && dt == OPS_DT_F16) add_vec_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(p);
+  else if (vec) add_vec_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(p);
   else if (dt == OPS_DT_F16) add_generic_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(p);
+  else if (dt == OPS_DT_BF16) add_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(p);
   else add_generic_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(p);
   return check_launch("add");
 }
@@ -259,14 +264,14 @@ OPS_API int ops_add_rows_launch(const ops_add_rows *op, const ops_add_rows_args 
   const isz *sd = a->dst_layout.strides, *ss = a->src_layout.strides, *si = a->idx_layout.strides;
   if (dyn(mt.batch) || dyn(mt.m) || dyn(mt.n) || dyn(mt.k) || dyn(sd[0]) || dyn(sd[1]) || dyn(sd[2]) || dyn(ss[0]) || dyn(ss[1]) || dyn(si[0]) || dyn(si[1]))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "add_rows: every shape and stride must be static at launch");
-  if (mt.dt != OPS_DT_F16 && mt.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "add_rows: f16 or f32 expected");
+  if (mt.dt != OPS_DT_F16 && mt.dt != OPS_DT_BF16 && mt.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "add_rows: f16, bf16 or f32 expected");
   if (mt.dt_idx != OPS_DT_U32 && mt.dt_idx != OPS_DT_U64) return fail(OPS_TYPE_NOT_SUPPORT, "add_rows: idx must be u32 or u64");
   if (mt.batch == 0 || mt.m == 0 || mt.n == 0) return OPS_OK;
   if (mt.batch * mt.m > 0x7fffffffu || mt.n > 0xffffffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "add_rows: shape too large");
   if (!a->dst_base || !a->src_base || !a->idx_base) return fail(OPS_DYNAMIC_NOT_SUPPORT, "add_rows: null base pointer at launch");
   cudaStream_t s = (cudaStream_t)stream;
   cudaSetDevice(op->base.device);
-  const int vec = mt.dt == OPS_DT_F16 && sd[2] == 2 && ss[1] == 2 && mt.n % 8 == 0 && sd[0] % 16 == 0 && sd[1] % 16 == 0 && ss[0] % 16 == 0 &&
+  const int vec = (mt.dt == OPS_DT_F16 || mt.dt == OPS_DT_BF16) && sd[2] == 2 && ss[1] == 2 && mt.n % 8 == 0 && sd[0] % 16 == 0 && sd[1] % 16 == 0 && ss[0] % 16 == 0 &&
                   aligned(a->dst_base, 16) && aligned(a->src_base, 16);
   const unsigned per_row = (unsigned)std::min<usz>(8, ((vec ? mt.n / 8 : mt.n) + 255) / 256);
   dim3 grid((unsigned)(mt.batch * mt.m), per_row);
@@ -275,6 +280,8 @@ OPS_API int ops_add_rows_launch(const ops_add_rows *op, const ops_add_rows_args 
                                               si[1], (unsigned)mt.m, (unsigned)mt.n, (unsigned long long)mt.k, vec, op->status_dev)
   if (mt.dt == OPS_DT_F16 && mt.dt_idx == OPS_DT_U32) ADD_ROWS(__half, uint32_t);
   else if (mt.dt == OPS_DT_F16) ADD_ROWS(__half, unsigned long long);
+  else if (mt.dt == OPS_DT_BF16 && mt.dt_idx == OPS_DT_U32) ADD_ROWS(__nv_bfloat16, uint32_t);
+  else if (mt.dt == OPS_DT_BF16) ADD_ROWS(__nv_bfloat16, unsigned long long);
   else if (mt.dt_idx == OPS_DT_U32) ADD_ROWS(float, uint32_t);
   else ADD_ROWS(float, unsigned long long);
 #undef ADD_ROWS

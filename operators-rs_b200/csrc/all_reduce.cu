@@ -108,6 +108,23 @@ template <> struct Acc8<__half> {
     return o.u;
   }
 };
+template <> struct Acc8<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void add(float *acc, uint4 raw) {
+    const __nv_bfloat16 *h = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(h[i]);
+  }
+  static __device__ __forceinline__ uint4 pack(const float *acc) {
+    union {
+      uint4 u;
+      __nv_bfloat16 h[8];
+    } o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.h[i] = __float2bfloat16_rn(acc[i]);
+    return o.u;
+  }
+};
 template <> struct Acc8<float> {
   static constexpr int N = 4;
   static __device__ __forceinline__ void add(float *acc, uint4 raw) {
@@ -125,9 +142,9 @@ template <> struct Acc8<float> {
 // One-shot: stage own input, tell the peers, wait for theirs, sum everything in rank order.
 // `vecs` = number of 16-byte vectors; CTA b owns vectors [b*per, (b+1)*per).
 template <class T>
-__global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
-                                                                  uint4 *__restrict__ dst, long long vecs) {
-  const unsigned int parity = a.epoch & 1u;
+__device__ __forceinline__ void one_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
+                                              long long vecs) {
+  const unsigned int parity = epoch & 1u;
   const long long per = (vecs + gridDim.x - 1) / gridDim.x;
   const long long lo = (long long)blockIdx.x * per, hi = min(vecs, lo + per);
   uint4 *mine = reinterpret_cast<uint4 *>(region_in(a.peers[a.rank], a.region_bytes, parity));
@@ -136,10 +153,10 @@ __global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_c
   __syncthreads();
   if ((int)threadIdx.x < a.size) {
     P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
-    st_release_sys(&pf->ready[a.rank][blockIdx.x], a.epoch);
+    st_release_sys(&pf->ready[a.rank][blockIdx.x], epoch);
   }
   const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
-  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, a.epoch, a.status, 1)) return;
+  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 1)) return;
   const uint4 *pin[MAX_RANKS];
 #pragma unroll
   for (int q = 0; q < MAX_RANKS; ++q) pin[q] = reinterpret_cast<const uint4 *>(region_in(a.peers[q < a.size ? q : 0], a.region_bytes, parity));
@@ -156,67 +173,107 @@ __global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_c
   }
 }
 
-// Two-shot: the message is cut into `size` parts of `part_vecs` vectors; CTA b owns slice b of every part.
 template <class T>
-__global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
-                                                                  uint4 *__restrict__ dst, long long vecs, long long part_vecs) {
-  const unsigned int parity = a.epoch & 1u;
+__global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+                                                                  uint4 *__restrict__ dst, long long vecs) {
+  const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
+  one_shot_body<T>(a, epoch, src, dst, vecs);
+  __syncthreads();
+  if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
+}
+
+// Two-shot: the message is cut into `size` parts of `part_vecs` vectors; CTA b owns slice b of every part.
+//   DIRECT: `src` already lies in this rank's "direct" region at byte offset `direct_off` (the same on every rank), so
+//           nothing is staged; peers are read at that offset of their direct regions.
+//   ADD:    dst <- dst + sum over ranks of src: the old value of dst (identical on every rank, e.g. a replicated residual
+//           stream) enters the f32 sum of the part this rank reduces, first, before rank 0's partial.
+template <class T, bool DIRECT, bool ADD>
+__device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
+                                              long long vecs, long long part_vecs, unsigned long long direct_off) {
+  const unsigned int parity = epoch & 1u;
   const long long per = (part_vecs + gridDim.x - 1) / gridDim.x;
   const long long s_lo = (long long)blockIdx.x * per, s_hi = min(part_vecs, s_lo + per);
-  uint4 *mine_in = reinterpret_cast<uint4 *>(region_in(a.peers[a.rank], a.region_bytes, parity));
   uint4 *mine_out = reinterpret_cast<uint4 *>(region_out(a.peers[a.rank], a.region_bytes, parity));
-  // stage slice b of every part (four vectors in flight per thread)
-  for (int part = 0; part < a.size; ++part) {
-    const long long base = (long long)part * part_vecs;
-    const long long stop = min(s_hi, vecs - base);
-    long long v = s_lo + threadIdx.x;
-    for (; v + 3 * blockDim.x < stop; v += 4 * blockDim.x) {
-      uint4 r[4];
+  if constexpr (!DIRECT) {
+    uint4 *mine_in = reinterpret_cast<uint4 *>(region_in(a.peers[a.rank], a.region_bytes, parity));
+    // stage slice b of every part (four vectors in flight per thread)
+    for (int part = 0; part < a.size; ++part) {
+      const long long base = (long long)part * part_vecs;
+      const long long stop = min(s_hi, vecs - base);
+      long long v = s_lo + threadIdx.x;
+      for (; v + 3 * blockDim.x < stop; v += 4 * blockDim.x) {
+        uint4 r[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) r[u] = src[base + v + u * blockDim.x];
+        for (int u = 0; u < 4; ++u) r[u] = src[base + v + u * blockDim.x];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) mine_in[base + v + u * blockDim.x] = r[u];
+        for (int u = 0; u < 4; ++u) mine_in[base + v + u * blockDim.x] = r[u];
+      }
+      for (; v < stop; v += blockDim.x) mine_in[base + v] = src[base + v];
     }
-    for (; v < stop; v += blockDim.x) mine_in[base + v] = src[base + v];
+    __threadfence_system();
   }
-  __threadfence_system();
   __syncthreads();
   if ((int)threadIdx.x < a.size) {
     P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
-    st_release_sys(&pf->ready[a.rank][blockIdx.x], a.epoch);
+    st_release_sys(&pf->ready[a.rank][blockIdx.x], epoch);
   }
   const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
-  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, a.epoch, a.status, 2)) return;
+  if (!wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 2)) return;
   // reduce my part, slice b: every peer's copy of a vector is requested before the first is consumed
   {
     const long long base = (long long)a.rank * part_vecs;
     const long long stop = min(s_hi, vecs - base);
     const uint4 *pin[MAX_RANKS];
 #pragma unroll
-    for (int q = 0; q < MAX_RANKS; ++q)
-      pin[q] = reinterpret_cast<const uint4 *>(region_in(a.peers[q < a.size ? q : 0], a.region_bytes, parity)) + base;
-    for (long long v = s_lo + threadIdx.x; v < stop; v += blockDim.x) {
-      uint4 raw[MAX_RANKS];
-#pragma unroll
-      for (int q = 0; q < MAX_RANKS; ++q)
-        if (q < a.size) raw[q] = ld_peer_16(pin[q] + v);
+    for (int q = 0; q < MAX_RANKS; ++q) {
+      char *pb = a.peers[q < a.size ? q : 0];
+      pin[q] = reinterpret_cast<const uint4 *>(DIRECT ? region_direct(pb, a.region_bytes) + direct_off : region_in(pb, a.region_bytes, parity)) + base;
+    }
+    auto reduce_one = [&](long long v, uint4 old, const uint4 (&raw)[MAX_RANKS]) {
       float acc[Acc8<T>::N] = {};
+      if constexpr (ADD) Acc8<T>::add(acc, old);
 #pragma unroll
       for (int q = 0; q < MAX_RANKS; ++q)
         if (q < a.size) Acc8<T>::add(acc, raw[q]);
       const uint4 r = Acc8<T>::pack(acc);
       mine_out[v] = r;
       dst[base + v] = r;
+    };
+    long long v = s_lo + threadIdx.x;
+    if (a.size <= 4) {  // few ranks: two vectors per peer in flight per thread
+      for (; v + blockDim.x < stop; v += 2 * blockDim.x) {
+        uint4 r0[MAX_RANKS], r1[MAX_RANKS], o0 = make_uint4(0, 0, 0, 0), o1 = o0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (q < a.size) {
+            r0[q] = ld_peer_16(pin[q] + v);
+            r1[q] = ld_peer_16(pin[q] + v + blockDim.x);
+          }
+        if constexpr (ADD) {
+          o0 = dst[base + v];
+          o1 = dst[base + v + blockDim.x];
+        }
+        reduce_one(v, o0, r0);
+        reduce_one(v + blockDim.x, o1, r1);
+      }
+    }
+    for (; v < stop; v += blockDim.x) {
+      uint4 raw[MAX_RANKS], old = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int q = 0; q < MAX_RANKS; ++q)
+        if (q < a.size) raw[q] = ld_peer_16(pin[q] + v);
+      if constexpr (ADD) old = dst[base + v];
+      reduce_one(v, old, raw);
     }
   }
   __threadfence_system();
   __syncthreads();
   if ((int)threadIdx.x < a.size) {
     P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
-    st_release_sys(&pf->reduced[a.rank][blockIdx.x], a.epoch);
+    st_release_sys(&pf->reduced[a.rank][blockIdx.x], epoch);
   }
-  if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, a.epoch, a.status, 3)) return;
-  // gather the other parts: one vector from every peer in flight per thread and trip
+  if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 3)) return;
+  // gather the other parts: one vector from every peer in flight per thread and trip (two with four ranks or fewer)
   {
     const uint4 *pout[MAX_RANKS];
     long long gbase[MAX_RANKS], gstop[MAX_RANKS];
@@ -227,7 +284,25 @@ __global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_c
       gbase[i] = (long long)q * part_vecs;
       gstop[i] = min(s_hi, vecs - gbase[i]);
     }
-    for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x) {
+    long long v = s_lo + threadIdx.x;
+    if (a.size <= 4) {
+      for (; v + blockDim.x < s_hi; v += 2 * blockDim.x) {
+        uint4 r0[3], r1[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i)
+          if (i < a.size - 1) {
+            if (v < gstop[i]) r0[i] = ld_peer_16(pout[i] + v);
+            if (v + blockDim.x < gstop[i]) r1[i] = ld_peer_16(pout[i] + v + blockDim.x);
+          }
+#pragma unroll
+        for (int i = 0; i < 3; ++i)
+          if (i < a.size - 1) {
+            if (v < gstop[i]) dst[gbase[i] + v] = r0[i];
+            if (v + blockDim.x < gstop[i]) dst[gbase[i] + v + blockDim.x] = r1[i];
+          }
+      }
+    }
+    for (; v < s_hi; v += blockDim.x) {
       uint4 raw[MAX_RANKS];
 #pragma unroll
       for (int i = 0; i < MAX_RANKS - 1; ++i)
@@ -237,6 +312,16 @@ __global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_c
         if (i < a.size - 1 && v < gstop[i]) dst[gbase[i] + v] = raw[i];
     }
   }
+}
+
+template <class T, bool DIRECT, bool ADD>
+__global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+                                                                  uint4 *__restrict__ dst, long long vecs, long long part_vecs,
+                                                                  unsigned long long direct_off) {
+  const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
+  two_shot_body<T, DIRECT, ADD>(a, epoch, src, dst, vecs, part_vecs, direct_off);
+  __syncthreads();
+  if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
 }
 
 struct AllReduceMeta {
@@ -401,7 +486,7 @@ OPS_API int ops_comm_p2p_export(ops_comm *c, size_t staging_bytes, uint8_t handl
   if (c->staging) return fail(OPS_ARGS_NOT_SUPPORT, "p2p staging already exported");
   cudaSetDevice(c->device);
   const size_t region = (staging_bytes + 255) / 256 * 256;
-  const size_t total = sizeof(P2PFlags) + 4 * region;
+  const size_t total = sizeof(P2PFlags) + (size_t)P2P_REGIONS * region;
   if (cudaMalloc(&c->staging, total) != cudaSuccess) {
     cudaGetLastError();
     c->staging = nullptr;
@@ -486,14 +571,24 @@ OPS_API int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args 
   return OPS_OK;
 }
 
+// Which path AUTO takes for a message of `bytes` over `p` ranks once the staging buffers are attached.  Measured on B200s
+// behind NVSwitch (max over ranks, back-to-back calls): the one-shot kernel wins while the message is latency-bound, NCCL
+// in the middle, and from a few MiB the two-shot kernel, whose NVLink traffic (2 (p-1)/p S per rank) matches NCCL's with
+// fewer synchronisation rounds.
+static int choose_algo(int p, usz bytes) {
+  if (bytes <= (usz)(64 << 10)) return OPS_ALL_REDUCE_P2P_ONE_SHOT;
+  if (p <= 2 && bytes <= (usz)(1 << 20)) return OPS_ALL_REDUCE_P2P_ONE_SHOT;  // with one peer one-shot moves no more bytes than two-shot
+  if (bytes >= (usz)(4 << 20) && p >= 8) return OPS_ALL_REDUCE_P2P_TWO_SHOT;
+  return OPS_ALL_REDUCE_NCCL;
+}
+
 template <class T>
-static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz bytes, cudaStream_t s) {
+static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz bytes, bool add, cudaStream_t s) {
   P2PKernelArgs a;
   for (int q = 0; q < MAX_RANKS; ++q) a.peers[q] = q < c->size ? c->peers[q] : nullptr;
   a.region_bytes = c->region_bytes;
   a.rank = c->rank;
   a.size = c->size;
-  a.epoch = ++c->epoch;
   a.status = c->status_dev;
   const long long vecs = (long long)(bytes / 16);
   if (algo == OPS_ALL_REDUCE_P2P_ONE_SHOT) {
@@ -508,16 +603,23 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     if (ctas > c->sm_count) ctas = c->sm_count;  // every CTA must be resident: same-index CTAs of different ranks wait for each other
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
-    all_reduce_two_shot_kernel<T><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part);
+    // zero-copy: the partial already lies in this rank's direct region (the producing kernel wrote it there)
+    const char *direct = region_direct(c->peers[c->rank], c->region_bytes);
+    const bool in_direct = (const char *)src >= direct && (const char *)src + bytes <= direct + c->region_bytes;
+    const unsigned long long off = in_direct ? (unsigned long long)((const char *)src - direct) : 0ull;
+#define OPS_TWO_SHOT(DIRECT, ADD) \
+  all_reduce_two_shot_kernel<T, DIRECT, ADD><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part, off)
+    if (in_direct && add) OPS_TWO_SHOT(true, true);
+    else if (in_direct) OPS_TWO_SHOT(true, false);
+    else if (add) OPS_TWO_SHOT(false, true);
+    else OPS_TWO_SHOT(false, false);
+#undef OPS_TWO_SHOT
   }
   return check_launch("all_reduce(p2p)");
 }
 
-OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream) {
-  (void)ws;
-  (void)ws_len;
+static int all_reduce_impl(const ops_all_reduce *op, const ops_all_reduce_args *args, bool add, cudaStream_t s) {
   ops_comm *c = op->comm;
-  cudaStream_t s = (cudaStream_t)stream;
   AllReduceMeta m;
   OPS_TRY(all_reduce_meta(args, &m));
   const usz bytes = m.len * dt_size(m.dt);
@@ -525,8 +627,9 @@ OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce
   void *dst = args->pair.dst_base;
   const void *src = args->pair.src_base;
   if (!dst || !src) return fail(OPS_DYNAMIC_NOT_SUPPORT, "all_reduce: null base pointer at launch");
+  if (add && dst == src) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce_add: dst and src must be different buffers");
   cudaSetDevice(c->device);
-  if (c->size == 1) {
+  if (c->size == 1 && !add) {
     // single rank: NonAllReduce, a plain copy unless in place (operators/src/lib.rs:199-224)
     if (dst != src) {
       OpBase base{c->device, c->sm_count};
@@ -535,12 +638,16 @@ OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce
     return OPS_OK;
   }
   int algo = op->algo;
-  const bool p2p_able = (c->p2p_ready || c->loopback) && args->op == OPS_REDUCE_SUM && (m.dt == OPS_DT_F16 || m.dt == OPS_DT_F32) && bytes % 16 == 0 &&
-                        aligned(dst, 16) && aligned(src, 16) && bytes <= c->region_bytes && 2 * c->sm_count >= 1;
-  if (algo == OPS_ALL_REDUCE_AUTO) {
-    if (!p2p_able) algo = OPS_ALL_REDUCE_NCCL;
-    else algo = bytes <= (usz)(64 << 10) ? OPS_ALL_REDUCE_P2P_ONE_SHOT : OPS_ALL_REDUCE_NCCL;  // measured on 4 B200: one-shot wins at 8 KiB, NCCL from 512 KiB up
+  const bool p2p_dt = m.dt == OPS_DT_F16 || m.dt == OPS_DT_BF16 || m.dt == OPS_DT_F32;
+  const bool p2p_able = (c->p2p_ready || c->loopback) && args->op == OPS_REDUCE_SUM && p2p_dt && bytes % 16 == 0 && aligned(dst, 16) && aligned(src, 16) &&
+                        bytes <= c->region_bytes;
+  if (add) {
+    // the residual enters the sum inside the two-shot kernel; there is no NCCL form of it
+    if (!p2p_able || c->size < 2)
+      return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce_add: needs >= 2 ranks, an attached staging buffer of >= %zu bytes, f16/bf16/f32 Sum, 16-byte aligned data", bytes);
+    algo = OPS_ALL_REDUCE_P2P_TWO_SHOT;
   }
+  if (algo == OPS_ALL_REDUCE_AUTO) algo = p2p_able ? choose_algo(c->size, bytes) : OPS_ALL_REDUCE_NCCL;
   if (algo == OPS_ALL_REDUCE_NCCL) {
     if (!c->has_nccl) return fail(OPS_EXECUTION_FAILED, "all_reduce: communicator has no NCCL handle");
     ncclDataType_t t;
@@ -551,9 +658,45 @@ OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce
     if (r != ncclSuccess) return fail(OPS_EXECUTION_FAILED, "ncclAllReduce: %s", n.GetErrorString(r));
     return OPS_OK;
   }
-  if (!p2p_able) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: the peer-to-peer path needs an attached staging buffer of >= %zu bytes, f16/f32 Sum, 16-byte aligned data", bytes);
-  if (m.dt == OPS_DT_F16) return launch_p2p<__half>(c, algo, src, dst, bytes, s);
-  return launch_p2p<float>(c, algo, src, dst, bytes, s);
+  if (!p2p_able) return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce: the peer-to-peer path needs an attached staging buffer of >= %zu bytes, f16/bf16/f32 Sum, 16-byte aligned data", bytes);
+  if (m.dt == OPS_DT_F16) return launch_p2p<__half>(c, algo, src, dst, bytes, add, s);
+  if (m.dt == OPS_DT_BF16) return launch_p2p<__nv_bfloat16>(c, algo, src, dst, bytes, add, s);
+  return launch_p2p<float>(c, algo, src, dst, bytes, add, s);
+}
+
+OPS_API int ops_all_reduce_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *ws, size_t ws_len, void *stream) {
+  (void)ws;
+  (void)ws_len;
+  return all_reduce_impl(op, args, false, (cudaStream_t)stream);
+}
+
+// dst <- dst + sum over ranks of src, one kernel: the all_reduce of a row-parallel projection with the residual add that
+// follows it folded in (the crate chains all_reduce and add, operators/src/add/common_cpu/mod.rs:29-75).
+OPS_API int ops_all_reduce_add_launch(const ops_all_reduce *op, const ops_all_reduce_args *args, void *stream) {
+  return all_reduce_impl(op, args, true, (cudaStream_t)stream);
+}
+
+// The zero-copy input region of this rank: a kernel that writes its partial here (same offset on every rank) lets
+// ops_all_reduce_launch / ops_all_reduce_add_launch skip their copy-in when they are given that pointer as src.
+OPS_API int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out) {
+  if (!c || !c->staging) return fail(OPS_ARGS_NOT_SUPPORT, "p2p: no staging buffer exported");
+  if (ptr_out) *ptr_out = region_direct(c->staging, c->region_bytes);
+  if (bytes_out) *bytes_out = c->region_bytes;
+  return OPS_OK;
+}
+
+// After a bounded wait has run out (ops_comm_p2p_status != 0) the ranks' epochs and flags no longer agree.  Once every
+// rank's streams are idle and the ranks have met at a host-side barrier, each rank calls this to start over: status word,
+// launch counter and every flag go back to zero.  Outputs of the launch that timed out are undefined.
+OPS_API int ops_comm_p2p_reset(ops_comm *c) {
+  if (!c) return fail(OPS_ARGS_NOT_SUPPORT, "null communicator");
+  cudaSetDevice(c->device);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess && c->staging) e = cudaMemset(c->staging, 0, sizeof(P2PFlags));
+  if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "p2p reset: %s", cudaGetErrorString(e));
+  return OPS_OK;
 }
 
 // ------------------------------------------------------------------------------------------------

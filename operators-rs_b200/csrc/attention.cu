@@ -128,7 +128,7 @@ int attention_enqueue(const ops_attention *op, const ops_attention_args *a, void
   if (dyn(m.nh) || dyn(m.seq) || dyn(m.dh) || dyn(m.nkvh) || dyn(m.att) || dyn(sq[0]) || dyn(sq[1]) || dyn(sq[2]) || dyn(sk[0]) ||
       dyn(sk[1]) || dyn(sk[2]))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "attention: every shape and the q, k strides must be static at launch");
-  if (m.dt != OPS_DT_F16 && m.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "attention: f16 or f32 expected");
+  if (m.dt != OPS_DT_F16 && m.dt != OPS_DT_BF16 && m.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "attention: f16, bf16 or f32 expected");
   if (m.nkvh == 0 || m.nh % m.nkvh != 0) return fail(OPS_SHAPE_MISMATCH, "attention: nh must be a multiple of nkvh");
   if (a->mask == OPS_MASK_CAUSAL && m.att < m.seq) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: causal mask needs att >= seq");
   if (m.nh == 0 || m.seq == 0 || m.dh == 0 || m.att == 0) return OPS_OK;

@@ -14,17 +14,19 @@
 
 namespace ops {
 
-constexpr int DEC_THREADS = 128;
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int DEC_MAX_ROWS = 8;
 constexpr int DEC_MAX_SPLITS = 64;
 constexpr int DEC_MAX_KV_HEADS = 1024;  // arrival counters in the handle's scratch
 
 struct DecodeArgs {
-  const __half *q, *k, *v;
-  __half *o;
+  const unsigned short *q, *k, *v;
+  unsigned short *o;
   long long q_sh, q_ss, k_sh, k_ss, v_sh, v_ss, o_sh, o_ss;  // element strides: head, row (dh contiguous)
   int group, seq, att, rows;  // rows = group * seq
   int causal;
+  int bf16;                   // elements are bf16 (else f16)
   int splits, keys_per_split;
   float scale_log2;
   float *partial;          // [nkvh][splits][rows][DH + 2]
@@ -36,22 +38,28 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float dec_to_f32(unsigned short b, int bf) {
+  return bf ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+}
+__device__ __forceinline__ unsigned short dec_from_f32(float v, int bf) {
+  return bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
 
-// DH = 64 or 128.  A key row is DH/8 lanes wide (8 halves per lane); LPK = lanes per key.
+// DH = 64 or 128.  A key row is DH/8 lanes wide (8 elements per lane); LPK = lanes per key.
 template <int DH, int ROWS>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr int LPK = DH / 8;              // 16 or 8 lanes per key row
   constexpr int KPW = 32 / LPK;            // keys per warp per step
   constexpr int GROUPS = DEC_THREADS / LPK;  // key rows in flight per CTA step
   __shared__ float q_s[ROWS][DH];
-  __shared__ float red_m[GROUPS][ROWS], red_l[GROUPS][ROWS];
-  __shared__ float red_o[GROUPS][ROWS][DH];  // 32 KB at most
+  __shared__ float red_m[DEC_WARPS][ROWS], red_l[DEC_WARPS][ROWS];
+  __shared__ float red_o[DEC_WARPS][ROWS][DH];  // 32 KB at most
   __shared__ unsigned int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPK, li = lane % LPK;  // which key of the warp step, which 8-column slice of dh
-  const int grp = warp * KPW + sub;
   const int off = a.att - a.seq;
+  const int bf = a.bf16;
 
   // q rows of this kv head, pre-scaled into the exp2 domain
   for (int i = threadIdx.x; i < ROWS * DH; i += DEC_THREADS) {
@@ -59,7 +67,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
     float val = 0.f;
     if (r < a.rows) {
       const int gi = r / a.seq, si = r - gi * a.seq;
-      val = __half2float(a.q[(long long)(kvh * a.group + gi) * a.q_sh + (long long)si * a.q_ss + c]) * a.scale_log2;
+      val = dec_to_f32(a.q[(long long)(kvh * a.group + gi) * a.q_sh + (long long)si * a.q_ss + c], bf) * a.scale_log2;
     }
     q_s[r][c] = val;
   }
@@ -85,21 +93,21 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
     for (int e = 0; e < 8; ++e) o[r][e] = 0.f;
   }
   const int k_begin = split * a.keys_per_split, k_end = min(a.att, k_begin + a.keys_per_split);
-  const __half *kbase = a.k + (long long)kvh * a.k_sh + li * 8;
-  const __half *vbase = a.v + (long long)kvh * a.v_sh + li * 8;
+  const unsigned short *kbase = a.k + (long long)kvh * a.k_sh + li * 8;
+  const unsigned short *vbase = a.v + (long long)kvh * a.v_sh + li * 8;
 #pragma unroll 4
   for (int kb = k_begin + warp * KPW; kb < k_end; kb += GROUPS) {  // warp-uniform trip count: the shuffles need every lane
     const int key = kb + sub;
     const bool valid = key < k_end;
     const int kload = valid ? key : k_end - 1;
-    Pack8 kk, vv;
+    Vec8<unsigned short> kk, vv;
     kk.u = ld_stream_16(kbase + (long long)kload * a.k_ss);
     vv.u = ld_stream_16(vbase + (long long)kload * a.v_ss);
     float kf[8], vf[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      kf[e] = __half2float(kk.h[e]);
-      vf[e] = __half2float(vv.h[e]);
+      kf[e] = dec_to_f32(kk.h[e], bf);
+      vf[e] = dec_to_f32(vv.h[e], bf);
     }
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
@@ -119,19 +127,39 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
     }
   }
 
-  // merge the key groups of this CTA in group order: common max, rescaled sums
+  // merge the key groups of one warp with shuffles (common max, rescaled sums), then the warps through shared memory
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r)
-    if (li == 0) red_m[grp][r] = m[r];
+  for (int r = 0; r < ROWS; ++r) {
+    float mm = m[r];
+#pragma unroll
+    for (int d = LPK; d < 32; d <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, d));
+    const float sc = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - mm);
+    float lr = l[r] * sc;
+#pragma unroll
+    for (int d = LPK; d < 32; d <<= 1) lr += __shfl_xor_sync(0xffffffffu, lr, d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float ov = o[r][e] * sc;
+#pragma unroll
+      for (int d = LPK; d < 32; d <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, d);
+      o[r][e] = ov;
+    }
+    m[r] = mm;
+    l[r] = lr;
+    if (lane == 0) red_m[warp][r] = mm;
+  }
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     float mm = -INFINITY;
-    for (int gq = 0; gq < GROUPS; ++gq) mm = fmaxf(mm, red_m[gq][r]);
-    const float sc = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - mm);
-    if (li == 0) red_l[grp][r] = l[r] * sc;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) red_o[grp][r][li * 8 + e] = o[r][e] * sc;
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, red_m[w][r]);
+    const float sc = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - mm);
+    if (lane == 0) red_l[warp][r] = l[r] * sc;
+    if (sub == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red_o[warp][r][li * 8 + e] = o[r][e] * sc;
+    }
   }
   __syncthreads();
   // park (m, l, o) of this split
@@ -139,15 +167,17 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   for (int i = threadIdx.x; i < ROWS * DH; i += DEC_THREADS) {
     const int r = i / DH, c = i - r * DH;
     float acc = 0.f;
-    for (int gq = 0; gq < GROUPS; ++gq) acc += red_o[gq][r][c];
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) acc += red_o[w][r][c];
     part[r * (DH + 2) + 2 + c] = acc;
   }
   if (threadIdx.x < ROWS) {
     const int r = threadIdx.x;
     float ls = 0.f, mm = -INFINITY;
-    for (int gq = 0; gq < GROUPS; ++gq) {
-      ls += red_l[gq][r];
-      mm = fmaxf(mm, red_m[gq][r]);
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      ls += red_l[w][r];
+      mm = fmaxf(mm, red_m[w][r]);
     }
     part[r * (DH + 2)] = mm;
     part[r * (DH + 2) + 1] = ls;
@@ -160,7 +190,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   __threadfence();
   if (threadIdx.x == 0) a.tickets[kvh] = 0;  // ready for the next launch
   // last CTA of this kv head: merge the splits in split order.  First the per-split weights 2^(m_s - m) and the
-  // denominators (one thread per (row, split) then per row), then every output element as an independent dot product.
+  // denominators (one thread per (row, split) then per row), then every output element as an independent dot product
+  // over the splits whose loads are all in flight together (one round trip to L2 for up to 16 splits).
   __shared__ float w_s[ROWS][DEC_MAX_SPLITS], l_s[ROWS][DEC_MAX_SPLITS];
   __shared__ float den_s[ROWS];
   const float *pall = a.partial + ((long long)kvh * a.splits) * ROWS * (DH + 2);
@@ -190,16 +221,23 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
     const float *col = pall + (long long)r * (DH + 2) + 2 + c;
     float num = 0.f;
     int sp = 0;
-    for (; sp + 8 <= a.splits; sp += 8) {  // eight loads in flight
-      float v[8];
+    for (; sp + 16 <= a.splits; sp += 16) {  // sixteen loads in flight
+      float v[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
+      for (int u = 0; u < 16; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
 #pragma unroll
-      for (int u = 0; u < 8; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
+      for (int u = 0; u < 16; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
+    }
+    for (; sp + 4 <= a.splits; sp += 4) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
     }
     for (; sp < a.splits; ++sp) num = fmaf(__ldcg(col + (long long)sp * ROWS * (DH + 2)), w_s[r][sp], num);
     const int gi = r / a.seq, si = r - gi * a.seq;
-    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + c] = __float2half_rn(num / den_s[r]);
+    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + c] = dec_from_f32(num / den_s[r], bf);
   }
 }
 
@@ -211,7 +249,7 @@ static bool rows_ok(const void *p, const isz *st, usz dh, bool need16) {
 }
 
 bool attention_decode_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh) {
-  if (a->q_layout.dt != OPS_DT_F16 || (dh != 64 && dh != 128)) return false;
+  if ((a->q_layout.dt != OPS_DT_F16 && a->q_layout.dt != OPS_DT_BF16) || (dh != 64 && dh != 128)) return false;
   const usz rows = nh / nkvh * seq;
   if (rows == 0 || rows > (usz)DEC_MAX_ROWS || att < 256 || nkvh > (usz)DEC_MAX_KV_HEADS || att > 0x3fffffffu) return false;
   const isz *sv = a->v_layout.strides, *so = a->o_layout.strides;
@@ -227,10 +265,11 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
                              unsigned int *tickets, cudaStream_t s) {
   DecodeArgs g;
   const isz *sq = a->q_layout.strides, *sk = a->k_layout.strides, *sv = a->v_layout.strides, *so = a->o_layout.strides;
-  g.q = (const __half *)a->q_base;
-  g.k = (const __half *)a->k_base;
-  g.v = (const __half *)a->v_base;
-  g.o = (__half *)a->o_base;
+  g.q = (const unsigned short *)a->q_base;
+  g.k = (const unsigned short *)a->k_base;
+  g.v = (const unsigned short *)a->v_base;
+  g.o = (unsigned short *)a->o_base;
+  g.bf16 = a->q_layout.dt == OPS_DT_BF16;
   g.q_sh = sq[0] / 2; g.q_ss = sq[1] / 2;
   g.k_sh = sk[0] / 2; g.k_ss = sk[1] / 2;
   g.v_sh = sv[0] / 2; g.v_ss = sv[1] / 2;
@@ -241,9 +280,10 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.rows = g.group * g.seq;
   g.causal = a->mask == OPS_MASK_CAUSAL;
   const int row_slots = g.rows <= 4 ? 4 : 8;
-  // about two CTAs per SM, at least 128 keys each, and partials that fit the scratch buffer
-  usz splits = (2 * (usz)base.sm_count + nkvh - 1) / nkvh;
-  splits = std::min<usz>(splits, (att + 127) / 128);
+  // about one 256-thread CTA per SM, at least 256 keys each (16 steps of 16 key rows), and partials that fit the scratch
+  // buffer; few splits keep the merge by the last CTA of a kv head short
+  usz splits = ((usz)base.sm_count + nkvh - 1) / nkvh;
+  splits = std::min<usz>(splits, (att + 255) / 256);
   splits = std::min<usz>(splits, DEC_MAX_SPLITS);
   const usz per_split = nkvh * (usz)row_slots * (dh + 2) * sizeof(float);
   splits = std::min<usz>(splits, attention_decode_scratch_bytes() / per_split);
@@ -251,7 +291,8 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.splits = (int)splits;
   g.keys_per_split = (int)((att + splits - 1) / splits);
   g.splits = (int)((att + g.keys_per_split - 1) / g.keys_per_split);
-  const float alpha = __half2float(__float2half_rn(1.f / sqrtf((float)dh)));
+  const float inv_sqrt = 1.f / sqrtf((float)dh);
+  const float alpha = g.bf16 ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
   g.scale_log2 = alpha * 1.4426950408889634f;
   g.partial = scratch;
   g.tickets = tickets;

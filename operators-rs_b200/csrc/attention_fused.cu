@@ -34,13 +34,14 @@ constexpr int FA_BN = 128;       // keys per block
 constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two per scheduler)
 
 struct FusedAttnArgs {
-  __half *o;
+  unsigned short *o;     // f16 or bf16 bit patterns
   long long o_sh, o_ss;  // element strides of o: head, row (dh contiguous)
   int nh, group, seq, att;
   int causal;
   int q_blocks;
   float scale_log2;      // alpha * log2(e)
   int vec_store;
+  int bf16;              // q, k, v, o are bf16 (else f16); the probabilities fed to the second MMA take the same type
   int *status;
 };
 
@@ -65,6 +66,15 @@ __device__ __forceinline__ float max3(float a, float b, float c) {  // three-inp
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
+}
+// two f32 -> one packed pair of f16 or bf16 (first value in the low half)
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi, int bf) {
+  if (bf) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -167,8 +177,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc_f16(FA_BM, FA_BN, 0, 0);
-      const uint32_t idesc_pv = make_idesc_f16(FA_BM, DH, 0, 1);
+      const uint32_t idesc_qk = make_idesc_f16(FA_BM, FA_BN, 0, 0, g.bf16);
+      const uint32_t idesc_pv = make_idesc_f16(FA_BM, DH, 0, 1, g.bf16);
       bool ok = mbar_wait(q_full, 0, g.status, 21);
       auto issue_pv = [&](int i) -> bool {
         const int b = i & 1;
@@ -315,8 +325,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             if (kv0 + c + e + 1 > limit) p1 = 0.f;
           }
           rowsum += p0 + p1;
-          __half2 h = __floats2half2_rn(p0, p1);
-          packed[e >> 1] = *reinterpret_cast<uint32_t *>(&h);
+          packed[e >> 1] = pack_pair(p0, p1, g.bf16);
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -344,18 +353,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     if (ok) ok = mbar_wait(l_bar(quarter), 0, g.status, 34);
     if (ok && q_row < g.seq) {
       const float inv = __frcp_rn(l + lsum[(half ^ 1) * FA_BM + row_in_tile]);
-      __half *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss + half * DHH;
+      unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss + half * DHH;
       if (g.vec_store) {
 #pragma unroll
         for (int c = 0; c < DHH; c += 8) {
-          Pack8 out;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(o[c + e] * inv);
-          st_global_16(orow + c, out.u);
+          uint4 out;
+          out.x = pack_pair(o[c] * inv, o[c + 1] * inv, g.bf16);
+          out.y = pack_pair(o[c + 2] * inv, o[c + 3] * inv, g.bf16);
+          out.z = pack_pair(o[c + 4] * inv, o[c + 5] * inv, g.bf16);
+          out.w = pack_pair(o[c + 6] * inv, o[c + 7] * inv, g.bf16);
+          st_global_16(orow + c, out);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < DHH; ++c) orow[c] = __float2half_rn(o[c] * inv);
+        for (int c = 0; c < DHH; c += 2) {
+          const uint32_t pr = pack_pair(o[c] * inv, o[c + 1] * inv, g.bf16);
+          orow[c] = (unsigned short)(pr & 0xffffu);
+          orow[c + 1] = (unsigned short)(pr >> 16);
+        }
       }
     }
   }
@@ -384,7 +399,7 @@ static EncodeTiledFn fa_encode_fn() {
 }
 
 // [heads, rows, dh] f16 tensor with dh contiguous as a rank-3 map (dh, rows, heads)
-static bool encode_hrd(CUtensorMap *map, const void *ptr, usz dh, usz rows, usz heads, isz row_stride_b, isz head_stride_b, uint32_t box_rows) {
+static bool encode_hrd(CUtensorMap *map, bool bf16, const void *ptr, usz dh, usz rows, usz heads, isz row_stride_b, isz head_stride_b, uint32_t box_rows) {
   EncodeTiledFn fn = fa_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {dh, rows, heads};
@@ -393,7 +408,7 @@ static bool encode_hrd(CUtensorMap *map, const void *ptr, usz dh, usz rows, usz 
   cuuint64_t strides[2] = {rs, hs};
   cuuint32_t box[3] = {64, box_rows, 1};
   cuuint32_t es[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -405,7 +420,7 @@ static bool hrd_ok(const void *p, const isz *st, usz heads, usz rows) {
 }
 
 bool attention_fused_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh) {
-  if (a->q_layout.dt != OPS_DT_F16 || (dh != 64 && dh != 128)) return false;
+  if ((a->q_layout.dt != OPS_DT_F16 && a->q_layout.dt != OPS_DT_BF16) || (dh != 64 && dh != 128)) return false;
   if (nh > 65535 || seq > 0x3fffffffu || att > 0x3fffffffu) return false;
   const isz *sv = a->v_layout.strides, *so = a->o_layout.strides;
   if (dyn(sv[0]) || dyn(sv[1]) || dyn(sv[2]) || dyn(so[0]) || dyn(so[1]) || dyn(so[2])) return false;
@@ -422,11 +437,13 @@ static int launch_fused(const OpBase &base, const ops_attention_args *a, usz nh,
   typedef FaCfg<DH> Cfg;
   CUtensorMap tq, tk, tv;
   const isz *sq = a->q_layout.strides, *sk = a->k_layout.strides, *sv = a->v_layout.strides, *so = a->o_layout.strides;
-  if (!encode_hrd(&tq, a->q_base, DH, seq, nh, sq[1], sq[0], FA_BM) || !encode_hrd(&tk, a->k_base, DH, att, nkvh, sk[1], sk[0], FA_BN) ||
-      !encode_hrd(&tv, a->v_base, DH, att, nkvh, sv[1], sv[0], 64))
+  const bool bf = a->q_layout.dt == OPS_DT_BF16;
+  if (!encode_hrd(&tq, bf, a->q_base, DH, seq, nh, sq[1], sq[0], FA_BM) || !encode_hrd(&tk, bf, a->k_base, DH, att, nkvh, sk[1], sk[0], FA_BN) ||
+      !encode_hrd(&tv, bf, a->v_base, DH, att, nkvh, sv[1], sv[0], 64))
     return fail(OPS_EXECUTION_FAILED, "attention: cuTensorMapEncodeTiled failed");
   FusedAttnArgs g;
-  g.o = (__half *)a->o_base;
+  g.o = (unsigned short *)a->o_base;
+  g.bf16 = bf ? 1 : 0;
   g.o_sh = so[0] / 2;
   g.o_ss = so[1] / 2;
   g.nh = (int)nh;
@@ -436,7 +453,8 @@ static int launch_fused(const OpBase &base, const ops_attention_args *a, usz nh,
   g.causal = a->mask == OPS_MASK_CAUSAL;
   g.q_blocks = (int)((seq + FA_BM - 1) / FA_BM);
   // the CPU path rounds alpha = 1/sqrt(dh) to f16 before the product (mat_mul/common_cpu/mod.rs:101)
-  const float alpha = __half2float(__float2half_rn(1.f / sqrtf((float)DH)));
+  const float inv_sqrt = 1.f / sqrtf((float)DH);
+  const float alpha = bf ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
   g.scale_log2 = alpha * 1.4426950408889634f;
   g.vec_store = aligned(a->o_base, 16) && so[0] % 16 == 0 && so[1] % 16 == 0;
   g.status = status;

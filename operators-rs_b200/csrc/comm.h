@@ -16,7 +16,9 @@ constexpr unsigned long long P2P_WAIT_LIMIT_NS = 1000000000ull;  // 1 s
 // ------------------------------------------------------------------------------------------------
 // peer-to-peer state
 // ------------------------------------------------------------------------------------------------
-// Staging buffer of one rank: [flags | in(parity 0) | in(parity 1) | out(parity 0) | out(parity 1)]
+// Staging buffer of one rank: [flags | in(parity 0) | in(parity 1) | out(parity 0) | out(parity 1) | direct]
+// "direct" is the zero-copy input region: a caller that lets the producing kernel write its partial there (same offset on
+// every rank) spares the all_reduce its copy-in.
 struct P2PFlags {
   unsigned int ready[MAX_RANKS][P2P_MAX_CTAS];   // ready[q][b]: epoch up to which rank q's CTA b has staged its input
   unsigned int reduced[MAX_RANKS][P2P_MAX_CTAS]; // reduced[q][b]: epoch up to which rank q's CTA b has published its reduced slice
@@ -25,7 +27,14 @@ struct P2PFlags {
   // [16w, 16w+16) of the reduced tile into this rank's "out" region
   unsigned int tile_ready[MAX_RANKS][P2P_MAX_TILE_FLAGS];
   unsigned int tile_done[P2P_MAX_TILE_FLAGS];
+  // Launch counter of this rank's peer-to-peer kernels.  It lives on the device and is advanced by the kernels themselves
+  // (the last CTA of a launch to finish), never by the host: a launch that is replayed from a CUDA graph therefore sees a
+  // fresh epoch every time.  Only the own copy is used; `done` counts the CTAs of the running launch that have finished.
+  unsigned int epoch;
+  unsigned int done;
 };
+
+constexpr int P2P_REGIONS = 5;  // in x2, out x2, direct
 
 struct P2PHandleBlob {  // what ops_comm_p2p_export ships (<= OPS_COMM_P2P_HANDLE_BYTES)
   cudaIpcMemHandle_t mem;
@@ -39,7 +48,6 @@ struct P2PKernelArgs {
   char *peers[MAX_RANKS];  // peers[q]: base of rank q's staging buffer as mapped here (own buffer for q == rank)
   unsigned long long region_bytes;
   int rank, size;
-  unsigned int epoch;
   int *status;
 };
 
@@ -57,7 +65,6 @@ struct ops_comm {
   char *peers[ops::MAX_RANKS];
   bool p2p_ready;
   bool loopback;               // every peer entry is the own buffer (time-out tests on one GPU)
-  unsigned int epoch;
   int *status_dev;
   int sm_count;
 };
@@ -88,6 +95,23 @@ __device__ __forceinline__ char *region_in(char *base, unsigned long long region
 }
 __device__ __forceinline__ char *region_out(char *base, unsigned long long region, unsigned int parity) {
   return base + sizeof(P2PFlags) + (2ull + parity) * region;
+}
+__host__ __device__ __forceinline__ char *region_direct(char *base, unsigned long long region) { return base + sizeof(P2PFlags) + 4ull * region; }
+
+// Epoch of the running launch: one more than the number of peer-to-peer launches this rank has completed.  Every thread
+// that needs it reads it at kernel start; it only changes after the last CTA of the launch has passed p2p_launch_done().
+__device__ __forceinline__ unsigned int p2p_epoch(const char *own_base) {
+  return *reinterpret_cast<const volatile unsigned int *>(&reinterpret_cast<const P2PFlags *>(own_base)->epoch) + 1u;
+}
+// Called by ONE thread per CTA after the CTA's last use of the epoch (on every exit path, time-outs included).
+__device__ __forceinline__ void p2p_launch_done(char *own_base) {
+  P2PFlags *f = reinterpret_cast<P2PFlags *>(own_base);
+  __threadfence();
+  if (atomicAdd(&f->done, 1u) == gridDim.x * gridDim.y * gridDim.z - 1u) {
+    f->done = 0;
+    __threadfence();
+    atomicAdd(&f->epoch, 1u);
+  }
 }
 
 }  // namespace ops

@@ -1,5 +1,6 @@
 // device_utils.cuh — small device-side helpers shared by the memory-bound kernels.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -12,6 +13,12 @@ union Pack8 {
   uint4 u;
   __half2 h2[4];
   __half h[8];
+};
+// The same for either 16-bit float type.
+template <class T> union Vec8 {
+  uint4 u;
+  T h[8];
+  __device__ __forceinline__ Vec8() {}
 };
 union Pack4 {
   uint2 u;
@@ -69,7 +76,9 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
 template <class T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <class T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 

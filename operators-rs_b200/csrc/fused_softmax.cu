@@ -26,7 +26,7 @@ __device__ __forceinline__ int row_limit(const SoftmaxParams &p, int k) { return
 
 // Register-resident row.  GROUP threads cooperate on one row (32 = a warp, else the whole CTA);
 // each owns VPT vectors of 8 halves, vector v = lane + i * GROUP.
-template <int VPT, bool WARP>
+template <class E, int VPT, bool WARP>
 __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_constant__ SoftmaxParams p) {
   __shared__ float scratch[33];
   const int group = WARP ? 32 : blockDim.x;
@@ -35,10 +35,10 @@ __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_const
   const long long row = WARP ? (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : (long long)blockIdx.x;
   if (row >= rows) return;  // warp-uniform in WARP mode, CTA-uniform otherwise
   const int j = (int)(row / p.seq), k = (int)(row - (long long)j * p.seq);
-  __half *att = byte_off((__half *)p.base, j * p.sh + k * p.ss);
+  E *att = byte_off((E *)p.base, j * p.sh + k * p.ss);
   const int limit = row_limit(p, k);
 
-  Pack8 xv[VPT];
+  Vec8<E> xv[VPT];
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_const
       xv[i].u = ld_global_16(att + c0);
 #pragma unroll
       for (int e = 0; e < 8; ++e)
-        if (c0 + e < limit) mx = fmaxf(mx, __half2float(xv[i].h[e]));
+        if (c0 + e < limit) mx = fmaxf(mx, to_f32(xv[i].h[e]));
     }
   }
   mx = WARP ? warp_max(mx) : block_max(mx, scratch);
@@ -60,8 +60,8 @@ __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_const
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         if (c0 + e < limit) {
-          const float ex = expf(__fsub_rn(__half2float(xv[i].h[e]), mx));
-          xv[i].h[e] = __float2half_rn(ex);
+          const float ex = expf(__fsub_rn(to_f32(xv[i].h[e]), mx));
+          xv[i].h[e] = from_f32<E>(ex);
           sum += ex;
         }
       }
@@ -74,10 +74,10 @@ __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_const
   for (int i = 0; i < VPT; ++i) {
     const int c0 = (lane + i * group) * 8;
     if (c0 < p.att_len) {
-      Pack8 out;
+      Vec8<E> out;
 #pragma unroll
       for (int e = 0; e < 8; ++e)
-        out.h[e] = (c0 + e < limit) ? __float2half_rn(__fmul_rn(__half2float(xv[i].h[e]), div)) : __ushort_as_half(0);
+        out.h[e] = (c0 + e < limit) ? from_f32<E>(__fmul_rn(to_f32(xv[i].h[e]), div)) : from_f32<E>(0.f);
       st_global_16(att + c0, out.u);
     }
   }
@@ -135,7 +135,7 @@ int ops::fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args 
   const isz sh = a->att_layout.strides[0], ss = a->att_layout.strides[1], sa = a->att_layout.strides[2];
   if (dyn(nh) || dyn(seq) || dyn(att_len) || dyn(sh) || dyn(ss) || dyn(sa))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "fused_softmax: every shape and stride must be static at launch");
-  if (dt != OPS_DT_F16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "fused_softmax: f16 or f32 expected");
+  if (dt != OPS_DT_F16 && dt != OPS_DT_BF16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "fused_softmax: f16, bf16 or f32 expected");
   if (a->att_mask != OPS_MASK_NONE && a->att_mask != OPS_MASK_CAUSAL) return fail(OPS_ARGS_NOT_SUPPORT, "fused_softmax: unknown mask %u", a->att_mask);
   if (nh == 0 || seq == 0 || att_len == 0) return OPS_OK;
   if (a->att_mask == OPS_MASK_CAUSAL && att_len < seq) return fail(OPS_SHAPE_NOT_SUPPORT, "fused_softmax: causal mask needs att_len >= seq_len");
@@ -146,25 +146,35 @@ int ops::fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args 
 
   SoftmaxParams p{a->att_base, sh, ss, sa, (int)nh, (int)seq, (int)att_len, a->att_mask == OPS_MASK_CAUSAL};
   const long long rows = (long long)nh * (long long)seq;
-  const bool vec = dt == OPS_DT_F16 && sa == 2 && att_len % 8 == 0 && sh % 16 == 0 && ss % 16 == 0 && aligned(a->att_base, 16);
+  const bool vec = (dt == OPS_DT_F16 || dt == OPS_DT_BF16) && sa == 2 && att_len % 8 == 0 && sh % 16 == 0 && ss % 16 == 0 && aligned(a->att_base, 16);
   const int nvec = (int)(att_len / 8);
-  if (vec && nvec <= 32 * 16) {
-    // one warp per row (rows up to 4096 columns live in 64 registers per lane): no block-level synchronisation,
-    // 8 rows per CTA keep enough bytes in flight even when a causal mask leaves most lanes of a row idle
-    const unsigned grid = (unsigned)((rows + 7) / 8);
-    if (nvec <= 32) softmax_f16_reg_kernel<1, true><<<grid, 256, 0, s>>>(p);
-    else if (nvec <= 64) softmax_f16_reg_kernel<2, true><<<grid, 256, 0, s>>>(p);
-    else if (nvec <= 128) softmax_f16_reg_kernel<4, true><<<grid, 256, 0, s>>>(p);
-    else if (nvec <= 256) softmax_f16_reg_kernel<8, true><<<grid, 256, 0, s>>>(p);
-    else softmax_f16_reg_kernel<16, true><<<grid, 256, 0, s>>>(p);
-  } else if (vec && nvec <= 256 * 8) {
-    // one CTA per row; every thread owns at most 8 vectors
-    softmax_f16_reg_kernel<8, false><<<(unsigned)rows, 256, 0, s>>>(p);
+#define OPS_SOFTMAX_REG(E)                                                                                     \
+  do {                                                                                                         \
+    if (nvec <= 32 * 16) {                                                                                     \
+      /* one warp per row (rows up to 4096 columns live in 64 registers per lane): no block-level synchronisation, */ \
+      /* 8 rows per CTA keep enough bytes in flight even when a causal mask leaves most lanes of a row idle */ \
+      const unsigned grid = (unsigned)((rows + 7) / 8);                                                        \
+      if (nvec <= 32) softmax_f16_reg_kernel<E, 1, true><<<grid, 256, 0, s>>>(p);                              \
+      else if (nvec <= 64) softmax_f16_reg_kernel<E, 2, true><<<grid, 256, 0, s>>>(p);                         \
+      else if (nvec <= 128) softmax_f16_reg_kernel<E, 4, true><<<grid, 256, 0, s>>>(p);                        \
+      else if (nvec <= 256) softmax_f16_reg_kernel<E, 8, true><<<grid, 256, 0, s>>>(p);                        \
+      else softmax_f16_reg_kernel<E, 16, true><<<grid, 256, 0, s>>>(p);                                        \
+    } else {                                                                                                   \
+      /* one CTA per row; every thread owns at most 8 vectors */                                               \
+      softmax_f16_reg_kernel<E, 8, false><<<(unsigned)rows, 256, 0, s>>>(p);                                   \
+    }                                                                                                          \
+  } while (0)
+  if (vec && nvec <= 256 * 8) {
+    if (dt == OPS_DT_F16) OPS_SOFTMAX_REG(__half);
+    else OPS_SOFTMAX_REG(__nv_bfloat16);
   } else if (dt == OPS_DT_F16) {
     softmax_generic_kernel<__half><<<(unsigned)rows, 256, 0, s>>>(p);
+  } else if (dt == OPS_DT_BF16) {
+    softmax_generic_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>(p);
   } else {
     softmax_generic_kernel<float><<<(unsigned)rows, 256, 0, s>>>(p);
   }
+#undef OPS_SOFTMAX_REG
   return check_launch("fused_softmax");
 }
 

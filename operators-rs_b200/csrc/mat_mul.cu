@@ -50,7 +50,7 @@ constexpr int GEMM_SPLIT_MAX_SLICES = 8;
 constexpr int GEMM_EPI_LD = 36;                    // padded row length (words) of the epilogue's shared-memory pad: conflict-free both ways
 
 struct GemmKernelArgs {
-  __half *d;             // row-major output
+  unsigned short *d;     // row-major output (f16 or bf16 bit patterns)
   long long ldd, d_bs;   // elements
   int m, n, k, batch;
   int tiles_m, tiles_n;
@@ -59,6 +59,8 @@ struct GemmKernelArgs {
   float alpha, beta;
   int read_c;
   int vec_store;         // rows of D are 16-byte aligned
+  int bf16;              // elements are bf16 (else f16)
+  int group_m;           // tile raster: m-tiles walked in groups of this many (>= tiles_m: plain m-fastest order)
   int *status;
   // Remainder wave: the tiles beyond the last full wave are cut along K into `split_g` slices, one (tile, slice) unit
   // per CTA; partial sums meet in `split_ws` (f32) and the last slice to arrive finishes the tile.
@@ -79,9 +81,34 @@ struct FusedArArgs {
   char *peers[MAX_RANKS];
   unsigned long long region_bytes;
   int rank, size;
-  unsigned int epoch;
   int *status;
 };
+
+// 16-bit float <-> f32 for either element type (warp-uniform selector)
+__device__ __forceinline__ float h16_to_f32(unsigned short b, int bf) {
+  return bf ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+}
+__device__ __forceinline__ unsigned short f32_to_h16(float v, int bf) {
+  return bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+
+// Tile number r of a batch -> (m-tile, n-tile).  Plain order walks m fastest, so a wave of CTAs shares a few B panels and
+// streams all of A (right when A fits in L2).  When A is too large for that, m-tiles are walked in groups of `group_m`, a
+// wave then covers a near-square block of tiles and re-reads less of both operands.
+__device__ __forceinline__ void tile_coords(int tiles_m, int tiles_n, int group_m, long long r, int &tm, int &tn) {
+  if (group_m >= tiles_m) {
+    tn = (int)(r / tiles_m);
+    tm = (int)(r - (long long)tn * tiles_m);
+    return;
+  }
+  const long long per_group = (long long)group_m * tiles_n;
+  const int grp = (int)(r / per_group);
+  const int first = grp * group_m;
+  const int gm = min(group_m, tiles_m - first);
+  const long long within = r - (long long)grp * per_group;
+  tn = (int)(within / gm);
+  tm = first + (int)(within - (long long)tn * gm);
+}
 
 struct GemmWork {
   long long t;
@@ -136,6 +163,9 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (g.k + GEMM_BK - 1) / GEMM_BK;
+  const int bf = g.bf16;
+  unsigned int fa_epoch = 0;  // epoch of this launch of the fused all_reduce (read from device memory: replay-safe)
+  if constexpr (FUSED) fa_epoch = p2p_epoch(fa.peers[fa.rank]);
   const long long tiles_per_batch = (long long)g.tiles_m * g.tiles_n;
   const long long num_tiles = tiles_per_batch * g.batch;
 
@@ -174,7 +204,8 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         const long long t = w.t;
         const int b = (int)(t / tiles_per_batch);
         const long long r = t - (long long)b * tiles_per_batch;
-        const int tn = (int)(r / g.tiles_m), tm = (int)(r - (long long)tn * g.tiles_m);
+        int tn, tm;
+        tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
         const int m0 = tm * GEMM_BM, n0 = tn * BN;
         const int ba = g.a_batched ? b : 0, bb = g.b_batched ? b : 0;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -204,7 +235,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major);
+      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major, g.bf16);
       const uint32_t a_lbo = g.a_mn_major ? GEMM_CHUNK_BYTES : 16, b_lbo = g.b_mn_major ? GEMM_CHUNK_BYTES : 16;
       const uint32_t a_kstep = g.a_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;  // bytes per UMMA_K
       const uint32_t b_kstep = g.b_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;
@@ -253,15 +284,16 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       const long long t = w.t;
       const int b = (int)(t / tiles_per_batch);
       const long long r = t - (long long)b * tiles_per_batch;
-      const int tn = (int)(r / g.tiles_m), tm = (int)(r - (long long)tn * g.tiles_m);
+      int tn, tm;
+      tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
       const int row = tm * GEMM_BM + quarter * 32 + lane;
       const int n0 = tn * BN;
       if (!(ok = mbar_wait(tmem_full_bar(acc), acc_phase, g.status, 4))) break;
       tc_fence_after();
-      __half *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
+      unsigned short *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
       // fused all_reduce: the partial goes to this rank's peer-visible "in" region (dense rows of n), C is only read
-      __half *wrow = drow;
-      if constexpr (FUSED) wrow = reinterpret_cast<__half *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa.epoch & 1u)) + (long long)row * g.n;
+      unsigned short *wrow = drow;
+      if constexpr (FUSED) wrow = reinterpret_cast<unsigned short *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa_epoch & 1u)) + (long long)row * g.n;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       // K-slice of a remainder tile: park the f32 partial; the last of the tile's slices to arrive (per 32-row quarter)
       // adds all of them up in slice order and takes over as if it had computed the whole tile
@@ -304,7 +336,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         const bool fast = g.vec_store && n0 + c + 32 <= g.n;
         const int rsub = lane >> 2, unit = lane & 3;
         const int tile_row0 = row - lane;
-        Pack8 oldc[4];
+        Vec8<unsigned short> oldc[4];
         if (FUSED || w.slice < 0) {
           tmem_ld_32x32(taddr + (uint32_t)c, v);
           if (fast && g.read_c) {
@@ -371,16 +403,16 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
             const float4 f0 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8);
             const float4 f1 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8 + 4);
             const float acc8[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-            Pack8 out;
+            Vec8<unsigned short> out;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               float val = __fmul_rn(g.alpha, acc8[e]);
-              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(oldc[it].h[e])), val);
-              out.h[e] = __float2half_rn(val);
+              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, h16_to_f32(oldc[it].h[e], bf)), val);
+              out.h[e] = f32_to_h16(val, bf);
             }
             if (grow < g.m) {
-              __half *wp;
-              if constexpr (FUSED) wp = reinterpret_cast<__half *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa.epoch & 1u)) + (long long)grow * g.n;
+              unsigned short *wp;
+              if constexpr (FUSED) wp = reinterpret_cast<unsigned short *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa_epoch & 1u)) + (long long)grow * g.n;
               else wp = g.d + (long long)b * g.d_bs + (long long)grow * g.ldd;
               st_global_16(wp + n0 + c + unit * 8, out.u);
             }
@@ -391,22 +423,22 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           for (int q = 0; q < 4; ++q) {
             const int col = n0 + c + q * 8;
             if (col >= g.n) break;
-            __half *dp = drow + col;
+            unsigned short *dp = drow + col;
             if (g.vec_store && col + 8 <= g.n) {
-              Pack8 out, old;
+              Vec8<unsigned short> out, old;
               if (g.read_c) old.u = ld_global_16(dp);
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
                 float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
-                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(old.h[e])), val);
-                out.h[e] = __float2half_rn(val);
+                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, h16_to_f32(old.h[e], bf)), val);
+                out.h[e] = f32_to_h16(val, bf);
               }
               st_global_16(wrow + col, out.u);
             } else {
               for (int e = 0; e < 8 && col + e < g.n; ++e) {
                 float val = __fmul_rn(g.alpha, __uint_as_float(v[q * 8 + e]));
-                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, __half2float(dp[e])), val);
-                dp[e] = __float2half_rn(val);
+                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, h16_to_f32(dp[e], bf)), val);
+                dp[e] = f32_to_h16(val, bf);
               }
             }
           }
@@ -420,7 +452,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         __syncwarp();
         if (lane == 0) {
           P2PFlags *owner = reinterpret_cast<P2PFlags *>(fa.peers[(int)(t % fa.size)]);
-          st_release_sys(&owner->tile_ready[fa.rank][t * 4 + quarter], fa.epoch);
+          st_release_sys(&owner->tile_ready[fa.rank][t * 4 + quarter], fa_epoch);
         }
       }
       if (++acc == 2) {
@@ -433,7 +465,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     // Eight warps; warp c works on rows [16c, 16c+16) of a tile, i.e. half of the 32-row quarter c/2 whose flag it watches.
     const int cw = warp - 6;
     const int cq = cw >> 1;  // quarter whose flags gate these rows
-    const unsigned int parity = fa.epoch & 1u;
+    const unsigned int parity = fa_epoch & 1u;
     P2PFlags *mine = reinterpret_cast<P2PFlags *>(fa.peers[fa.rank]);
     constexpr int VPR = BN / 8;       // 16-byte vectors per tile row
     constexpr int RPP = 32 / VPR;     // tile rows per warp pass
@@ -441,7 +473,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     bool ok = true;
     auto wait_flag = [&](const unsigned int *flag, int code) -> bool {
       const unsigned long long t0 = p2p_now();
-      while ((int)(ld_acquire_sys(flag) - fa.epoch) < 0) {
+      while ((int)(ld_acquire_sys(flag) - fa_epoch) < 0) {
         if (p2p_now() - t0 > P2P_WAIT_LIMIT_NS) {
           atomicCAS(fa.status, 0, code);
           return false;
@@ -492,7 +524,8 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       if (lane < fa.size) mine_ok = wait_flag(&mine->tile_ready[lane][f], 40 + lane);
       ok = __all_sync(0xffffffffu, mine_ok);
       if (!ok) break;
-      const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
+      int tn, tm;
+      tile_coords(g.tiles_m, g.tiles_n, g.group_m, t, tm, tn);
       const int col = tn * BN + vec * 8;
       const int rbase = tm * GEMM_BM + cw * 16 + sub;
       if (fa.size <= 4) {
@@ -504,7 +537,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       __syncwarp();
       // these 16 rows of the tile are final on every rank: flag them (per tile and warp, so that the warp that moves the
       // same rows to C in phase B depends on nothing else)
-      if (lane < fa.size) st_release_sys(&reinterpret_cast<P2PFlags *>(fa.peers[lane])->tile_done[t * 8 + cw], fa.epoch);
+      if (lane < fa.size) st_release_sys(&reinterpret_cast<P2PFlags *>(fa.peers[lane])->tile_done[t * 8 + cw], fa_epoch);
     }
     // phase B: every rank needs every tile: move this CTA's share from the "out" region to C
     for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -512,7 +545,8 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       if (lane == 0) mine_ok = wait_flag(&mine->tile_done[t * 8 + cw], 60);
       ok = __all_sync(0xffffffffu, mine_ok);
       if (!ok) break;
-      const int tn = (int)(t / g.tiles_m), tm = (int)(t - (long long)tn * g.tiles_m);
+      int tn, tm;
+      tile_coords(g.tiles_m, g.tiles_n, g.group_m, t, tm, tn);
       const int col = tn * BN + vec * 8;
       const char *outp = region_out(fa.peers[fa.rank], fa.region_bytes, parity);
       const int rbase = tm * GEMM_BM + cw * 16 + sub;
@@ -537,6 +571,9 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     if (*reinterpret_cast<volatile int *>(g.status) != 0) __nanosleep(1000000);  // let stray copies land before the CTA goes away
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  if constexpr (FUSED) {
+    if (threadIdx.x == 0) p2p_launch_done(fa.peers[fa.rank]);
   }
 }
 
@@ -691,7 +728,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // One operand as a rank-3 f16 tensor map: dims (inner, outer, batch), 128-byte swizzle.
-static bool encode_operand(CUtensorMap *map, const void *ptr, usz inner, usz outer, usz batch, isz outer_stride_el, isz batch_stride_el,
+static bool encode_operand(CUtensorMap *map, bool bf16, const void *ptr, usz inner, usz outer, usz batch, isz outer_stride_el, isz batch_stride_el,
                            uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
@@ -702,7 +739,7 @@ static bool encode_operand(CUtensorMap *map, const void *ptr, usz inner, usz out
   cuuint64_t strides[2] = {os, bs};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -739,15 +776,16 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   typedef GemmCfg<BN> Cfg;
   CUtensorMap ta, tb;
   bool ok;
-  if (a_mn) ok = encode_operand(&ta, p.a_ptr, p.m, p.k, eff_batch_a, p.a.cs, p.a.stride, 64, GEMM_BK);
-  else ok = encode_operand(&ta, p.a_ptr, p.k, p.m, eff_batch_a, p.a.rs, p.a.stride, GEMM_BK, GEMM_BM);
+  const bool bf = p.dt == OPS_DT_BF16;
+  if (a_mn) ok = encode_operand(&ta, bf, p.a_ptr, p.m, p.k, eff_batch_a, p.a.cs, p.a.stride, 64, GEMM_BK);
+  else ok = encode_operand(&ta, bf, p.a_ptr, p.k, p.m, eff_batch_a, p.a.rs, p.a.stride, GEMM_BK, GEMM_BM);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for A");
-  if (b_mn) ok = encode_operand(&tb, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
-  else ok = encode_operand(&tb, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
+  if (b_mn) ok = encode_operand(&tb, bf, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
+  else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B");
 
   GemmKernelArgs g;
-  g.d = (__half *)p.d_ptr;
+  g.d = (unsigned short *)p.d_ptr;
   g.ldd = p.d.rs;
   g.d_bs = p.d.stride;
   g.m = (int)p.m;
@@ -764,6 +802,9 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   g.beta = beta;
   g.read_c = beta != 0.f;
   g.vec_store = aligned(p.d_ptr, 16) && (p.m == 1 || p.d.rs % 8 == 0) && (p.batch == 1 || p.d.stride % 8 == 0);
+  g.bf16 = bf ? 1 : 0;
+  // A panel set too large to stay in L2 next to the streamed B panels: walk m-tiles in groups so that a wave re-reads less
+  g.group_m = (p.m * p.k * 2 > ((usz)48 << 20) && g.tiles_m > 16) ? 16 : g.tiles_m;
   g.status = op->st.status_dev;
   const long long tiles = (long long)g.tiles_m * g.tiles_n * g.batch;
   const unsigned grid = (unsigned)std::min<long long>(tiles, op->base.sm_count);
@@ -816,7 +857,6 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
     fa.region_bytes = comm->region_bytes;
     fa.rank = comm->rank;
     fa.size = comm->size;
-    fa.epoch = ++comm->epoch;
     fa.status = comm->status_dev;
     const int slot = BN == 256 ? 2 : 3;
     if (!mop->st.attr_set[slot]) {
@@ -846,7 +886,7 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
   GemmProblem p;
   OPS_TRY(solve_layout(args, &p));
   if (dyn(args->alpha) || dyn(args->beta)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: alpha and beta must be static at launch");
-  if (p.dt != OPS_DT_F16 && p.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "Unsupported element type %u", p.dt);
+  if (p.dt != OPS_DT_F16 && p.dt != OPS_DT_BF16 && p.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "Unsupported element type %u", p.dt);
   if (p.m == 0 || p.n == 0 || p.batch == 0) return OPS_OK;
   if (p.m > 0x7fffffffu || p.n > 0x7fffffffu || p.k > 0x7fffffffu || p.batch > 65535u) return fail(OPS_SHAPE_NOT_SUPPORT, "mat_mul: shape too large");
   if (!p.a_ptr || !p.b_ptr || !p.d_ptr) return fail(OPS_DYNAMIC_NOT_SUPPORT, "mat_mul: null base pointer at launch");
@@ -855,9 +895,12 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
   if (p.dt == OPS_DT_F16) {  // the CPU path rounds both scalars to the element type first (mat_mul/common_cpu/mod.rs:101)
     alpha = __half2float(__float2half_rn(alpha));
     beta = __half2float(__float2half_rn(beta));
+  } else if (p.dt == OPS_DT_BF16) {  // the same rule for the second 16-bit type
+    alpha = __bfloat162float(__float2bfloat16_rn(alpha));
+    beta = __bfloat162float(__float2bfloat16_rn(beta));
   }
 
-  if (p.dt == OPS_DT_F16 && p.k > 0) {
+  if ((p.dt == OPS_DT_F16 || p.dt == OPS_DT_BF16) && p.k > 0) {
     // operand majors: A is [m,k] (K-major when its column stride is 1), B is [k,n] (K-major when its row stride is 1)
     const bool a_mn = !(p.a.cs == 1 || p.k == 1) ;
     const bool b_mn = !(p.b.rs == 1 || p.k == 1);
@@ -870,7 +913,7 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
       // what the fused kernel needs on top of the tensor-core path: one matrix, dense 16-byte rows, a staging region that
       // holds the whole partial, a flag per (tile, quarter), one CTA per SM resident
       const long long tiles = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + (p.n > 128 ? 256 : 128) - 1) / (p.n > 128 ? 256 : 128));
-      const bool fused_ok = a_ok && b_ok && d_ok && encode_tiled_fn() && p.batch == 1 && p.n % 8 == 0 && p.d.rs % 8 == 0 && aligned(p.d_ptr, 16) &&
+      const bool fused_ok = p.dt == OPS_DT_F16 && a_ok && b_ok && d_ok && encode_tiled_fn() && p.batch == 1 && p.n % 8 == 0 && p.d.rs % 8 == 0 && aligned(p.d_ptr, 16) &&
                             comm->p2p_ready && p.m * p.n * 2 <= comm->region_bytes && tiles * 8 <= P2P_MAX_TILE_FLAGS && comm->device == op->base.device;
       if (!fused_ok) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: needs f16 TMA-describable operands, one dense matrix whose partial fits the attached staging region");
       if (p.n > 128) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s, comm);
@@ -898,6 +941,7 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
   dim3 grid((unsigned)((p.n + 63) / 64), (unsigned)((p.m + 63) / 64), (unsigned)p.batch);
   if (grid.y > 65535u) return fail(OPS_SHAPE_NOT_SUPPORT, "mat_mul: m too large for the generic kernel");
   if (p.dt == OPS_DT_F16) gemm_simt_kernel<__half><<<grid, 256, 0, s>>>(g);
+  else if (p.dt == OPS_DT_BF16) gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(g);
   else gemm_simt_kernel<float><<<grid, 256, 0, s>>>(g);
   return check_launch("mat_mul(simt)");
 }

@@ -49,7 +49,7 @@ template <> __device__ __forceinline__ uint32_t raw_bits<float>(float v) { retur
 // ------------------------------------------------------------------------------------------------
 // argmax
 // ------------------------------------------------------------------------------------------------
-struct ArgmaxScratch {          // per row, zero-initialised before the launch
+struct ArgmaxScratch {          // per row; all zero between launches (the CTA that finishes a row puts it back)
   unsigned long long best;      // (ordered value << 32) | index, over non-NaN elements
   unsigned int last_nan;        // 1 + index of the last NaN, 0 if none
   unsigned int tickets;         // CTAs of this row that have finished
@@ -129,8 +129,9 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
   if (atomicAdd(&sc->tickets, 1u) != (unsigned)(split - 1)) return;
   // last CTA of the row: finish
   __threadfence();
-  const unsigned long long gbest = atomicMax(&sc->best, 0ull);
-  const unsigned int gnan = atomicMax(&sc->last_nan, 0u);
+  const unsigned long long gbest = atomicExch(&sc->best, 0ull);  // read and leave zero for the next launch
+  const unsigned int gnan = atomicExch(&sc->last_nan, 0u);
+  sc->tickets = 0;
   unsigned int idx;
   if (gnan == 0) {
     idx = (unsigned int)(gbest & 0xffffffffull);
@@ -247,7 +248,33 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restr
 
   // ---- S1: row maximum --------------------------------------------------------------------------
   float mx = -INFINITY;
-  for (int i = tid; i < n; i += SAMPLE_THREADS) mx = fmaxf(mx, to_f32(x[i]));
+  {
+    constexpr int PER = 16 / (int)sizeof(T);
+    if ((((uintptr_t)x) & 15) == 0) {
+      const int nv = n / PER;
+      int v = tid;
+      for (; v + 3 * SAMPLE_THREADS < nv; v += 4 * SAMPLE_THREADS) {  // four 128-bit loads in flight per thread
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) raw[u] = ld_global_16(reinterpret_cast<const uint4 *>(x) + v + u * SAMPLE_THREADS);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const T *e = reinterpret_cast<const T *>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < PER; ++j) mx = fmaxf(mx, to_f32(e[j]));
+        }
+      }
+      for (; v < nv; v += SAMPLE_THREADS) {
+        const uint4 raw = ld_global_16(reinterpret_cast<const uint4 *>(x) + v);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) mx = fmaxf(mx, to_f32(e[j]));
+      }
+      for (int i = nv * PER + tid; i < n; i += SAMPLE_THREADS) mx = fmaxf(mx, to_f32(x[i]));
+    } else {
+      for (int i = tid; i < n; i += SAMPLE_THREADS) mx = fmaxf(mx, to_f32(x[i]));
+    }
+  }
   mx = block_max(mx, sh.red_f);
 
   // ---- S2: keep (in index order) every element that can still move the sum ----------------------
@@ -280,6 +307,19 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restr
     __syncthreads();
   }
   const int M = sh.kept;
+  if (M == 0) {
+    // Nothing can be ordered: every logit is -inf, or one is +inf or NaN poisons x - max.  The CPU loop panics or
+    // produces garbage on such rows; here the row gets a defined answer without touching the scratch: the argmax rule
+    // (last index of the maximum) with the cumulative mass 1 as value.
+    if (tid == 0) {
+      int best = 0;
+      for (int i = 1; i < n; ++i)
+        if (!(to_f32(x[best]) > to_f32(x[i]))) best = i;
+      out[row].idx = (unsigned)best;
+      out[row].val = raw_bits(from_f32<T>(1.f));
+    }
+    return;
+  }
 
   // ---- S3: stable LSD radix sort of the kept prefix, 4 bits per pass ----------------------------
   uint2 *src = buf_a, *dst = buf_b;
@@ -506,9 +546,11 @@ static inline bool is_argmax(const ops_sample_args &c) { return c.temperature ==
 static usz argmax_ws(usz rows) { return rows * sizeof(ArgmaxScratch); }
 static usz sample_ws_row(usz n) { return (n * 16 + 255) / 256 * 256; }
 
+// `arg_scratch`: `arg_rows` zeroed, self-resetting ArgmaxScratch records that belong to the caller's handle (or to the
+// built-in array of the allocation-free entry); rows beyond that take theirs from the workspace, cleared on the stream.
 static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const void *logits, isz row_stride, void *kv_out,
                        const ops_sample_args &cfg, const float *seeds_dev, float seed_scalar, void *ws, usz ws_len,
-                       cudaStream_t s) {
+                       ArgmaxScratch *arg_scratch, usz arg_rows, cudaStream_t s) {
   if (dt != OPS_DT_F16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "random_sample: f16 or f32 logits expected");
   if (rows == 0) return OPS_OK;
   if (n == 0) return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: empty logits");
@@ -516,9 +558,13 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
   if (!logits || !kv_out) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: null base pointer at launch");
   cudaSetDevice(base.device);
   if (is_argmax(cfg)) {
-    const usz need = argmax_ws(rows);
-    if (ws_len < need || !ws) return need_workspace(need);
-    cudaMemsetAsync(ws, 0, need, s);
+    ArgmaxScratch *scratch = arg_scratch;
+    if (!scratch || rows > arg_rows) {
+      const usz need = argmax_ws(rows);
+      if (ws_len < need || !ws) return need_workspace(need);
+      cudaMemsetAsync(ws, 0, need, s);
+      scratch = (ArgmaxScratch *)ws;
+    }
     // split a row over several CTAs when there are few rows; keep >= 8 KiB per CTA
     const usz row_bytes = n * dt_size(dt);
     usz split = (8 * (usz)base.sm_count + rows - 1) / rows;  // ~8 CTAs per SM keep enough loads in flight
@@ -527,9 +573,9 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
     if (split < 1) split = 1;
     const unsigned grid = (unsigned)(rows * split);
     if (dt == OPS_DT_F16)
-      argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half *)logits, row_stride, (int)n, (int)split, (ArgmaxScratch *)ws, (KVPair *)kv_out);
+      argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half *)logits, row_stride, (int)n, (int)split, scratch, (KVPair *)kv_out);
     else
-      argmax_kernel<float><<<grid, 256, 0, s>>>((const float *)logits, row_stride, (int)n, (int)split, (ArgmaxScratch *)ws, (KVPair *)kv_out);
+      argmax_kernel<float><<<grid, 256, 0, s>>>((const float *)logits, row_stride, (int)n, (int)split, scratch, (KVPair *)kv_out);
     return check_launch("random_sample(argmax)");
   }
   if (!(cfg.temperature > 0.f)) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: temperature must be >= 0");
@@ -554,7 +600,50 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
 
 using namespace ops;
 
-OPS_DEFINE_SIMPLE_HANDLE(random_sample)
+// The handle owns the few bytes per row the argmax kernel meets in (zeroed once, left at zero by every launch), so the
+// argmax path needs neither a workspace nor a clearing launch.  One stream at a time per handle.
+constexpr usz ARGMAX_OWN_ROWS = 4096;
+struct ops_random_sample {
+  ops::OpBase base;
+  ops::ArgmaxScratch *arg_scratch;
+};
+
+namespace ops {
+static int noalloc_scratch(int device, void **out);
+}
+
+OPS_API int ops_random_sample_create(int device, ops_random_sample **out) {
+  if (!out) return fail(OPS_ARGS_NOT_SUPPORT, "null out pointer");
+  ops_random_sample *h = new ops_random_sample();
+  h->arg_scratch = nullptr;
+  int rc = init_base(&h->base, device);
+  if (rc != OPS_OK) {
+    delete h;
+    return rc;
+  }
+  cudaSetDevice(device);
+  if (cudaMalloc(&h->arg_scratch, ARGMAX_OWN_ROWS * sizeof(ArgmaxScratch)) != cudaSuccess ||
+      cudaMemset(h->arg_scratch, 0, ARGMAX_OWN_ROWS * sizeof(ArgmaxScratch)) != cudaSuccess) {
+    cudaGetLastError();  // without it the argmax path takes its records from the caller's workspace
+    if (h->arg_scratch) cudaFree(h->arg_scratch);
+    h->arg_scratch = nullptr;
+  }
+  // Look up the built-in scratch array of the allocation-free entry point now, so that its launches — the first one
+  // included — do no driver work.  A failure here is not fatal: that entry point tries again when it is first used.
+  void *unused = nullptr;
+  if (noalloc_scratch(device, &unused) != OPS_OK) cudaGetLastError();
+  *out = h;
+  return OPS_OK;
+}
+
+OPS_API void ops_random_sample_destroy(ops_random_sample *op) {
+  if (!op) return;
+  if (op->arg_scratch) {
+    cudaSetDevice(op->base.device);
+    cudaFree(op->arg_scratch);
+  }
+  delete op;
+}
 
 OPS_API int ops_sample_args_new(float temperature, float top_p, size_t top_k, ops_sample_args *out) {
   if (temperature < 0.f) return 1;
@@ -592,14 +681,16 @@ OPS_API int ops_random_sample_launch(const ops_random_sample *op, const ops_rand
   const isz st = a->logits.strides[0];
   if (dyn(st) || st != (isz)dt_size(m.dt)) return fail(OPS_STRIDES_NOT_SUPPORT, "random_sample: logits must be contiguous");
   if (dyn(m.n)) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: n must be static at launch");
-  return launch_rows(op->base, m.dt, 1, m.n, a->logits_base, 0, a->kv_pair_base, a->config, nullptr, a->seed, ws, ws_len, (cudaStream_t)stream);
+  return launch_rows(op->base, m.dt, 1, m.n, a->logits_base, 0, a->kv_pair_base, a->config, nullptr, a->seed, ws, ws_len, op->arg_scratch, ARGMAX_OWN_ROWS,
+                     (cudaStream_t)stream);
 }
 
 OPS_API int ops_random_sample_launch_batched(const ops_random_sample *op, uint32_t dt, size_t rows, size_t n, const void *logits_base,
                                              ptrdiff_t row_stride, void *kv_pairs_base, const ops_sample_args *config,
                                              const float *seeds_dev, void *ws, size_t ws_len, void *stream) {
   if (!is_argmax(*config) && !seeds_dev) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: batched sampling needs one seed per row");
-  return launch_rows(op->base, dt, rows, n, logits_base, row_stride, kv_pairs_base, *config, seeds_dev, 0.f, ws, ws_len, (cudaStream_t)stream);
+  return launch_rows(op->base, dt, rows, n, logits_base, row_stride, kv_pairs_base, *config, seeds_dev, 0.f, ws, ws_len, op->arg_scratch, ARGMAX_OWN_ROWS,
+                     (cudaStream_t)stream);
 }
 
 OPS_API int ops_random_sample_build_indices(size_t n, uint32_t *host_out) {
@@ -618,8 +709,9 @@ OPS_API int ops_random_sample_build_indices(size_t n, uint32_t *host_out) {
 // process exits.
 //
 // The array is shared by every call on a device and keeps whatever the previous call left in it.  The
-// argmax path clears the few bytes it needs to start from zero on the stream before its kernel; the
-// sampling path overwrites everything it later reads.  Two calls that overlap on the GPU (different
+// argmax path meets in a record behind the sampling area that starts at zero when the library is loaded
+// and that the kernel itself puts back to zero before it ends; the sampling path overwrites everything
+// it later reads.  Two calls that overlap on the GPU (different
 // streams, or graphs replayed concurrently) would race on the array: serialise them.
 // ------------------------------------------------------------------------------------------------
 namespace ops {
@@ -627,10 +719,12 @@ namespace ops {
 constexpr usz NOALLOC_MAX_LOGITS = 131072;                       // one row of up to 128 Ki logits
 constexpr usz NOALLOC_SCRATCH_BYTES = NOALLOC_MAX_LOGITS * 16;   // 2 MiB: what the sampling kernel needs for such a row
 
-static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+constexpr usz NOALLOC_ARGMAX_BYTES = 256;                        // behind it: the argmax record (zero at load, left at zero by every call)
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES + NOALLOC_ARGMAX_BYTES];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
-static void *g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of the array on each device, resolved on first use
+static void *g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of the array on each device: looked up when a handle is created there
 static std::mutex g_noalloc_mutex;
 
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use:
@@ -668,5 +762,5 @@ OPS_API int ops_random_sample_launch_noalloc(const ops_random_sample *op, const 
   void *scratch = nullptr;
   OPS_TRY(noalloc_scratch(op->base.device, &scratch));
   return launch_rows(op->base, m.dt, 1, m.n, a->logits_base, 0, a->kv_pair_base, a->config, nullptr, a->seed, scratch, NOALLOC_SCRATCH_BYTES,
-                     (cudaStream_t)stream);
+                     (ArgmaxScratch *)((unsigned char *)scratch + NOALLOC_SCRATCH_BYTES), 1, (cudaStream_t)stream);
 }

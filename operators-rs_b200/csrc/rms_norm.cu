@@ -18,24 +18,35 @@ __device__ __forceinline__ float rms_scale(float sum, float d, float eps) {
 
 // Fast path: f16 activations, unit inner strides, 16-byte aligned rows, d % 8 == 0.
 // Each thread owns VPT vectors of 8 halves: vector index v = threadIdx.x + i * blockDim.x.
-template <int VPT, class W>
-__global__ void __launch_bounds__(1024) rms_norm_rows_kernel(__half *__restrict__ y, long long nsy, const __half *__restrict__ x,
-                                                             long long nsx, const W *__restrict__ w, int d, float eps) {
+// ADD: the residual form.  x <- x + r first (one rounding to the element type, as the crate's add operator rounds,
+// operators/src/add/common_cpu/mod.rs:29-75), written back in place, and the norm is taken of that sum.
+template <int VPT, class A, class W, bool ADD>
+__global__ void __launch_bounds__(1024) rms_norm_rows_kernel(A *__restrict__ y, long long nsy, A *__restrict__ x,
+                                                             long long nsx, const W *__restrict__ w, int d, float eps,
+                                                             const A *__restrict__ r, long long nsr) {
   __shared__ float scratch[33];
   const int nvec = d >> 3;
-  const __half *xr = byte_off(x, (long long)blockIdx.x * nsx);
-  __half *yr = byte_off(y, (long long)blockIdx.x * nsy);
+  A *xr = byte_off(x, (long long)blockIdx.x * nsx);
+  A *yr = byte_off(y, (long long)blockIdx.x * nsy);
+  const A *rr = ADD ? byte_off(r, (long long)blockIdx.x * nsr) : nullptr;
 
-  Pack8 xv[VPT];
+  Vec8<A> xv[VPT];
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
       xv[i].u = ld_global_16(xr + v * 8);
+      if constexpr (ADD) {
+        Vec8<A> rv;
+        rv.u = ld_global_16(rr + v * 8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xv[i].h[e] = from_f32<A>(__fadd_rn(to_f32(xv[i].h[e]), to_f32(rv.h[e])));
+        st_global_16(xr + v * 8, xv[i].u);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        float f = __half2float(xv[i].h[e]);
+        float f = to_f32(xv[i].h[e]);
         sum = fmaf(f, f, sum);
       }
     }
@@ -49,19 +60,19 @@ __global__ void __launch_bounds__(1024) rms_norm_rows_kernel(__half *__restrict_
     if (v < nvec) {
       float wf[8];
       if constexpr (sizeof(W) == 2) {
-        Pack8 wv;
+        Vec8<W> wv;
         wv.u = __ldg(reinterpret_cast<const uint4 *>(w) + v);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) wf[e] = __half2float(wv.h[e]);
+        for (int e = 0; e < 8; ++e) wf[e] = to_f32(wv.h[e]);
       } else {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(w) + 2 * v);
         const float4 b = __ldg(reinterpret_cast<const float4 *>(w) + 2 * v + 1);
         wf[0] = a.x; wf[1] = a.y; wf[2] = a.z; wf[3] = a.w;
         wf[4] = b.x; wf[5] = b.y; wf[6] = b.z; wf[7] = b.w;
       }
-      Pack8 out;
+      Vec8<A> out;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(__fmul_rn(__fmul_rn(k, wf[e]), __half2float(xv[i].h[e])));
+      for (int e = 0; e < 8; ++e) out.h[e] = from_f32<A>(__fmul_rn(__fmul_rn(k, wf[e]), to_f32(xv[i].h[e])));
       st_global_16(yr + v * 8, out.u);
     }
   }
@@ -107,22 +118,23 @@ static int rms_meta(const ops_rms_norm_args *a, RmsMeta *m) {
   return OPS_OK;
 }
 
-template <class W>
-static void launch_rows(const ops_rms_norm_args *a, const RmsMeta &m, cudaStream_t s) {
+template <class A, class W, bool ADD = false>
+static void launch_rows(const ops_rms_norm_args *a, const RmsMeta &m, cudaStream_t s, const void *r_base = nullptr, long long nsr = 0) {
   const int nvec = (int)(m.d / 8);
   int vpt = 1;
   while (vpt < 4 && (nvec + vpt - 1) / vpt > 256) vpt *= 2;  // prefer <= 256 threads per row
   while ((nvec + vpt - 1) / vpt > 1024) vpt *= 2;            // vpt <= 4 guaranteed by the caller
   int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
-  __half *y = (__half *)a->y_base;
-  const __half *x = (const __half *)a->x_base;
+  A *y = (A *)a->y_base;
+  A *x = (A *)a->x_base;
   const W *w = (const W *)a->w_base;
+  const A *r = (const A *)r_base;
   const long long nsy = a->y_layout.strides[0], nsx = a->x_layout.strides[0];
   dim3 grid((unsigned)m.n);
   switch (vpt) {
-    case 1: rms_norm_rows_kernel<1, W><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon); break;
-    case 2: rms_norm_rows_kernel<2, W><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon); break;
-    default: rms_norm_rows_kernel<4, W><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon); break;
+    case 1: rms_norm_rows_kernel<1, A, W, ADD><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon, r, nsr); break;
+    case 2: rms_norm_rows_kernel<2, A, W, ADD><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon, r, nsr); break;
+    default: rms_norm_rows_kernel<4, A, W, ADD><<<grid, threads, 0, s>>>(y, nsy, x, nsx, w, (int)m.d, a->epsilon, r, nsr); break;
   }
 }
 
@@ -158,23 +170,63 @@ OPS_API int ops_rms_norm_launch(const ops_rms_norm *op, const ops_rms_norm_args 
   const isz dsw = a->w_layout.strides[0];
   if (dyn(m.n) || dyn(m.d) || dyn(nsy) || dyn(dsy) || dyn(nsx) || dyn(dsx) || dyn(dsw) || dyn(a->epsilon))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "rms_norm: every shape, stride and epsilon must be static at launch");
-  const bool a16 = m.dt_a == OPS_DT_F16, a32 = m.dt_a == OPS_DT_F32;
-  const bool w16 = m.dt_w == OPS_DT_F16, w32 = m.dt_w == OPS_DT_F32;
-  if (!((a16 && (w16 || w32)) || (a32 && w32)))
-    return fail(OPS_TYPE_NOT_SUPPORT, "rms_norm: (w, a) must be (f16,f16), (f32,f16) or (f32,f32)");
+  const bool a16 = m.dt_a == OPS_DT_F16, abf = m.dt_a == OPS_DT_BF16, a32 = m.dt_a == OPS_DT_F32;
+  const bool w16 = m.dt_w == OPS_DT_F16, wbf = m.dt_w == OPS_DT_BF16, w32 = m.dt_w == OPS_DT_F32;
+  if (!((a16 && (w16 || w32)) || (abf && (wbf || w32)) || (a32 && w32)))
+    return fail(OPS_TYPE_NOT_SUPPORT, "rms_norm: (w, a) must be (f16,f16), (f32,f16), (bf16,bf16), (f32,bf16) or (f32,f32)");
   if (m.n == 0 || m.d == 0) return OPS_OK;
   if (m.n > 0x7fffffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "rms_norm: n too large");
   if (!a->y_base || !a->x_base || !a->w_base) return fail(OPS_DYNAMIC_NOT_SUPPORT, "rms_norm: null base pointer at launch");
   cudaStream_t s = (cudaStream_t)stream;
   cudaSetDevice(op->base.device);
 
-  const bool fast = a16 && dsx == 2 && dsy == 2 && dsw == (isz)dt_size(m.dt_w) && m.d % 8 == 0 && m.d <= 8 * 4 * 1024 &&
+  const bool fast = (a16 || abf) && dsx == 2 && dsy == 2 && dsw == (isz)dt_size(m.dt_w) && m.d % 8 == 0 && m.d <= 8 * 4 * 1024 &&
                     nsx % 16 == 0 && nsy % 16 == 0 && aligned(a->x_base, 16) && aligned(a->y_base, 16) && aligned(a->w_base, 16);
   if (fast) {
-    if (w16) launch_rows<__half>(a, m, s);
-    else launch_rows<float>(a, m, s);
+    if (a16 && w16) launch_rows<__half, __half>(a, m, s);
+    else if (a16) launch_rows<__half, float>(a, m, s);
+    else if (wbf) launch_rows<__nv_bfloat16, __nv_bfloat16>(a, m, s);
+    else launch_rows<__nv_bfloat16, float>(a, m, s);
   } else if (a16 && w16) launch_generic<__half, __half>(a, m, s);
   else if (a16) launch_generic<__half, float>(a, m, s);
+  else if (abf && wbf) launch_generic<__nv_bfloat16, __nv_bfloat16>(a, m, s);
+  else if (abf) launch_generic<__nv_bfloat16, float>(a, m, s);
   else launch_generic<float, float>(a, m, s);
   return check_launch("rms_norm");
+}
+
+// rms_norm with the residual add in front of it folded in: x <- x + r (in place), y <- rms_norm(x).  No counterpart in the
+// crate, which chains add and rms_norm as two operators; one pass over the row instead of two.  Takes the layouts the
+// vectorised kernel takes (f16 or bf16 rows with unit inner stride, 16-byte aligned, d a multiple of 8 up to 32768) and
+// answers OPS_ARGS_NOT_SUPPORT otherwise: chain ops_add_launch and ops_rms_norm_launch then.
+OPS_API int ops_rms_norm_add_launch(const ops_rms_norm *op, const ops_rms_norm_add_args *aa, void *stream) {
+  const ops_rms_norm_args *a = &aa->norm;
+  RmsMeta m;
+  OPS_TRY(rms_meta(a, &m));
+  if (aa->r_layout.ndim != 2) return fail(OPS_RANK_NOT_SUPPORT, "r.ndim = %u, 2 expected", aa->r_layout.ndim);
+  if (aa->r_layout.dt != m.dt_a) return fail(OPS_TYPE_MISMATCH, "r and x element types differ");
+  const isz nsy = a->y_layout.strides[0], dsy = a->y_layout.strides[1];
+  const isz nsx = a->x_layout.strides[0], dsx = a->x_layout.strides[1];
+  const isz nsr = aa->r_layout.strides[0], dsr = aa->r_layout.strides[1];
+  const isz dsw = a->w_layout.strides[0];
+  if (dyn(m.n) || dyn(m.d) || dyn(nsy) || dyn(dsy) || dyn(nsx) || dyn(dsx) || dyn(nsr) || dyn(dsr) || dyn(dsw) || dyn(a->epsilon) ||
+      dyn(aa->r_layout.shape[0]) || dyn(aa->r_layout.shape[1]))
+    return fail(OPS_DYNAMIC_NOT_SUPPORT, "rms_norm_add: every shape, stride and epsilon must be static at launch");
+  if (aa->r_layout.shape[0] != m.n || aa->r_layout.shape[1] != m.d) return fail(OPS_SHAPE_MISMATCH, "shape of r differs from x");
+  const bool a16 = m.dt_a == OPS_DT_F16, abf = m.dt_a == OPS_DT_BF16;
+  const bool w16 = m.dt_w == OPS_DT_F16, wbf = m.dt_w == OPS_DT_BF16, w32 = m.dt_w == OPS_DT_F32;
+  if (!((a16 && (w16 || w32)) || (abf && (wbf || w32)))) return fail(OPS_TYPE_NOT_SUPPORT, "rms_norm_add: (w, a) must be (f16,f16), (f32,f16), (bf16,bf16) or (f32,bf16)");
+  if (m.n == 0 || m.d == 0) return OPS_OK;
+  if (m.n > 0x7fffffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "rms_norm_add: n too large");
+  if (!a->y_base || !a->x_base || !a->w_base || !aa->r_base) return fail(OPS_DYNAMIC_NOT_SUPPORT, "rms_norm_add: null base pointer at launch");
+  const bool fast = dsx == 2 && dsy == 2 && dsr == 2 && dsw == (isz)dt_size(m.dt_w) && m.d % 8 == 0 && m.d <= 8 * 4 * 1024 && nsx % 16 == 0 &&
+                    nsy % 16 == 0 && nsr % 16 == 0 && aligned(a->x_base, 16) && aligned(a->y_base, 16) && aligned(a->w_base, 16) && aligned(aa->r_base, 16);
+  if (!fast) return fail(OPS_ARGS_NOT_SUPPORT, "rms_norm_add: needs contiguous, 16-byte aligned rows with d a multiple of 8 (<= 32768); chain add and rms_norm instead");
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaSetDevice(op->base.device);
+  if (a16 && w16) launch_rows<__half, __half, true>(a, m, s, aa->r_base, nsr);
+  else if (a16) launch_rows<__half, float, true>(a, m, s, aa->r_base, nsr);
+  else if (wbf) launch_rows<__nv_bfloat16, __nv_bfloat16, true>(a, m, s, aa->r_base, nsr);
+  else launch_rows<__nv_bfloat16, float, true>(a, m, s, aa->r_base, nsr);
+  return check_launch("rms_norm_add");
 }

@@ -21,8 +21,8 @@ struct RopeDivisors {
   float v[ROPE_MAX_HALF];
 };
 
-template <class P>
-__global__ void __launch_bounds__(256) rope_f16_kernel(__half *__restrict__ t, long long st, long long sh, const P *__restrict__ pos,
+template <class E, class P>
+__global__ void __launch_bounds__(256) rope_f16_kernel(E *__restrict__ t, long long st, long long sh, const P *__restrict__ pos,
                                                        long long sp, int nh, int half_dh, const __grid_constant__ RopeDivisors div) {
   extern __shared__ float2 sincos_tab[];  // [half_dh] (sin, cos)
   const long long tok = blockIdx.x;
@@ -33,20 +33,20 @@ __global__ void __launch_bounds__(256) rope_f16_kernel(__half *__restrict__ t, l
     sincos_tab[k] = make_float2(s, c);
   }
   __syncthreads();
-  __half *row = byte_off(t, tok * st);
+  E *row = byte_off(t, tok * st);
   const int vec_per_head = half_dh >> 2;  // 4 pairs = 8 halves per vector
   const int total = nh * vec_per_head;
   for (int v = threadIdx.x; v < total; v += blockDim.x) {
     const int head = v / vec_per_head, kv = v - head * vec_per_head;
-    __half *ptr = byte_off(row, (long long)head * sh) + kv * 8;
-    Pack8 in, out;
+    E *ptr = byte_off(row, (long long)head * sh) + kv * 8;
+    Vec8<E> in, out;
     in.u = ld_global_16(ptr);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 sc = sincos_tab[kv * 4 + e];
-      const float a = __half2float(in.h[2 * e]), b = __half2float(in.h[2 * e + 1]);
-      out.h[2 * e] = __float2half_rn(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
-      out.h[2 * e + 1] = __float2half_rn(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
+      const float a = to_f32(in.h[2 * e]), b = to_f32(in.h[2 * e + 1]);
+      out.h[2 * e] = from_f32<E>(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
+      out.h[2 * e + 1] = from_f32<E>(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
     }
     st_global_16(ptr, out.u);
   }
@@ -121,7 +121,7 @@ OPS_API int ops_rope_launch(const ops_rope *op, const ops_rope_args *a, void *ws
   if (dyn(m.nt) || dyn(nh) || dyn(dh) || dyn(st) || dyn(sh) || dyn(sd) || dyn(sp) || dyn(a->theta))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "rope: every shape, stride and theta must be static at launch");
   if (sd != (isz)dt_size(m.dt_t)) return fail(OPS_STRIDES_NOT_SUPPORT, "rope: last dim of t must be contiguous");
-  if (m.dt_t != OPS_DT_F16 && m.dt_t != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "rope: t must be f16 or f32");
+  if (m.dt_t != OPS_DT_F16 && m.dt_t != OPS_DT_BF16 && m.dt_t != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "rope: t must be f16, bf16 or f32");
   if (m.dt_p != OPS_DT_U32 && m.dt_p != OPS_DT_U64) return fail(OPS_TYPE_NOT_SUPPORT, "rope: p must be u32 or u64");
   if (dh % 2) return fail(OPS_SHAPE_NOT_SUPPORT, "rope: dh must be even");
   if (m.nt == 0 || nh == 0 || dh == 0) return OPS_OK;
@@ -135,18 +135,23 @@ OPS_API int ops_rope_launch(const ops_rope *op, const ops_rope_args *a, void *ws
   const int use_table = half_dh <= ROPE_MAX_HALF;
   if (use_table)
     for (int k = 0; k < half_dh; ++k) div.v[k] = powf(a->theta, (float)k / (float)half_dh);
-  const bool fast = m.dt_t == OPS_DT_F16 && use_table && dh % 8 == 0 && st % 16 == 0 && sh % 16 == 0 && aligned(a->t_base, 16);
+  const bool t16 = m.dt_t == OPS_DT_F16 || m.dt_t == OPS_DT_BF16;
+  const bool fast = t16 && use_table && dh % 8 == 0 && st % 16 == 0 && sh % 16 == 0 && aligned(a->t_base, 16);
   const dim3 grid((unsigned)m.nt);
   if (fast) {
     const usz smem = (usz)half_dh * sizeof(float2);
-    if (m.dt_p == OPS_DT_U32)
-      rope_f16_kernel<uint32_t><<<grid, 256, smem, s>>>((__half *)a->t_base, st, sh, (const uint32_t *)a->p_base, sp, (int)nh, half_dh, div);
-    else
-      rope_f16_kernel<unsigned long long><<<grid, 256, smem, s>>>((__half *)a->t_base, st, sh, (const unsigned long long *)a->p_base, sp, (int)nh, half_dh, div);
+#define ROPE_FAST(E, P) rope_f16_kernel<E, P><<<grid, 256, smem, s>>>((E *)a->t_base, st, sh, (const P *)a->p_base, sp, (int)nh, half_dh, div)
+    if (m.dt_t == OPS_DT_F16 && m.dt_p == OPS_DT_U32) ROPE_FAST(__half, uint32_t);
+    else if (m.dt_t == OPS_DT_F16) ROPE_FAST(__half, unsigned long long);
+    else if (m.dt_p == OPS_DT_U32) ROPE_FAST(__nv_bfloat16, uint32_t);
+    else ROPE_FAST(__nv_bfloat16, unsigned long long);
+#undef ROPE_FAST
   } else {
 #define ROPE_GENERIC(T, P) rope_generic_kernel<T, P><<<grid, 256, 0, s>>>((T *)a->t_base, st, sh, (const P *)a->p_base, sp, (int)nh, half_dh, a->theta, div, use_table)
     if (m.dt_t == OPS_DT_F16 && m.dt_p == OPS_DT_U32) ROPE_GENERIC(__half, uint32_t);
     else if (m.dt_t == OPS_DT_F16) ROPE_GENERIC(__half, unsigned long long);
+    else if (m.dt_t == OPS_DT_BF16 && m.dt_p == OPS_DT_U32) ROPE_GENERIC(__nv_bfloat16, uint32_t);
+    else if (m.dt_t == OPS_DT_BF16) ROPE_GENERIC(__nv_bfloat16, unsigned long long);
     else if (m.dt_p == OPS_DT_U32) ROPE_GENERIC(float, uint32_t);
     else ROPE_GENERIC(float, unsigned long long);
 #undef ROPE_GENERIC

@@ -142,10 +142,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   d |= (uint64_t)2 << 61;  // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: f16 x f16 -> f32, dense.  *_mn_major: 0 = K-major operand, 1 = MN-major.
-__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
+// Instruction descriptor of kind::f16: A, B both f16 or both bf16 (bits 7-9 and 10-12: 0 = f16, 1 = bf16), f32
+// accumulator (bits 4-5 = 1), dense.  *_mn_major: 0 = K-major operand, 1 = MN-major.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn_major, int b_mn_major, int bf16 = 0) {
+  return (1u << 4) | ((uint32_t)(bf16 ? 1 : 0) << 7) | ((uint32_t)(bf16 ? 1 : 0) << 10) | ((uint32_t)a_mn_major << 15) |
+         ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {

@@ -18,18 +18,19 @@ __device__ __forceinline__ float swiglu_f32(float a, float b) {
 
 // Fast path: f16, unit inner strides, d % 8 == 0, 16-byte aligned rows.  blockIdx.x = row, blockIdx.y = 2048-column
 // chunk (blockIdx.x = row * chunks + chunk): no per-element index division, one 128-bit gate load and one up load in flight per thread, thousands of CTAs.
-__global__ void __launch_bounds__(256) swiglu_vec_kernel(__half *__restrict__ gate, long long sgn, const __half *__restrict__ up,
+template <class E>
+__global__ void __launch_bounds__(256) swiglu_vec_kernel(E *__restrict__ gate, long long sgn, const E *__restrict__ up,
                                                          long long sun, int vec_per_row, int chunks) {
   const unsigned row = blockIdx.x / (unsigned)chunks, chunk = blockIdx.x - row * (unsigned)chunks;  // one division per CTA
   const int v = (int)chunk * (int)blockDim.x + (int)threadIdx.x;
   if (v >= vec_per_row) return;
-  __half *g = byte_off(gate, (long long)row * sgn) + v * 8;
-  const __half *u = byte_off(up, (long long)row * sun) + v * 8;
-  Pack8 gv, uv, out;
+  E *g = byte_off(gate, (long long)row * sgn) + v * 8;
+  const E *u = byte_off(up, (long long)row * sun) + v * 8;
+  Vec8<E> gv, uv, out;
   gv.u = ld_global_16(g);
   uv.u = ld_stream_16(u);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) out.h[e] = __float2half_rn(swiglu_f32(__half2float(gv.h[e]), __half2float(uv.h[e])));
+  for (int e = 0; e < 8; ++e) out.h[e] = from_f32<E>(swiglu_f32(to_f32(gv.h[e]), to_f32(uv.h[e])));
   st_global_16(g, out.u);
 }
 
@@ -85,25 +86,30 @@ OPS_API int ops_swiglu_launch(const ops_swiglu *op, const ops_swiglu_args *a, vo
   const isz sun = a->up_layout.strides[0], sud = a->up_layout.strides[1];
   if (dyn(m.n) || dyn(m.d) || dyn(sgn) || dyn(sgd) || dyn(sun) || dyn(sud))
     return fail(OPS_DYNAMIC_NOT_SUPPORT, "swiglu: every shape and stride must be static at launch");
-  if (m.dt != OPS_DT_F16 && m.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "swiglu: f16 or f32 expected");
+  if (m.dt != OPS_DT_F16 && m.dt != OPS_DT_BF16 && m.dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "swiglu: f16, bf16 or f32 expected");
   if (m.n == 0 || m.d == 0) return OPS_OK;
   if (!a->gate_base || !a->up_base) return fail(OPS_DYNAMIC_NOT_SUPPORT, "swiglu: null base pointer at launch");
   cudaStream_t s = (cudaStream_t)stream;
   cudaSetDevice(op->base.device);
   const int max_blocks = op->base.sm_count * 8;
 
-  const bool fast = m.dt == OPS_DT_F16 && sgd == 2 && sud == 2 && m.d % 8 == 0 && sgn % 16 == 0 && sun % 16 == 0 &&
+  const bool fast = (m.dt == OPS_DT_F16 || m.dt == OPS_DT_BF16) && sgd == 2 && sud == 2 && m.d % 8 == 0 && sgn % 16 == 0 && sun % 16 == 0 &&
                     aligned(a->gate_base, 16) && aligned(a->up_base, 16) && m.n * ((m.d / 8 + 255) / 256) <= 0x7fffffffu;
   if (fast) {
     const int vpr = (int)(m.d / 8);
     const int chunks = (vpr + 255) / 256;
-    swiglu_vec_kernel<<<(unsigned)(m.n * (usz)chunks), 256, 0, s>>>((__half *)a->gate_base, sgn, (const __half *)a->up_base, sun, vpr, chunks);
+    if (m.dt == OPS_DT_F16)
+      swiglu_vec_kernel<__half><<<(unsigned)(m.n * (usz)chunks), 256, 0, s>>>((__half *)a->gate_base, sgn, (const __half *)a->up_base, sun, vpr, chunks);
+    else
+      swiglu_vec_kernel<__nv_bfloat16><<<(unsigned)(m.n * (usz)chunks), 256, 0, s>>>((__nv_bfloat16 *)a->gate_base, sgn, (const __nv_bfloat16 *)a->up_base, sun, vpr, chunks);
   } else {
     const long long total = (long long)m.n * (long long)m.d;
     const long long blocks = (total + 255) / 256;
     const unsigned grid = (unsigned)(blocks < max_blocks ? blocks : max_blocks);
     if (m.dt == OPS_DT_F16)
       swiglu_generic_kernel<__half><<<grid, 256, 0, s>>>((__half *)a->gate_base, sgn, sgd, (const __half *)a->up_base, sun, sud, (long long)m.d, total);
+    else if (m.dt == OPS_DT_BF16)
+      swiglu_generic_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16 *)a->gate_base, sgn, sgd, (const __nv_bfloat16 *)a->up_base, sun, sud, (long long)m.d, total);
     else
       swiglu_generic_kernel<float><<<grid, 256, 0, s>>>((float *)a->gate_base, sgn, sgd, (const float *)a->up_base, sun, sud, (long long)m.d, total);
   }

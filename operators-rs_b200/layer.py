@@ -8,9 +8,8 @@ them for one Llama-shaped layer (BASELINE config 3) and its tensor-parallel form
 
 Every step is one `Operator.launch` through the C ABI on torch-owned device buffers.  Tensor
 parallelism follows the usual split: QKV and gate|up by columns (whole heads per rank, the GQA group
-kept together), O and down by rows, f16 sum all_reduce of the [T, d] partials.  Rank 0 folds the
-residual into its partial with beta = 1; the other ranks write their partial to a scratch buffer
-(beta = 0) that becomes their residual stream after the all_reduce — no extra copy, no `add` operator.
+kept together), O and down by rows, f16 sum all_reduce of the [T, d] partials — see DecoderLayer for
+how the partials and the residual meet.
 """
 from dataclasses import dataclass
 
@@ -72,26 +71,60 @@ def _contig(x):
     return np.ascontiguousarray(x)
 
 
+class _Lane:
+    """What one stream of the tensor-parallel tail needs for itself: operator handles whose scratch must not be shared
+    between streams, the communicator of that stream and (when attached) its zero-copy all_reduce input region."""
+
+    def __init__(self, idx, comm, algo, d, device, own_stream):
+        import torch
+        self.rms_norm, self.swiglu, self.mat_mul = RmsNorm(idx), Swiglu(idx), MatMul(idx)
+        self.comm = comm
+        self.all_reduce = None
+        self.direct = None
+        if comm is not None:
+            self.all_reduce = AllReduce(comm)
+            self.all_reduce.set_algo(algo)
+            try:
+                self.direct = comm.p2p_direct(torch.float16)
+            except Exception:
+                self.direct = None  # no staging attached: NCCL only
+        self.stream = torch.cuda.Stream(device) if own_stream else None
+        self.d = d
+
+
 class DecoderLayer:
-    """One (possibly tensor-parallel) decoder layer on one GPU.  `weights` are this rank's shards on the device."""
+    """One (possibly tensor-parallel) decoder layer on one GPU.  `weights` are this rank's shards on the device.
+
+    Tensor-parallel exchange, in order of preference:
+      * direct (default once peer-to-peer staging is attached, messages of 1 MiB or more): the row-parallel projection
+        writes its partial straight into the communicator's zero-copy region and ONE kernel adds the partials of all
+        ranks onto the residual stream (ops_all_reduce_add_launch) — no copy-in, no residual read in the GEMM;
+      * otherwise rank 0 folds the residual into its partial with beta = 1 and an in-place all_reduce follows.
+    With `pipeline` > 1 the rows are cut into that many chunks after attention and each chunk runs the rest of the
+    chain (everything after attention is row-wise independent) on its own stream with its own communicator, so the
+    exchange of one chunk overlaps the projections of the other.
+    """
 
     STEPS = ("rms_norm_1", "mat_mul_qkv", "rope", "attention", "mat_mul_o", "all_reduce_1", "rms_norm_2", "mat_mul_gate_up",
              "swiglu", "mat_mul_down", "all_reduce_2")
+    DIRECT_MIN_BYTES = 1 << 20
 
-    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1, fused_all_reduce=False):
+    def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1,
+                 fused_all_reduce=False, direct=True, pipeline=1, comms=None):
         import torch
         self.overlap_chunks = max(1, int(overlap_chunks))
         self.fused_all_reduce = bool(fused_all_reduce) and tp > 1  # row-parallel GEMM and its all_reduce as one kernel
-        self.comm = comm
+        comms = list(comms) if comms else ([comm] if comm is not None else [])
+        self.comm = comms[0] if comms else None
         self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and self.overlap_chunks > 1) else None
         self.cfg, self.w, self.device, self.tp, self.rank = cfg, weights, device, tp, rank
         idx = device.index if device.index is not None else 0
-        self.rms_norm, self.rope, self.swiglu = RmsNorm(idx), Rope(idx), Swiglu(idx)
-        self.mat_mul, self.attention = MatMul(idx), Attention(idx)
-        self.all_reduce = None
-        if tp > 1:
-            self.all_reduce = AllReduce(comm)
-            self.all_reduce.set_algo(all_reduce_algo)
+        self.rope, self.attention = Rope(idx), Attention(idx)
+        self.pipeline = max(1, min(int(pipeline), len(comms))) if tp > 1 else 1
+        self.lanes = [_Lane(idx, comms[i] if tp > 1 else None, all_reduce_algo, cfg.d, device, self.pipeline > 1) for i in range(self.pipeline)]
+        self.rms_norm, self.swiglu, self.mat_mul = self.lanes[0].rms_norm, self.lanes[0].swiglu, self.lanes[0].mat_mul
+        self.all_reduce = self.lanes[0].all_reduce
+        self.direct = bool(direct) and tp > 1 and not self.fused_all_reduce and self.overlap_chunks == 1 and all(l.direct is not None for l in self.lanes)
         self.nq, self.nkv, self.f = cfg.nh // tp, cfg.nkvh // tp, cfg.ffn // tp
         T, f16 = max_tokens, torch.float16
         self.h = torch.empty(T, cfg.d, dtype=f16, device=device)
@@ -99,17 +132,18 @@ class DecoderLayer:
         self.att_out = torch.empty(T, self.nq * cfg.dh, dtype=f16, device=device)
         self.gu = torch.empty(T, 2 * self.f, dtype=f16, device=device)
         self.scratch = torch.empty(T, cfg.d, dtype=f16, device=device) if (tp > 1 and rank != 0) else None
-        ws_bytes = self.nq * T * (cfg.dh + T) * 2
-        self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        self.ws = torch.empty(16, dtype=torch.uint8, device=device)  # the fused attention kernels need none; the chain allocates
         self.max_tokens = T
 
     def forward(self, x, pos, on_step=None):
-        """x [T, d] f16 on the device (the residual stream; updated in place on rank 0 / single GPU), pos [T] u32.
-        Returns the tensor holding the layer output.  `on_step(name)` is called after each launch (timing hooks)."""
+        """x [T, d] f16 on the device (the residual stream; updated in place on rank 0 / single GPU / in direct mode),
+        pos [T] u32.  Returns the tensor holding the layer output.  `on_step(name)` is called after each launch (timing
+        hooks; with it the tail runs unpipelined so that the hooks see one operator at a time)."""
+        import torch
         cfg, T = self.cfg, x.shape[0]
         assert T <= self.max_tokens
         mark = on_step or (lambda name: None)
-        h, qkv, att_out, gu = self.h[:T], self.qkv[:T], self.att_out[:T], self.gu[:T]
+        h, qkv, att_out = self.h[:T], self.qkv[:T], self.att_out[:T]
         self.rms_norm.launch(RmsNormArgs.of(h, x, self.w["w_norm1"], cfg.eps))
         mark("rms_norm_1")
         self.mat_mul.launch(MatMulArgs.of(qkv, 0.0, h, self.w["w_qkv"], 1.0))
@@ -123,48 +157,78 @@ class DecoderLayer:
         o = att_out.view(T, self.nq, cfg.dh).permute(1, 0, 2)
         self.attention.launch(AttentionArgs.of(q, k, v, o, MASK_CAUSAL), self.ws)
         mark("attention")
-        x = self._project_and_reduce(x, att_out, self.w["w_o"], "mat_mul_o", "all_reduce_1", mark)
-        self.rms_norm.launch(RmsNormArgs.of(h, x, self.w["w_norm2"], cfg.eps))
-        mark("rms_norm_2")
-        self.mat_mul.launch(MatMulArgs.of(gu, 0.0, h, self.w["w_gu"], 1.0))
-        mark("mat_mul_gate_up")
-        self.swiglu.launch(SwigluArgs.of(gu[:, : self.f], gu[:, self.f:]))
-        mark("swiglu")
-        x = self._project_and_reduce(x, gu[:, : self.f], self.w["w_down"], "mat_mul_down", "all_reduce_2", mark)
-        return x
+        if self.pipeline > 1 and on_step is None and T >= 256 * self.pipeline and self._use_direct(T // self.pipeline):
+            main = torch.cuda.current_stream()
+            ready = main.record_event()
+            step = (T + self.pipeline - 1) // self.pipeline
+            step = (step + 127) // 128 * 128
+            for lane, lo in zip(self.lanes, range(0, T, step)):
+                hi = min(T, lo + step)
+                lane.stream.wait_event(ready)
+                with torch.cuda.stream(lane.stream):
+                    self._tail(lane, x, lo, hi, mark)
+            for lane in self.lanes:
+                main.wait_stream(lane.stream)
+            return x
+        return self._tail(self.lanes[0], x, 0, T, mark)
 
-    def _project_and_reduce(self, x, a, w, mm_name, ar_name, mark):
-        """Row-parallel projection + all_reduce.  With overlap_chunks > 1 the token dimension is cut into chunks: the
-        all_reduce of chunk c runs on a second stream while the tensor cores work on chunk c+1."""
+    def _use_direct(self, rows):
+        return self.direct and rows * self.cfg.d * 2 >= self.DIRECT_MIN_BYTES
+
+    def _tail(self, lane, x, lo, hi, mark):
+        """Everything after attention for rows [lo, hi): O projection, exchange, rms_norm, gate|up, swiglu, down, exchange."""
+        cfg = self.cfg
+        h, att_out, gu = self.h[lo:hi], self.att_out[lo:hi], self.gu[lo:hi]
+        xr = x[lo:hi]
+        xr = self._project_and_reduce(lane, xr, att_out, self.w["w_o"], "mat_mul_o", "all_reduce_1", mark, lo, hi)
+        lane.rms_norm.launch(RmsNormArgs.of(h, xr, self.w["w_norm2"], cfg.eps))
+        mark("rms_norm_2")
+        lane.mat_mul.launch(MatMulArgs.of(gu, 0.0, h, self.w["w_gu"], 1.0))
+        mark("mat_mul_gate_up")
+        lane.swiglu.launch(SwigluArgs.of(gu[:, : self.f], gu[:, self.f:]))
+        mark("swiglu")
+        xr = self._project_and_reduce(lane, xr, gu[:, : self.f], self.w["w_down"], "mat_mul_down", "all_reduce_2", mark, lo, hi)
+        return xr
+
+    def _project_and_reduce(self, lane, x, a, w, mm_name, ar_name, mark, lo, hi):
+        """Row-parallel projection + exchange for the rows held in `x`.  With overlap_chunks > 1 the token dimension is cut
+        into chunks: the all_reduce of chunk c runs on a second stream while the tensor cores work on chunk c+1."""
         import torch
         T = x.shape[0]
+        if self.tp > 1 and self._use_direct(T):
+            part = lane.direct[: T * self.cfg.d].view(T, self.cfg.d)
+            lane.mat_mul.launch(MatMulArgs.of(part, 0.0, a, w, 1.0))
+            mark(mm_name)
+            lane.all_reduce.launch_add(AllReduceArgs.of(x, part))
+            mark(ar_name)
+            return x
         first = self.tp == 1 or self.rank == 0
         # rank 0 (and the single-GPU case) folds the residual in: x <- x + a w.  The other ranks never read the
         # residual: their partial goes to scratch, which holds the stream from here on.
-        out, beta = (x, 1.0) if first else (self.scratch[:T], 0.0)
+        out, beta = (x, 1.0) if first else (self.scratch[lo:hi], 0.0)
         chunks = self.overlap_chunks if (self.tp > 1 and T >= 256 * self.overlap_chunks) else 1
         if self.fused_all_reduce:
-            self.mat_mul.launch_all_reduce(self.comm, MatMulArgs.of(out, beta, a, w, 1.0))
+            lane.mat_mul.launch_all_reduce(self.comm, MatMulArgs.of(out, beta, a, w, 1.0))
             mark(mm_name)
             mark(ar_name)
             return out
         if chunks == 1:
-            self.mat_mul.launch(MatMulArgs.of(out, beta, a, w, 1.0))
+            lane.mat_mul.launch(MatMulArgs.of(out, beta, a, w, 1.0))
             mark(mm_name)
             if self.tp > 1:
-                self.all_reduce.launch(AllReduceArgs.of(out, out))
+                lane.all_reduce.launch(AllReduceArgs.of(out, out))
                 mark(ar_name)
             return out
         main = torch.cuda.current_stream()
         step = (T + chunks - 1) // chunks
         step = (step + 127) // 128 * 128
-        for lo in range(0, T, step):
-            hi = min(T, lo + step)
-            self.mat_mul.launch(MatMulArgs.of(out[lo:hi], beta, a[lo:hi], w, 1.0))
+        for c0 in range(0, T, step):
+            c1 = min(T, c0 + step)
+            lane.mat_mul.launch(MatMulArgs.of(out[c0:c1], beta, a[c0:c1], w, 1.0))
             ready = main.record_event()
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                self.all_reduce.launch(AllReduceArgs.of(out[lo:hi], out[lo:hi]))
+                lane.all_reduce.launch(AllReduceArgs.of(out[c0:c1], out[c0:c1]))
         mark(mm_name)
         main.wait_stream(self.comm_stream)
         mark(ar_name)

@@ -29,6 +29,10 @@
 #include "../include/ops_b200.h"
 
 typedef _Float16 f16;
+// bf16 has no CPU path in the reference (its operators take f16/f32/f64); the crate's GPU handle names nv_bfloat16
+// (operators/src/handle/cuda/mod.rs:188-210).  For it the oracle is the same restated algorithm with bf16 rounding points:
+// __bf16 converts to and from float with round-to-nearest-even, like f16 above.
+typedef __bf16 bf16;
 typedef ptrdiff_t isz;
 typedef size_t usz;
 
@@ -102,6 +106,14 @@ inline int16_t total_key(f16 v) {  // f16::total_cmp order
 }
 template <class T> inline bool total_less(T a, T b);
 template <> inline bool total_less<f16>(f16 a, f16 b) { return total_key(a) < total_key(b); }
+template <> inline bool total_less<bf16>(bf16 a, bf16 b) {
+  int16_t x, y;
+  std::memcpy(&x, &a, 2);
+  std::memcpy(&y, &b, 2);
+  x = (int16_t)(x ^ (int16_t)(((uint16_t)(x >> 15)) >> 1));
+  y = (int16_t)(y ^ (int16_t)(((uint16_t)(y >> 15)) >> 1));
+  return x < y;
+}
 template <> inline bool total_less<float>(float a, float b) {
   int32_t x, y;
   std::memcpy(&x, &a, 4);
@@ -397,6 +409,10 @@ int mat_mul(uint32_t dt, usz nd_c, const usz *sh_c, const isz *st_c, void *c, fl
       float al = (float)(f16)alpha, be = (float)(f16)beta;  // mat_mul/common_cpu/mod.rs:101
       gemm_f32acc<f16>(C.r, C.c, A.c, (f16 *)c + (isz)i * C.stride, C.rs, C.cs, read_c, be,
                        (const f16 *)a + (isz)i * A.stride, A.rs, A.cs, (const f16 *)b + (isz)i * B.stride, B.rs, B.cs, al);
+    } else if (dt == OPS_DT_BF16) {
+      float al = (float)(bf16)alpha, be = (float)(bf16)beta;
+      gemm_f32acc<bf16>(C.r, C.c, A.c, (bf16 *)c + (isz)i * C.stride, C.rs, C.cs, read_c, be,
+                        (const bf16 *)a + (isz)i * A.stride, A.rs, A.cs, (const bf16 *)b + (isz)i * B.stride, B.rs, B.cs, al);
     } else if (dt == OPS_DT_F32) {
       gemm_f32acc<float>(C.r, C.c, A.c, (float *)c + (isz)i * C.stride, C.rs, C.cs, read_c, beta,
                          (const float *)a + (isz)i * A.stride, A.rs, A.cs, (const float *)b + (isz)i * B.stride, B.rs,
@@ -422,7 +438,7 @@ template <class T> void softmax_dt(uint32_t, usz nh, usz seq, usz att, void *bas
 int attention(uint32_t dt, usz nh, usz nkvh, usz seq, usz att, usz dh, void *q, const isz *sq, const void *k,
               const isz *sk, const void *v, const isz *sv, void *o, const isz *so, int mask) {
   const usz es = orc_dtype_nbytes(dt);
-  if (dt != OPS_DT_F16 && dt != OPS_DT_F32 && dt != OPS_DT_F64) return OPS_TYPE_NOT_SUPPORT;
+  if (dt != OPS_DT_F16 && dt != OPS_DT_BF16 && dt != OPS_DT_F32 && dt != OPS_DT_F64) return OPS_TYPE_NOT_SUPPORT;
   if (nkvh == 0 || nh % nkvh) return OPS_SHAPE_MISMATCH;
   const usz group = nh / nkvh;
   const bool merge = sq[0] == (isz)seq * sq[1];  // merge_be(0, 2) on [nh, seq, dh]
@@ -455,6 +471,7 @@ int attention(uint32_t dt, usz nh, usz nkvh, usz seq, usz att, usz dh, void *q, 
   int e = mat_mul(dt, 3, sha, sta, attbuf.data(), 0.f, 3, shx, stx, qb, 3, shk, stk, k, alpha);
   if (e) return e;
   if (dt == OPS_DT_F16) softmax_dt<f16>(dt, nh, seq, att, attbuf.data(), mask);
+  else if (dt == OPS_DT_BF16) softmax_dt<bf16>(dt, nh, seq, att, attbuf.data(), mask);
   else if (dt == OPS_DT_F32) softmax_dt<float>(dt, nh, seq, att, attbuf.data(), mask);
   else softmax_dt<double>(dt, nh, seq, att, attbuf.data(), mask);
   const usz shv[3] = {nkvh, att, dh};
@@ -526,6 +543,7 @@ int all_reduce(uint32_t dt, usz p, usz len, void *const *bufs) {
       const void *src = bufs[r - stride];
       switch (dt) {
         case OPS_DT_F16: sum_into<f16, float>((f16 *)dst, (const f16 *)src, len); break;
+        case OPS_DT_BF16: sum_into<bf16, float>((bf16 *)dst, (const bf16 *)src, len); break;
         case OPS_DT_F32: sum_into<float, float>((float *)dst, (const float *)src, len); break;
         case OPS_DT_F64: sum_into<double, double>((double *)dst, (const double *)src, len); break;
         case OPS_DT_U32: sum_into<uint32_t, uint32_t>((uint32_t *)dst, (const uint32_t *)src, len); break;
@@ -560,6 +578,8 @@ ORC_API int orc_rms_norm(uint32_t dt_a, uint32_t dt_w, usz n, usz d, void *y, is
                          isz dsx, const void *w, isz dsw, float eps) {
   if (dt_w == OPS_DT_F16 && dt_a == OPS_DT_F16) rms_norm<f16, f16>(n, d, (f16 *)y, nsy, dsy, (const f16 *)x, nsx, dsx, (const f16 *)w, dsw, eps);
   else if (dt_w == OPS_DT_F32 && dt_a == OPS_DT_F16) rms_norm<float, f16>(n, d, (f16 *)y, nsy, dsy, (const f16 *)x, nsx, dsx, (const float *)w, dsw, eps);
+  else if (dt_w == OPS_DT_BF16 && dt_a == OPS_DT_BF16) rms_norm<bf16, bf16>(n, d, (bf16 *)y, nsy, dsy, (const bf16 *)x, nsx, dsx, (const bf16 *)w, dsw, eps);
+  else if (dt_w == OPS_DT_F32 && dt_a == OPS_DT_BF16) rms_norm<float, bf16>(n, d, (bf16 *)y, nsy, dsy, (const bf16 *)x, nsx, dsx, (const float *)w, dsw, eps);
   else if (dt_w == OPS_DT_F32 && dt_a == OPS_DT_F32) rms_norm<float, float>(n, d, (float *)y, nsy, dsy, (const float *)x, nsx, dsx, (const float *)w, dsw, eps);
   else if (dt_w == OPS_DT_F64 && dt_a == OPS_DT_F64) rms_norm<double, double>(n, d, (double *)y, nsy, dsy, (const double *)x, nsx, dsx, (const double *)w, dsw, eps);
   else return OPS_TYPE_NOT_SUPPORT;
@@ -571,6 +591,8 @@ ORC_API int orc_rope(uint32_t dt_t, uint32_t dt_p, usz nt, usz nh, usz dh, void 
 #define ROPE_CASE(A, DA, P, DP) if (dt_t == DA && dt_p == DP) { rope<A, P>(nt, nh, dh, (A *)t, st, sh, (const P *)p, sp, theta); return 0; }
   ROPE_CASE(f16, OPS_DT_F16, uint32_t, OPS_DT_U32)
   ROPE_CASE(f16, OPS_DT_F16, uint64_t, OPS_DT_U64)
+  ROPE_CASE(bf16, OPS_DT_BF16, uint32_t, OPS_DT_U32)
+  ROPE_CASE(bf16, OPS_DT_BF16, uint64_t, OPS_DT_U64)
   ROPE_CASE(float, OPS_DT_F32, uint32_t, OPS_DT_U32)
   ROPE_CASE(float, OPS_DT_F32, uint64_t, OPS_DT_U64)
   ROPE_CASE(double, OPS_DT_F64, uint32_t, OPS_DT_U32)
@@ -581,6 +603,7 @@ ORC_API int orc_rope(uint32_t dt_t, uint32_t dt_p, usz nt, usz nh, usz dh, void 
 
 ORC_API int orc_fused_softmax(uint32_t dt, usz nh, usz seq, usz att, void *base, isz sh, isz ss, isz sa, int mask) {
   if (dt == OPS_DT_F16) fused_softmax<f16>(nh, seq, att, (f16 *)base, sh, ss, sa, mask);
+  else if (dt == OPS_DT_BF16) fused_softmax<bf16>(nh, seq, att, (bf16 *)base, sh, ss, sa, mask);
   else if (dt == OPS_DT_F32) fused_softmax<float>(nh, seq, att, (float *)base, sh, ss, sa, mask);
   else if (dt == OPS_DT_F64) fused_softmax<double>(nh, seq, att, (double *)base, sh, ss, sa, mask);
   else return OPS_TYPE_NOT_SUPPORT;
@@ -589,6 +612,7 @@ ORC_API int orc_fused_softmax(uint32_t dt, usz nh, usz seq, usz att, void *base,
 
 ORC_API int orc_swiglu(uint32_t dt, usz n, usz d, void *gate, isz sgn, isz sgd, const void *up, isz sun, isz sud) {
   if (dt == OPS_DT_F16) swiglu<f16>(n, d, (f16 *)gate, sgn, sgd, (const f16 *)up, sun, sud);
+  else if (dt == OPS_DT_BF16) swiglu<bf16>(n, d, (bf16 *)gate, sgn, sgd, (const bf16 *)up, sun, sud);
   else if (dt == OPS_DT_F32) swiglu<float>(n, d, (float *)gate, sgn, sgd, (const float *)up, sun, sud);
   else if (dt == OPS_DT_F64) swiglu<double>(n, d, (double *)gate, sgn, sgd, (const double *)up, sun, sud);
   else return OPS_TYPE_NOT_SUPPORT;
@@ -678,6 +702,7 @@ ORC_API int orc_add(uint32_t dt, usz ndim, const usz *shape, void *c, const isz 
       ob += (isz)k * sb[d];
     }
     if (dt == OPS_DT_F16) *at((f16 *)c, oc) = (f16)((float)*at((const f16 *)a, oa) + (float)*at((const f16 *)b, ob));
+    else if (dt == OPS_DT_BF16) *at((bf16 *)c, oc) = (bf16)((float)*at((const bf16 *)a, oa) + (float)*at((const bf16 *)b, ob));
     else if (dt == OPS_DT_F32) *at((float *)c, oc) = *at((const float *)a, oa) + *at((const float *)b, ob);
     else if (dt == OPS_DT_F64) *at((double *)c, oc) = *at((const double *)a, oa) + *at((const double *)b, ob);
     else return OPS_TYPE_NOT_SUPPORT;
@@ -696,6 +721,7 @@ ORC_API int orc_add_rows(uint32_t dt, uint32_t dt_idx, usz batch, usz m, usz n, 
       for (usz j = 0; j < n; ++j) {
         const isz od = (isz)b * bsd + (isz)r * msd + (isz)j * nsd, os = (isz)id * kss + (isz)j * nss;
         if (dt == OPS_DT_F16) *at((f16 *)dst, od) = (f16)((float)*at((f16 *)dst, od) + (float)*at((const f16 *)src, os));
+        else if (dt == OPS_DT_BF16) *at((bf16 *)dst, od) = (bf16)((float)*at((bf16 *)dst, od) + (float)*at((const bf16 *)src, os));
         else if (dt == OPS_DT_F32) *at((float *)dst, od) += *at((const float *)src, os);
         else if (dt == OPS_DT_F64) *at((double *)dst, od) += *at((const double *)src, os);
         else return OPS_TYPE_NOT_SUPPORT;

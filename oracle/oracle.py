@@ -23,6 +23,42 @@ DT = {np.dtype(np.float16): 1, np.dtype(np.float32): 3, np.dtype(np.float64): 4,
 _lib = None
 
 
+class Bf16Array(np.ndarray):
+    """bf16 values held as their uint16 bit patterns (NumPy has no bf16 type).  Slices, reshapes and transposes keep
+    the tag, which is what tells the functions below to run the bf16 instantiation of the oracle."""
+
+
+def bf16_from_f32(a):
+    """Round f32 values to bf16 (nearest, ties to even) -> tagged uint16 array."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + 0x7FFF
+    return ((u + r) >> 16).astype(np.uint16).view(Bf16Array)
+
+
+def bf16_bits(a):
+    """Tag an array of uint16 bit patterns as bf16."""
+    return np.asarray(a, dtype=np.uint16).view(Bf16Array)
+
+
+def bf16_to_f32(a):
+    return (np.asarray(a).view(np.ndarray).astype(np.uint32) << 16).view(np.float32)
+
+
+def _dt(a):
+    if isinstance(a, Bf16Array):
+        return 2
+    return DT[a.dtype]
+
+
+def _zeros(shape, like):
+    z = np.zeros(shape, like.dtype)
+    return z.view(Bf16Array) if isinstance(like, Bf16Array) else z
+
+
+def _empty_like(a):
+    return _zeros(a.shape, a)
+
+
 def build():
     """Compile liboracle.so with the Makefile (g++)."""
     subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
@@ -79,7 +115,7 @@ def _arr_isz(vals):
 
 def rms_norm(y, x, w, eps):
     n, d = x.shape
-    _chk(lib().orc_rms_norm(DT[x.dtype], DT[w.dtype], _sz(n), _sz(d), _p(y), _isz(y.strides[0]), _isz(y.strides[1]),
+    _chk(lib().orc_rms_norm(_dt(x), _dt(w), _sz(n), _sz(d), _p(y), _isz(y.strides[0]), _isz(y.strides[1]),
                             _p(x), _isz(x.strides[0]), _isz(x.strides[1]), _p(w), _isz(w.strides[0]),
                             ctypes.c_float(eps)))
     return y
@@ -88,21 +124,21 @@ def rms_norm(y, x, w, eps):
 def rope(t, pos, theta):
     nt, nh, dh = t.shape
     assert t.strides[2] == t.itemsize
-    _chk(lib().orc_rope(DT[t.dtype], DT[pos.dtype], _sz(nt), _sz(nh), _sz(dh), _p(t), _isz(t.strides[0]),
+    _chk(lib().orc_rope(_dt(t), _dt(pos), _sz(nt), _sz(nh), _sz(dh), _p(t), _isz(t.strides[0]),
                         _isz(t.strides[1]), _p(pos), _isz(pos.strides[0]), ctypes.c_float(theta)))
     return t
 
 
 def fused_softmax(att, causal=True):
     nh, seq, al = att.shape
-    _chk(lib().orc_fused_softmax(DT[att.dtype], _sz(nh), _sz(seq), _sz(al), _p(att), _isz(att.strides[0]),
+    _chk(lib().orc_fused_softmax(_dt(att), _sz(nh), _sz(seq), _sz(al), _p(att), _isz(att.strides[0]),
                                  _isz(att.strides[1]), _isz(att.strides[2]), ctypes.c_int(1 if causal else 0)))
     return att
 
 
 def swiglu(gate, up):
     n, d = gate.shape
-    _chk(lib().orc_swiglu(DT[gate.dtype], _sz(n), _sz(d), _p(gate), _isz(gate.strides[0]), _isz(gate.strides[1]),
+    _chk(lib().orc_swiglu(_dt(gate), _sz(n), _sz(d), _p(gate), _isz(gate.strides[0]), _isz(gate.strides[1]),
                           _p(up), _isz(up.strides[0]), _isz(up.strides[1])))
     return gate
 
@@ -125,7 +161,7 @@ def rearrange(dst, src):
 
 
 def mat_mul(c, beta, a, b, alpha):
-    _chk(lib().orc_mat_mul(DT[c.dtype], _sz(c.ndim), _arr_sz(c.shape), _arr_isz(c.strides), _p(c), ctypes.c_float(beta),
+    _chk(lib().orc_mat_mul(_dt(c), _sz(c.ndim), _arr_sz(c.shape), _arr_isz(c.strides), _p(c), ctypes.c_float(beta),
                            _sz(a.ndim), _arr_sz(a.shape), _arr_isz(a.strides), _p(a),
                            _sz(b.ndim), _arr_sz(b.shape), _arr_isz(b.strides), _p(b), ctypes.c_float(alpha)))
     return c
@@ -134,7 +170,7 @@ def mat_mul(c, beta, a, b, alpha):
 def attention(q, k, v, o, causal=True):
     nh, seq, dh = q.shape
     nkvh, att, _ = k.shape
-    _chk(lib().orc_attention(DT[q.dtype], _sz(nh), _sz(nkvh), _sz(seq), _sz(att), _sz(dh), _p(q), _arr_isz(q.strides),
+    _chk(lib().orc_attention(_dt(q), _sz(nh), _sz(nkvh), _sz(seq), _sz(att), _sz(dh), _p(q), _arr_isz(q.strides),
                              _p(k), _arr_isz(k.strides), _p(v), _arr_isz(v.strides), _p(o), _arr_isz(o.strides),
                              ctypes.c_int(1 if causal else 0)))
     return o
@@ -143,7 +179,7 @@ def attention(q, k, v, o, causal=True):
 def attention_kv_cached(q, k, v, o, k_cache, v_cache, pos, causal=True):
     nh, seq, dh = q.shape
     nkvh = k.shape[0]
-    _chk(lib().orc_attention_kv_cached(DT[q.dtype], _sz(nh), _sz(nkvh), _sz(seq), _sz(dh), _sz(k_cache.shape[1]),
+    _chk(lib().orc_attention_kv_cached(_dt(q), _sz(nh), _sz(nkvh), _sz(seq), _sz(dh), _sz(k_cache.shape[1]),
                                        _sz(v_cache.shape[1]), _sz(pos), _p(q), _arr_isz(q.strides), _p(k),
                                        _arr_isz(k.strides), _p(v), _arr_isz(v.strides), _p(o), _arr_isz(o.strides),
                                        _p(k_cache), _arr_isz(k_cache.strides), _p(v_cache),
@@ -155,7 +191,7 @@ def random_sample(logits, temperature=0.0, top_p=1.0, top_k=2 ** 64 - 1, seed=0.
     """Returns (idx, val_bits) of the KVPair the reference would write."""
     assert logits.ndim == 1 and logits.strides[0] == logits.itemsize
     out = (ctypes.c_uint32 * 2)()
-    _chk(lib().orc_random_sample(DT[logits.dtype], _sz(logits.shape[0]), _p(logits), ctypes.c_float(temperature),
+    _chk(lib().orc_random_sample(_dt(logits), _sz(logits.shape[0]), _p(logits), ctypes.c_float(temperature),
                                  ctypes.c_float(min(top_p, 1.0)), _sz(top_k), ctypes.c_float(seed), out))
     return int(out[0]), int(out[1])
 
@@ -164,7 +200,7 @@ def all_reduce(bufs):
     """Sum over the list of per-rank arrays, in place in every array (tree order of the reference)."""
     p = len(bufs)
     ptrs = (ctypes.c_void_p * p)(*[b.ctypes.data for b in bufs])
-    _chk(lib().orc_all_reduce(DT[bufs[0].dtype], _sz(p), _sz(bufs[0].size), ptrs))
+    _chk(lib().orc_all_reduce(_dt(bufs[0]), _sz(p), _sz(bufs[0].size), ptrs))
     return bufs
 
 
@@ -176,14 +212,14 @@ def broadcast(bufs, root):
 
 
 def add(c, a, b):
-    _chk(lib().orc_add(DT[c.dtype], _sz(c.ndim), _arr_sz(c.shape), _p(c), _arr_isz(c.strides), _p(a), _arr_isz(a.strides), _p(b),
+    _chk(lib().orc_add(_dt(c), _sz(c.ndim), _arr_sz(c.shape), _p(c), _arr_isz(c.strides), _p(a), _arr_isz(a.strides), _p(b),
                        _arr_isz(b.strides)))
     return c
 
 
 def add_rows(dst, src, idx):
     batch, m, n = dst.shape
-    _chk(lib().orc_add_rows(DT[dst.dtype], DT[idx.dtype], _sz(batch), _sz(m), _sz(n), _sz(src.shape[0]), _p(dst), _isz(dst.strides[0]),
+    _chk(lib().orc_add_rows(_dt(dst), _dt(idx), _sz(batch), _sz(m), _sz(n), _sz(src.shape[0]), _p(dst), _isz(dst.strides[0]),
                             _isz(dst.strides[1]), _isz(dst.strides[2]), _p(src), _isz(src.strides[0]), _isz(src.strides[1]), _p(idx),
                             _isz(idx.strides[0]), _isz(idx.strides[1])))
     return dst
@@ -207,17 +243,17 @@ def decoder_layer(x, pos, shards, cfg):
             out = xs[r]
             mat_mul(out, 1.0, a, w_, 1.0)
         else:
-            out = np.zeros((T, d), x.dtype)
+            out = _zeros((T, d), x)
             mat_mul(out, 0.0, a, w_, 1.0)
         return out
 
     parts = []
     for r, w in enumerate(shards):
-        h = rms_norm(np.empty_like(x), xs[r], w["w_norm1"], cfg["eps"])
-        qkv = mat_mul(np.zeros((T, (nq + 2 * nkv) * dh), x.dtype), 0.0, h, w["w_qkv"], 1.0)
+        h = rms_norm(_empty_like(x), xs[r], w["w_norm1"], cfg["eps"])
+        qkv = mat_mul(_zeros((T, (nq + 2 * nkv) * dh), x), 0.0, h, w["w_qkv"], 1.0)
         heads = qkv.reshape(T, nq + 2 * nkv, dh)
         rope(heads[:, : nq + nkv], pos, cfg["theta"])
-        att_out = np.zeros((T, nq * dh), x.dtype)
+        att_out = _zeros((T, nq * dh), x)
         attention(heads[:, :nq].transpose(1, 0, 2), heads[:, nq:nq + nkv].transpose(1, 0, 2), heads[:, nq + nkv:].transpose(1, 0, 2),
                   att_out.reshape(T, nq, dh).transpose(1, 0, 2), True)
         parts.append(project(r, att_out, w["w_o"]))
@@ -226,8 +262,8 @@ def decoder_layer(x, pos, shards, cfg):
     xs = parts
     parts = []
     for r, w in enumerate(shards):
-        h = rms_norm(np.empty_like(x), xs[r], w["w_norm2"], cfg["eps"])
-        gu = mat_mul(np.zeros((T, 2 * f), x.dtype), 0.0, h, w["w_gu"], 1.0)
+        h = rms_norm(_empty_like(x), xs[r], w["w_norm2"], cfg["eps"])
+        gu = mat_mul(_zeros((T, 2 * f), x), 0.0, h, w["w_gu"], 1.0)
         swiglu(gu[:, :f], gu[:, f:])
         parts.append(project(r, gu[:, :f], w["w_down"]))
     if tp > 1:

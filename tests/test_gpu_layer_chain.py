@@ -1,0 +1,163 @@
+"""One-GPU parity of the decoder-layer chain itself and of the config-3 shapes the chain is made of.
+
+The layer driver (operators-rs_b200/layer.py) strings the operators together in ways no single-operator test
+exercises: the residual folded into the O and down projections with beta = 1, rope and attention on strided views
+of the fused QKV buffer, swiglu on the two halves of one buffer whose first half then feeds the down projection as
+an A operand with row stride 2*ffn.  Here that chain runs at the full width of BASELINE config 3 (d 4096, 32/8
+heads, dh 128, ffn 14336) and is compared with the oracle's chain of the restated common_cpu operators
+(oracle.decoder_layer; attention follows operators/src/attention/operator.rs:136-277).
+
+Also here: the gate|up and down projections and the causal softmax at their full config-2/3 sizes, checked on
+sampled rows (rows of a product and of a softmax are independent, so the oracle only needs the sampled ones).
+
+Tolerance everywhere: max-abs 1e-2 on f16 outputs (BASELINE's budget; one f16 ulp is 2e-3 at |x| in [2,4)).
+"""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import __graft_entry__ as graft
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+CFG3 = dict(d=4096, nh=32, nkvh=8, dh=128, ffn=14336, theta=5e5, eps=1e-5)
+
+
+def _weights(dev, cfg, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    d, nh, nkvh, dh, ffn = cfg["d"], cfg["nh"], cfg["nkvh"], cfg["dh"], cfg["ffn"]
+
+    def proj(r, c):
+        return (torch.randn(r, c, generator=g, device=dev, dtype=torch.float32) * 0.02).half()
+
+    def norm():
+        return (torch.rand(d, generator=g, device=dev, dtype=torch.float32) + 0.5).half()
+
+    return {"w_norm1": norm(), "w_qkv": proj(d, (nh + 2 * nkvh) * dh), "w_o": proj(nh * dh, d), "w_norm2": norm(),
+            "w_gu": proj(d, 2 * ffn), "w_down": proj(ffn, d)}
+
+
+@pytest.mark.parametrize("tokens", [320, 1])
+def test_decoder_layer_full_width_matches_oracle_chain(pkg, orc, dev, tokens):
+    layer_mod = importlib.import_module(graft.PKG_NAME + ".layer")
+    cfg = layer_mod.LayerConfig(**CFG3)
+    w = _weights(dev, CFG3, 11)
+    g = torch.Generator(device=dev).manual_seed(12)
+    x = torch.randn(tokens, CFG3["d"], generator=g, device=dev, dtype=torch.float32).half()
+    x_host = x.cpu().numpy().copy()
+    pos = torch.arange(tokens, dtype=torch.int32, device=dev).view(torch.uint32)
+    layer = layer_mod.DecoderLayer(cfg, w, tokens, dev)
+    out = layer.forward(x, pos)
+    torch.cuda.synchronize()
+    assert layer.mat_mul.status() == 0 and layer.attention.status() == 0
+    ref = orc.decoder_layer(x_host, np.arange(tokens, dtype=np.uint32), [{k: v.cpu().numpy() for k, v in w.items()}], CFG3)
+    # the residual stream has |x| up to ~5: one f16 ulp there is 4e-3, two roundings apart at most
+    assert_close(out.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens")
+    # a second pass over the same buffers (the chain updates the stream in place; scratch is reused)
+    x.copy_(torch.from_numpy(x_host))
+    out2 = layer.forward(x, pos)
+    torch.cuda.synchronize()
+    assert_close(out2.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens, second pass")
+
+
+def _sample_rows(n, count, seed):
+    return sorted(set([0, 127, 128, n - 1] + [int(v) for v in np.random.default_rng(seed).integers(0, n, count)]))
+
+
+def test_gate_up_projection_full_size_sampled_rows(pkg, orc, dev):
+    # [4096, 4096] x [4096, 28672]: the dominant kernel of the layer
+    g = torch.Generator(device=dev).manual_seed(21)
+    a = torch.randn(4096, 4096, generator=g, device=dev).half()
+    w = (torch.randn(4096, 28672, generator=g, device=dev) * 0.02).half()
+    c = torch.empty(4096, 28672, dtype=torch.float16, device=dev)
+    mm = pkg.MatMul(0)
+    mm.launch(pkg.MatMulArgs.of(c, 0.0, a, w, 1.0))
+    torch.cuda.synchronize()
+    assert mm.status() == 0
+    rows = _sample_rows(4096, 12, 1)
+    ref = orc.mat_mul(np.zeros((len(rows), 28672), np.float16), 0.0, a[rows].cpu().numpy(), w.cpu().numpy(), 1.0)
+    assert_close(c[rows].cpu().numpy(), ref, 1e-2, "gate|up projection")
+
+
+def test_down_projection_full_size_sampled_rows(pkg, orc, dev):
+    # [4096, 14336] (row stride 2*ffn: the gate half of the gate|up buffer) x [14336, 4096], beta = 1: the K-split
+    # remainder wave at 512 tiles, with the residual folded in
+    g = torch.Generator(device=dev).manual_seed(22)
+    gu = torch.randn(4096, 2 * 14336, generator=g, device=dev).half()
+    w = (torch.randn(14336, 4096, generator=g, device=dev) * 0.02).half()
+    x = torch.randn(4096, 4096, generator=g, device=dev).half()
+    x0 = x.clone()
+    a = gu[:, :14336]
+    mm = pkg.MatMul(0)
+    mm.launch(pkg.MatMulArgs.of(x, 1.0, a, w, 1.0))
+    mm.launch(pkg.MatMulArgs.of(x, 1.0, a, w, 1.0))  # twice: the arrival counters of the K split must be back at zero
+    torch.cuda.synchronize()
+    assert mm.status() == 0
+    rows = _sample_rows(4096, 12, 2)
+    an, wn = a[rows].cpu().numpy(), w.cpu().numpy()
+    ref = orc.mat_mul(x0[rows].cpu().numpy().copy(), 1.0, an, wn, 1.0)
+    ref = orc.mat_mul(ref, 1.0, an, wn, 1.0)
+    # |x| grows to ~2.4 * 2 + 1: ulp 4e-3..8e-3 in [4,16) — the budget here is two f16 ulps at that magnitude
+    assert_close(x[rows].cpu().numpy(), ref, 2e-2, "down projection (beta = 1, twice)")
+
+
+def test_o_projection_full_size_sampled_rows(pkg, orc, dev):
+    g = torch.Generator(device=dev).manual_seed(23)
+    a = torch.randn(4096, 4096, generator=g, device=dev).half()
+    w = (torch.randn(4096, 4096, generator=g, device=dev) * 0.02).half()
+    x = torch.randn(4096, 4096, generator=g, device=dev).half()
+    x0 = x.clone()
+    mm = pkg.MatMul(0)
+    mm.launch(pkg.MatMulArgs.of(x, 1.0, a, w, 1.0))
+    torch.cuda.synchronize()
+    assert mm.status() == 0
+    rows = _sample_rows(4096, 16, 3)
+    ref = orc.mat_mul(x0[rows].cpu().numpy().copy(), 1.0, a[rows].cpu().numpy(), w.cpu().numpy(), 1.0)
+    assert_close(x[rows].cpu().numpy(), ref, 1e-2, "O projection (beta = 1)")
+
+
+@pytest.mark.parametrize("seq", [2048, 4096])
+def test_fused_softmax_config_size_sampled_heads(pkg, orc, dev, seq):
+    # config 2: [32, 2048, 2048]; config 3's score matrix is [32, 4096, 4096] (checked on 8 heads to bound memory).
+    # Heads are independent: the oracle runs on three of them.
+    nh = 32 if seq == 2048 else 8
+    g = torch.Generator(device=dev).manual_seed(31)
+    att = (torch.randn(nh, seq, seq, generator=g, device=dev) * 2.0).half()
+    heads = [0, nh // 2, nh - 1]
+    ref = att[heads].cpu().numpy().copy()
+    pkg.FusedSoftmax(0).launch(pkg.FusedSoftmaxArgs.of(att))
+    torch.cuda.synchronize()
+    orc.fused_softmax(ref, True)
+    got = att[heads].cpu().numpy()
+    assert_close(got, ref, 1e-2, f"fused_softmax [{nh},{seq},{seq}]")
+    # masked entries are exact zeros, every row sums to one within f16 rounding of its entries
+    k = np.arange(seq)
+    assert (got[:, k[:, None] < k[None, :]] == 0).all()
+    np.testing.assert_allclose(got.astype(np.float32).sum(-1), 1.0, atol=2e-2)
+
+
+def test_attention_config3_size_sampled_heads(pkg, orc, dev):
+    # 4096 tokens, 32/8 heads, dh 128 on the GPU; the oracle (crate's chain on the CPU) runs one GQA group's worth:
+    # kv head 5 with its four q heads, which is independent of the others.
+    nh, nkvh, seq, dh = 32, 8, 4096, 128
+    g = torch.Generator(device=dev).manual_seed(41)
+    qkv = torch.randn(seq, nh + 2 * nkvh, dh, generator=g, device=dev).half()  # token-major, as the layer holds it
+    q = qkv[:, :nh].permute(1, 0, 2)
+    k = qkv[:, nh:nh + nkvh].permute(1, 0, 2)
+    v = qkv[:, nh + nkvh:].permute(1, 0, 2)
+    o = torch.zeros(seq, nh, dh, dtype=torch.float16, device=dev)
+    op = pkg.Attention(0)
+    args = pkg.AttentionArgs.of(q, k, v, o.permute(1, 0, 2), pkg.MASK_CAUSAL)
+    ws = torch.empty(16, dtype=torch.uint8, device=dev)  # the fused kernel needs no workspace (the chain would want 1 GiB)
+    op.launch(args, ws)
+    torch.cuda.synchronize()
+    assert op.status() == 0
+    kvh = 5
+    qs = q[4 * kvh: 4 * kvh + 4].contiguous().cpu().numpy()
+    on = np.zeros_like(qs)
+    orc.attention(qs.copy(), k[kvh:kvh + 1].contiguous().cpu().numpy(), v[kvh:kvh + 1].contiguous().cpu().numpy(), on, True)
+    got = o.permute(1, 0, 2)[4 * kvh: 4 * kvh + 4].cpu().numpy()
+    assert_close(got, on, 1e-2, "attention, 4096 tokens (one GQA group)")
