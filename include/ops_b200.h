@@ -218,7 +218,9 @@ int ops_mat_mul_status(const ops_mat_mul *op);
  * As in the crate, q may be overwritten when its (nh, seq) dims are mergeable.
  * `algo`: 0 = the crate's own chain (rearrange, mat_mul, fused_softmax, mat_mul, rearrange) with
  * the score matrix in workspace, every intermediate rounded to f16 where the crate rounds it;
- * 1 = one fused flash-attention kernel (no score matrix, no workspace, q left untouched).
+ * 1 = one fused flash-attention kernel (no score matrix, no workspace, q left untouched); for dh = 128 a CTA owns two
+ *     128-row q tiles whose softmax and tensor-core work interleave; 2 = the same with one q tile per CTA (the kernel
+ *     dh = 64 always takes), kept selectable for comparison.
  * ------------------------------------------------------------------------------------------- */
 typedef struct ops_attention ops_attention;
 typedef struct {
@@ -228,7 +230,7 @@ typedef struct {
   ops_layout o_layout; void *o_base;
   uint8_t mask;
 } ops_attention_args;
-enum { OPS_ATTENTION_CHAIN = 0, OPS_ATTENTION_FUSED = 1 };
+enum { OPS_ATTENTION_CHAIN = 0, OPS_ATTENTION_FUSED = 1, OPS_ATTENTION_FUSED_ONE_TILE = 2 };
 int ops_attention_create(int device, ops_attention **out);
 int ops_attention_set_algo(ops_attention *op, int algo); /* default OPS_ATTENTION_FUSED (falls back to the chain when a layout rules it out) */
 int ops_attention_status(const ops_attention *op);      /* 0, or the code of a bounded wait that ran out; synchronises; no counterpart in the crate */

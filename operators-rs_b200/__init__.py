@@ -34,7 +34,7 @@ DYN_STRIDE = (1 << 63) - 1        # isize::MAX
 DYN_F32 = float("inf")
 MASK_NONE, MASK_CAUSAL = 0, 1
 REDUCE_SUM, REDUCE_PROD, REDUCE_MIN, REDUCE_MAX, REDUCE_MEAN = range(5)
-ATTENTION_CHAIN, ATTENTION_FUSED = 0, 1
+ATTENTION_CHAIN, ATTENTION_FUSED, ATTENTION_FUSED_ONE_TILE = 0, 1, 2
 ALL_REDUCE_AUTO, ALL_REDUCE_NCCL, ALL_REDUCE_P2P_ONE_SHOT, ALL_REDUCE_P2P_TWO_SHOT = range(4)
 COMM_ID_BYTES, COMM_P2P_HANDLE_BYTES = 128, 128
 

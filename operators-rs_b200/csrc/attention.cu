@@ -21,7 +21,7 @@ struct ops_attention {
   ops_mat_mul *mat_mul;
   int algo;
   int *status_dev;      // written by the fused kernel when a bounded wait runs out
-  bool attr_set[2];
+  bool attr_set[3];
   float *decode_scratch;          // split-KV partials of the decode kernel (owned by the handle; one stream at a time)
   unsigned int *decode_tickets;   // arrival counters, left at zero by every launch
 };
@@ -132,13 +132,14 @@ int attention_enqueue(const ops_attention *op, const ops_attention_args *a, void
   if (m.nkvh == 0 || m.nh % m.nkvh != 0) return fail(OPS_SHAPE_MISMATCH, "attention: nh must be a multiple of nkvh");
   if (a->mask == OPS_MASK_CAUSAL && m.att < m.seq) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: causal mask needs att >= seq");
   if (m.nh == 0 || m.seq == 0 || m.dh == 0 || m.att == 0) return OPS_OK;
-  if (op->algo == OPS_ATTENTION_FUSED && a->q_base && a->k_base && a->v_base && a->o_base && op->decode_scratch &&
+  const bool fused = op->algo == OPS_ATTENTION_FUSED || op->algo == OPS_ATTENTION_FUSED_ONE_TILE;
+  if (fused && a->q_base && a->k_base && a->v_base && a->o_base && op->decode_scratch &&
       attention_decode_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh))
     return attention_decode_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->decode_scratch, op->decode_tickets, s);
-  if (op->algo == OPS_ATTENTION_FUSED && a->q_base && a->k_base && a->v_base && a->o_base &&
-      attention_fused_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh)) {
+  if (fused && a->q_base && a->k_base && a->v_base && a->o_base && attention_fused_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh)) {
     ops_attention *mop = const_cast<ops_attention *>(op);
-    return attention_fused_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->status_dev, mop->attr_set, s);
+    return attention_fused_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->status_dev, mop->attr_set, s,
+                                   op->algo == OPS_ATTENTION_FUSED_ONE_TILE);
   }
   return attention_chain(op, a, m, ws, ws_len, s);
 }
@@ -151,7 +152,7 @@ OPS_API int ops_attention_create(int device, ops_attention **out) {
   h->mat_mul = nullptr;
   h->algo = OPS_ATTENTION_FUSED;
   h->status_dev = nullptr;
-  h->attr_set[0] = h->attr_set[1] = false;
+  h->attr_set[0] = h->attr_set[1] = h->attr_set[2] = false;
   h->decode_scratch = nullptr;
   h->decode_tickets = nullptr;
   int rc = init_base(&h->base, device);
@@ -187,7 +188,7 @@ OPS_API void ops_attention_destroy(ops_attention *op) {
 }
 
 OPS_API int ops_attention_set_algo(ops_attention *op, int algo) {
-  if (algo != OPS_ATTENTION_CHAIN && algo != OPS_ATTENTION_FUSED) return fail(OPS_ARGS_NOT_SUPPORT, "attention: unknown algorithm %d", algo);
+  if (algo != OPS_ATTENTION_CHAIN && algo != OPS_ATTENTION_FUSED && algo != OPS_ATTENTION_FUSED_ONE_TILE) return fail(OPS_ARGS_NOT_SUPPORT, "attention: unknown algorithm %d", algo);
   op->algo = algo;
   return OPS_OK;
 }

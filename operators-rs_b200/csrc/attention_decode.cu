@@ -95,34 +95,46 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   const int k_begin = split * a.keys_per_split, k_end = min(a.att, k_begin + a.keys_per_split);
   const unsigned short *kbase = a.k + (long long)kvh * a.k_sh + li * 8;
   const unsigned short *vbase = a.v + (long long)kvh * a.v_sh + li * 8;
-#pragma unroll 4
-  for (int kb = k_begin + warp * KPW; kb < k_end; kb += GROUPS) {  // warp-uniform trip count: the shuffles need every lane
-    const int key = kb + sub;
-    const bool valid = key < k_end;
-    const int kload = valid ? key : k_end - 1;
-    Vec8<unsigned short> kk, vv;
-    kk.u = ld_stream_16(kbase + (long long)kload * a.k_ss);
-    vv.u = ld_stream_16(vbase + (long long)kload * a.v_ss);
-    float kf[8], vf[8];
+  // Keys are taken eight steps at a time: the sixteen 128-bit loads of a batch (K and V of eight key rows per lane) are
+  // all issued before the first is used, so a CTA pays the DRAM latency once per 128 keys, not once per 16.
+  constexpr int UN = 8;
+  for (int kb0 = k_begin + warp * KPW; kb0 < k_end; kb0 += GROUPS * UN) {  // warp-uniform trip count: the shuffles need every lane
+    uint4 kq[UN], vq[UN];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      kf[e] = dec_to_f32(kk.h[e], bf);
-      vf[e] = dec_to_f32(vv.h[e], bf);
+    for (int u = 0; u < UN; ++u) {
+      const int key = kb0 + u * GROUPS + sub;
+      const int kload = key < k_end ? key : k_end - 1;
+      kq[u] = __ldcs(reinterpret_cast<const uint4 *>(kbase + (long long)kload * a.k_ss));
+      vq[u] = __ldcs(reinterpret_cast<const uint4 *>(vbase + (long long)kload * a.v_ss));
     }
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      float s = 0.f;
+    for (int u = 0; u < UN; ++u) {
+      const int key = kb0 + u * GROUPS + sub;
+      const bool valid = key < k_end;
+      Vec8<unsigned short> kk, vv;
+      kk.u = kq[u];
+      vv.u = vq[u];
+      float kf[8], vf[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s = fmaf(qr[r][e], kf[e], s);
+      for (int e = 0; e < 8; ++e) {
+        kf[e] = dec_to_f32(kk.h[e], bf);
+        vf[e] = dec_to_f32(vv.h[e], bf);
+      }
 #pragma unroll
-      for (int d = LPK / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // stays inside the LPK-lane group
-      if (valid && key <= lim[r]) {
-        const float m_new = fmaxf(m[r], s);
-        const float alpha = ex2f(m[r] - m_new), p = ex2f(s - m_new);
-        l[r] = fmaf(l[r], alpha, p);
+      for (int r = 0; r < ROWS; ++r) {
+        float s = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[r][e] = fmaf(o[r][e], alpha, p * vf[e]);
-        m[r] = m_new;
+        for (int e = 0; e < 8; ++e) s = fmaf(qr[r][e], kf[e], s);
+#pragma unroll
+        for (int d = LPK / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // stays inside the LPK-lane group
+        if (valid && key <= lim[r]) {
+          const float m_new = fmaxf(m[r], s);
+          const float alpha = ex2f(m[r] - m_new), p = ex2f(s - m_new);
+          l[r] = fmaf(l[r], alpha, p);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[r][e] = fmaf(o[r][e], alpha, p * vf[e]);
+          m[r] = m_new;
+        }
       }
     }
   }

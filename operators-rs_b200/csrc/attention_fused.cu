@@ -384,6 +384,397 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The kernel for dh = 128: two 128-row q tiles per CTA played against each other.
+//
+// The fast path behind attention::Args (operators/src/attention/args.rs:10-24) for dh = 128: the same function as the
+// crate's composition (operators/src/attention/operator.rs:199-275) computed with online softmax, so HBM sees q, k, v and o
+// once.  What bounds a one-tile kernel on this machine is not the tensor pipe but the chain of hand-offs around the softmax
+// of each 128-key block; here one CTA owns TWO q tiles (256 rows of one head), each with its own softmax warpgroup, and the
+// tensor pipe always has the other tile's products to run while one tile's exponentials are in flight:
+//
+//   warp 0        TMA producer: both q tiles once, then K and V blocks of 128 keys through two-stage rings;
+//   warp 1        tcgen05.mma issuer, in the order  PV(t0,j)  QK(t0,j+1)  PV(t1,j)  QK(t1,j+1)  ...  so that the two tiles
+//                 fall half a period apart;
+//   warps 4-7     softmax of tile 0, warps 8-11 of tile 1: ONE thread per q row.  It reads its whole S row from tensor memory
+//                 (128 registers), takes the maximum, publishes the rescaling factor, writes the probabilities back INTO
+//                 tensor memory as packed 16-bit pairs over the columns S occupied — the second product takes them from there
+//                 (A operand in tensor memory), no shared-memory round trip;
+//   warps 12-15   correction: O lives in tensor memory and accumulates across blocks; when a row maximum moved, these warps
+//                 rescale that tile's O (tcgen05.ld, multiply, tcgen05.st) while the softmax warps are busy with the
+//                 exponentials, and at the end they divide by the row sums and store o.
+// Registers are redistributed after start-up (setmaxnreg): the softmax threads get the 184 they need for a whole row.
+// Every mbarrier wait is bounded; a wait that runs out records its code and every role unwinds to the common teardown.
+constexpr int FP_BM = 128;        // rows per q tile
+constexpr int FP_BN = 128;        // keys per block
+constexpr int FP_DH = 128;
+constexpr int FP_THREADS = 512;   // 4 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1, correction
+constexpr int FP_TILE_BYTES = FP_BM * FP_DH * 2;  // one q tile, one K block or one V block: 32 KB
+
+struct PairAttnArgs {
+  unsigned short *o;     // f16 or bf16 bit patterns
+  long long o_sh, o_ss;  // element strides of o: head, row (dh contiguous)
+  int nh, group, seq, att;
+  int causal;
+  int pairs;             // q-tile pairs per head
+  float scale_log2;      // alpha * log2(e)
+  int vec_store;
+  int bf16;
+  int *status;
+};
+
+struct FpSmem {
+  static constexpr int OFF_Q = 0;                          // 2 tiles
+  static constexpr int OFF_K = OFF_Q + 2 * FP_TILE_BYTES;  // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * FP_TILE_BYTES;  // 2 stages
+  static constexpr int OFF_BAR = OFF_V + 2 * FP_TILE_BYTES;
+  static constexpr int NUM_BARS = 22;
+  static constexpr int OFF_TMEM_SLOT = OFF_BAR + NUM_BARS * 8;
+  static constexpr int OFF_ALPHA = OFF_TMEM_SLOT + 16;            // [2 tiles][128 rows] f32 rescaling factors of the current block
+  static constexpr int OFF_L = OFF_ALPHA + 2 * FP_BM * 4;         // [2 tiles][128 rows] f32 row sums
+  static constexpr int BYTES = OFF_L + 2 * FP_BM * 4 + 1024 /* alignment slack */;
+};
+
+__device__ __forceinline__ float fp_max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float fp_ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t fp_pack(float lo, float hi, int bf) {
+  if (bf) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+__global__ void __launch_bounds__(FP_THREADS, 1)
+    attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ PairAttnArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar0 = base + FpSmem::OFF_BAR;
+  auto q_full = [&](int t) { return bar0 + 8u * (0 + t); };
+  auto k_full = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (6 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (8 + s); };
+  auto s_full = [&](int t) { return bar0 + 8u * (10 + t); };      // S of tile t complete (tensor pipe -> softmax)
+  auto p_full = [&](int t) { return bar0 + 8u * (12 + t); };      // P of tile t written to tensor memory (softmax -> issuer)
+  auto alpha_full = [&](int t) { return bar0 + 8u * (14 + t); };  // rescaling factors of tile t published (softmax -> correction)
+  auto o_scaled = [&](int t) { return bar0 + 8u * (16 + t); };    // O of tile t rescaled (correction -> issuer)
+  auto o_final = [&](int t) { return bar0 + 8u * (18 + t); };     // last PV of tile t complete (tensor pipe -> correction)
+  auto l_full = [&](int t) { return bar0 + 8u * (20 + t); };      // row sums of tile t published (softmax -> correction)
+  const uint32_t tmem_slot = base + FpSmem::OFF_TMEM_SLOT;
+  uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(base_ptr + FpSmem::OFF_TMEM_SLOT);
+  float *alpha_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_ALPHA);
+  float *l_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_L);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest pairs first, the heads of one pair next to each other (a GQA group shares its K/V blocks through L2)
+  const int pair = g.pairs - 1 - (int)(blockIdx.x / g.nh);
+  const int head = (int)(blockIdx.x % g.nh);
+  const int kv_head = head / g.group;
+  const int q0 = pair * 2 * FP_BM;
+  const int off = g.att - g.seq;  // causal row r sees keys <= off + r
+  int nblk[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = q0 + t * FP_BM;
+    int k_end = g.att;
+    if (g.causal) k_end = min(g.att, off + r0 + FP_BM);
+    nblk[t] = r0 < g.seq ? (k_end + FP_BN - 1) / FP_BN : 0;
+  }
+  const int nmax = max(nblk[0], nblk[1]);
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(q_full(t), 1);
+      mbar_init(k_full(t), 1);
+      mbar_init(k_empty(t), 1);
+      mbar_init(v_full(t), 1);
+      mbar_init(v_empty(t), 1);
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), 4);
+      mbar_init(alpha_full(t), 4);
+      mbar_init(o_scaled(t), 4);
+      mbar_init(o_final(t), 1);
+      mbar_init(l_full(t), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  // tensor memory columns: S0 | S1 | O0 | O1, 128 each; P of a tile overwrites the first 64 columns of its S
+  auto s_col = [&](int t) { return (uint32_t)(t * 128); };
+  auto o_col = [&](int t) { return (uint32_t)(256 + t * 128); };
+
+  if (warp < 4) {
+    setmaxnreg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      for (int t = 0; t < 2; ++t) {
+        if (nblk[t] == 0) continue;
+        mbar_arrive_expect_tx(q_full(t), FP_TILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(base + FpSmem::OFF_Q + t * FP_TILE_BYTES + h * (FP_BM * 128), &tmap_q, q_full(t), h * 64, q0 + t * FP_BM, head);
+      }
+      bool ok = true;
+      for (int j = 0; j < nmax && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!(ok = mbar_wait(k_empty(s), ph ^ 1u, g.status, 111))) break;
+        mbar_arrive_expect_tx(k_full(s), FP_TILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(base + FpSmem::OFF_K + s * FP_TILE_BYTES + h * (FP_BN * 128), &tmap_k, k_full(s), h * 64, j * FP_BN, kv_head);
+        if (!(ok = mbar_wait(v_empty(s), ph ^ 1u, g.status, 112))) break;
+        mbar_arrive_expect_tx(v_full(s), FP_TILE_BYTES);
+#pragma unroll
+        for (int kg = 0; kg < 2; ++kg)
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+            tma_load_3d(base + FpSmem::OFF_V + s * FP_TILE_BYTES + (kg * 2 + c) * 8192, &tmap_v, v_full(s), c * 64, j * FP_BN + kg * 64, kv_head);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_qk = make_idesc_f16(FP_BM, FP_BN, 0, 0, g.bf16);
+      const uint32_t idesc_pv = make_idesc_f16(FP_BM, FP_DH, 0, 1, g.bf16);
+      bool ok = true;
+      // S(t) = Q(t) K_b^T
+      auto issue_qk = [&](int t, int b) -> bool {
+        const int s = b & 1;
+        if (!mbar_wait(k_full(s), (uint32_t)((b >> 1) & 1), g.status, 121)) return false;
+        tc_fence_after();
+        const uint32_t qa = base + FpSmem::OFF_Q + t * FP_TILE_BYTES, ka = base + FpSmem::OFF_K + s * FP_TILE_BYTES;
+        const uint32_t d = tmem_base + s_col(t);
+#pragma unroll
+        for (int ks = 0; ks < FP_DH / 16; ++ks) {
+          const uint64_t da = make_smem_desc_sw128(qa + (ks >> 2) * (FP_BM * 128) + (ks & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(ka + (ks >> 2) * (FP_BN * 128) + (ks & 3) * 32, 16, 1024);
+          umma_f16_ss(d, da, db, idesc_qk, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full(t));
+        const bool last_user = t == 1 || b >= nblk[1];
+        if (last_user) umma_commit(k_empty(s));
+        return true;
+      };
+      // O(t) (+)= P(t) V_b, P from tensor memory
+      auto issue_pv = [&](int t, int b) -> bool {
+        const int s = b & 1;
+        const uint32_t ph = (uint32_t)(b & 1);
+        if (!mbar_wait(v_full(s), (uint32_t)((b >> 1) & 1), g.status, 122)) return false;
+        if (!mbar_wait(p_full(t), ph, g.status, 123)) return false;
+        if (!mbar_wait(o_scaled(t), ph, g.status, 124)) return false;
+        tc_fence_after();
+        const uint32_t va = base + FpSmem::OFF_V + s * FP_TILE_BYTES;
+        const uint32_t d = tmem_base + o_col(t);
+        const uint32_t p = tmem_base + s_col(t);
+#pragma unroll
+        for (int ks = 0; ks < FP_BN / 16; ++ks) {
+          const uint64_t db = make_smem_desc_sw128(va + (ks >> 2) * (2 * 8192) + (ks & 3) * 2048, 8192, 1024);
+          umma_f16_ts(d, p + (uint32_t)(ks * 8), db, idesc_pv, (b != 0 || ks != 0) ? 1u : 0u);
+        }
+        if (b == nblk[t] - 1) umma_commit(o_final(t));
+        const bool last_user = t == 1 || b >= nblk[1];
+        if (last_user) umma_commit(v_empty(s));
+        return true;
+      };
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (nblk[t] == 0) continue;
+        if (!(ok = mbar_wait(q_full(t), 0, g.status, 120))) break;
+        ok = issue_qk(t, 0);
+      }
+      for (int j = 0; j < nmax && ok; ++j) {
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= nblk[t]) continue;
+          ok = issue_pv(t, j);
+          if (ok && j + 1 < nblk[t]) ok = issue_qk(t, j + 1);
+        }
+      }
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ softmax: one thread per q row
+    setmaxnreg_inc<184>();
+    const int t = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int q_row = q0 + t * FP_BM + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int limit = g.causal ? min(g.att - 1, off + q_row) : g.att - 1;  // last key this row may see
+    const int bf = g.bf16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk[t] && ok; ++j) {
+      const int kv0 = j * FP_BN;
+      if (!(ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 131))) break;
+      tc_fence_after();
+      const uint32_t ta = tmem_base + lane_addr + s_col(t);
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_32x32(ta, s0);
+      tmem_ld_32x32(ta + 32u, s1);
+      tmem_ld_32x32(ta + 64u, s2);
+      tmem_ld_32x32(ta + 96u, s3);
+      tmem_wait_ld();
+      const bool need_mask = kv0 + FP_BN - 1 > limit;
+      auto chunk_max = [&](const uint32_t (&v)[32], int k0, float mx) -> float {
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (k0 + e <= limit) mx = fmaxf(mx, __uint_as_float(v[e]));
+          return mx;
+        }
+        float m0 = mx, m1 = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          m0 = fp_max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+          m1 = fp_max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+        }
+        return fmaxf(m0, m1);
+      };
+      float mx = chunk_max(s0, kv0, -INFINITY);
+      mx = chunk_max(s1, kv0 + 32, mx);
+      mx = chunk_max(s2, kv0 + 64, mx);
+      mx = chunk_max(s3, kv0 + 96, mx);
+      const float m_raw = fmaxf(m, mx * g.scale_log2);
+      const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // a row with nothing visible yet: keep the arithmetic finite
+      const float alpha = fp_ex2(m - m_new);                 // 0 on the first block (m = -inf)
+      alpha_s[t * FP_BM + row_in_tile] = alpha;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(alpha_full(t));
+      // probabilities -> tensor memory, packed pairs over the first 64 columns of this tile's S; row sum
+      float rowsum = 0.f;
+      auto emit = [&](const uint32_t (&v)[32], int c) {  // c = first key column (0..127) of these 32 values
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = fp_ex2(fmaf(__uint_as_float(v[e]), g.scale_log2, -m_new));
+          float p1 = fp_ex2(fmaf(__uint_as_float(v[e + 1]), g.scale_log2, -m_new));
+          if (need_mask) {
+            if (kv0 + c + e > limit) p0 = 0.f;
+            if (kv0 + c + e + 1 > limit) p1 = 0.f;
+          }
+          rowsum += p0 + p1;
+          packed[e >> 1] = fp_pack(p0, p1, bf);
+        }
+        tmem_st_32x16(ta + (uint32_t)(c >> 1), packed);
+      };
+      emit(s0, 0);
+      emit(s1, 32);
+      emit(s2, 64);
+      emit(s3, 96);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(t));
+      l = fmaf(l, alpha, rowsum);
+      m = m_new;
+    }
+    l_s[t * FP_BM + row_in_tile] = l;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(l_full(t));
+  } else {
+    // ------------------------------------------------------------------ correction and output (warps 12..15)
+    setmaxnreg_dec<80>();
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+    for (int j = 0; j < nmax && ok; ++j) {
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j >= nblk[t]) continue;
+        // s_full(t) of block j also tells that PV(t, j-1) has completed (the tensor pipe retires in order): O is stable
+        if (!(ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 140))) break;
+        if (!(ok = mbar_wait(alpha_full(t), (uint32_t)(j & 1), g.status, 141))) break;
+        if (j > 0) {
+          const float a = alpha_s[t * FP_BM + row_in_tile];
+          if (__any_sync(0xffffffffu, a != 1.f)) {  // some row maximum of these 32 rows moved: rescale their O
+            tc_fence_after();
+            const uint32_t to = tmem_base + lane_addr + o_col(t);
+#pragma unroll 1
+            for (int c = 0; c < FP_DH; c += 32) {
+              uint32_t v[32];
+              tmem_ld_32x32(to + (uint32_t)c, v);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * a);
+              tmem_st_32x32(to + (uint32_t)c, v);
+            }
+            tmem_wait_st();
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_scaled(t));
+      }
+    }
+    for (int t = 0; t < 2 && ok; ++t) {
+      if (nblk[t] == 0) continue;
+      if (!(ok = mbar_wait(o_final(t), 0, g.status, 142))) break;
+      if (!(ok = mbar_wait(l_full(t), 0, g.status, 143))) break;
+      tc_fence_after();
+      const int q_row = q0 + t * FP_BM + row_in_tile;
+      const float inv = __frcp_rn(l_s[t * FP_BM + row_in_tile]);
+      const uint32_t to = tmem_base + lane_addr + o_col(t);
+      unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss;
+#pragma unroll 1
+      for (int c = 0; c < FP_DH; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(to + (uint32_t)c, v);
+        tmem_wait_ld();
+        if (q_row < g.seq) {
+          if (g.vec_store) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 out;
+              out.x = fp_pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv, g.bf16);
+              out.y = fp_pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, g.bf16);
+              out.z = fp_pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, g.bf16);
+              out.w = fp_pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, g.bf16);
+              st_global_16(orow + c + q4 * 8, out);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const uint32_t pr = fp_pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv, g.bf16);
+              orow[c + e] = (unsigned short)(pr & 0xffffu);
+              orow[c + e + 1] = (unsigned short)(pr >> 16);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*reinterpret_cast<volatile int *>(g.status) != 0) __nanosleep(1000000);  // let stray copies land before the CTA goes away
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (shared with mat_mul.cu's approach)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -469,8 +860,46 @@ static int launch_fused(const OpBase &base, const ops_attention_args *a, usz nh,
   return check_launch("attention(fused)");
 }
 
+static int launch_pair(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, int *status, bool *attr_set,
+                       cudaStream_t s) {
+  CUtensorMap tq, tk, tv;
+  const isz *sq = a->q_layout.strides, *sk = a->k_layout.strides, *sv = a->v_layout.strides, *so = a->o_layout.strides;
+  const bool bf = a->q_layout.dt == OPS_DT_BF16;
+  if (!encode_hrd(&tq, bf, a->q_base, FP_DH, seq, nh, sq[1], sq[0], FP_BM) || !encode_hrd(&tk, bf, a->k_base, FP_DH, att, nkvh, sk[1], sk[0], FP_BN) ||
+      !encode_hrd(&tv, bf, a->v_base, FP_DH, att, nkvh, sv[1], sv[0], 64))
+    return fail(OPS_EXECUTION_FAILED, "attention: cuTensorMapEncodeTiled failed");
+  PairAttnArgs g;
+  g.o = (unsigned short *)a->o_base;
+  g.o_sh = so[0] / 2;
+  g.o_ss = so[1] / 2;
+  g.nh = (int)nh;
+  g.group = (int)(nh / nkvh);
+  g.seq = (int)seq;
+  g.att = (int)att;
+  g.causal = a->mask == OPS_MASK_CAUSAL;
+  g.pairs = (int)((seq + 2 * FP_BM - 1) / (2 * FP_BM));
+  // the CPU path rounds alpha = 1/sqrt(dh) to the element type before the product (mat_mul/common_cpu/mod.rs:101)
+  const float inv_sqrt = 1.f / sqrtf((float)FP_DH);
+  const float alpha = bf ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
+  g.scale_log2 = alpha * 1.4426950408889634f;
+  g.vec_store = aligned(a->o_base, 16) && so[0] % 16 == 0 && so[1] % 16 == 0;
+  g.bf16 = bf ? 1 : 0;
+  g.status = status;
+  cudaSetDevice(base.device);
+  if (!*attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FpSmem::BYTES);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention: cannot reserve %d bytes of shared memory: %s", FpSmem::BYTES, cudaGetErrorString(e));
+    *attr_set = true;
+  }
+  const unsigned grid = (unsigned)(nh * (usz)g.pairs);
+  attention_pair_kernel<<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
+  return check_launch("attention(fused, tile pair)");
+}
+
 int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
-                            bool *attr_set, cudaStream_t s) {
+                            bool *attr_set, cudaStream_t s, bool single_tile) {
+  // dh = 128 with more than one q tile: the two-tile kernel; everything else (and on request) one tile per CTA
+  if (dh == 128 && seq > (usz)FP_BM && !single_tile) return launch_pair(base, a, nh, nkvh, seq, att, status, &attr_set[2], s);
   if (dh == 128) return launch_fused<128>(base, a, nh, nkvh, seq, att, status, &attr_set[0], s);
   return launch_fused<64>(base, a, nh, nkvh, seq, att, status, &attr_set[1], s);
 }

@@ -19,7 +19,7 @@ constexpr unsigned long long P2P_WAIT_LIMIT_NS = 1000000000ull;  // 1 s
 // Staging buffer of one rank: [flags | in(parity 0) | in(parity 1) | out(parity 0) | out(parity 1) | direct]
 // "direct" is the zero-copy input region: a caller that lets the producing kernel write its partial there (same offset on
 // every rank) spares the all_reduce its copy-in.
-struct P2PFlags {
+struct alignas(256) P2PFlags {  // the data regions start right behind it: keep them 256-byte aligned
   unsigned int ready[MAX_RANKS][P2P_MAX_CTAS];   // ready[q][b]: epoch up to which rank q's CTA b has staged its input
   unsigned int reduced[MAX_RANKS][P2P_MAX_CTAS]; // reduced[q][b]: epoch up to which rank q's CTA b has published its reduced slice
   // GEMM + all_reduce kernel: tile_ready[q][f] = epoch at which rank q stored its partial of (tile, quarter) f in its "in"
@@ -33,6 +33,8 @@ struct P2PFlags {
   unsigned int epoch;
   unsigned int done;
 };
+
+static_assert(sizeof(P2PFlags) % 256 == 0, "the staging regions behind the flags must stay aligned");
 
 constexpr int P2P_REGIONS = 5;  // in x2, out x2, direct
 

@@ -70,6 +70,9 @@ struct GemmKernelArgs {
   int kb_per_slice;
   float *split_ws;         // [grid][128][BN] f32
   unsigned int *split_tickets;  // [split_r][4] arrivals per 32-row quarter, self-resetting
+  // Or (short K): the remainder tiles are cut along N into pieces `tail_w` columns wide (128 or 64), `tail_count` of them
+  // in all, dealt out round-robin after the whole tiles: the last wave then costs a fraction of a tile time per CTA.
+  int tail_w, tail_count;
 };
 
 // GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
@@ -114,13 +117,30 @@ struct GemmWork {
   long long t;
   int kb0, kb1;
   int slice;  // -1: whole tile
+  int sub;    // column piece of a remainder tile cut along N (0 when the tile is whole)
+  int bn;     // columns of this unit
 };
 
 // Work unit number `it` of this CTA: whole tiles strided by the grid, then at most one K-slice of a remainder tile.
+template <int BN>
 __device__ __forceinline__ bool gemm_work(const GemmKernelArgs &g, int it, int num_kb, GemmWork &w) {
   const long long t = blockIdx.x + (long long)it * gridDim.x;
+  w.sub = 0;
+  w.bn = BN;
   if (t < g.normal_tiles) {
     w.t = t;
+    w.kb0 = 0;
+    w.kb1 = num_kb;
+    w.slice = -1;
+    return true;
+  }
+  if (g.tail_w > 0) {
+    const long long u = (long long)blockIdx.x + (long long)(it - g.normal_iters) * gridDim.x;
+    if (it < g.normal_iters || u >= g.tail_count) return false;
+    const int per = BN / g.tail_w;
+    w.t = g.normal_tiles + u / per;
+    w.sub = (int)(u % per);
+    w.bn = g.tail_w;
     w.kb0 = 0;
     w.kb1 = num_kb;
     w.slice = -1;
@@ -200,17 +220,18 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       GemmWork w;
-      for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
+      for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
         const long long t = w.t;
         const int b = (int)(t / tiles_per_batch);
         const long long r = t - (long long)b * tiles_per_batch;
         int tn, tm;
         tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
-        const int m0 = tm * GEMM_BM, n0 = tn * BN;
+        const int m0 = tm * GEMM_BM, n0 = tn * BN + w.sub * w.bn;
         const int ba = g.a_batched ? b : 0, bb = g.b_batched ? b : 0;
+        const int b_chunks = w.bn / 64;  // B travels in boxes of 64 rows (K-major) / 64 columns (MN-major)
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, g.status, 1))) break;
-          mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+          mbar_arrive_expect_tx(full_bar(stage), GEMM_A_BYTES + b_chunks * GEMM_CHUNK_BYTES);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES, sb = sa + GEMM_A_BYTES;
           const int k0 = kb * GEMM_BK;
           if (g.a_mn_major) {
@@ -220,10 +241,9 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
             tma_load_3d(sa, &tmap_a, full_bar(stage), k0, m0, ba);
           }
           if (g.b_mn_major) {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
-          } else {
-            tma_load_3d(sb, &tmap_b, full_bar(stage), k0, n0, bb);
+            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
+          } else {  // 64 rows of 128 swizzled bytes per box: stacked boxes give the layout of one tall box
+            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), k0, n0 + 64 * c, bb);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -235,7 +255,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major, g.bf16);
+      const uint32_t idesc_full = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major, g.bf16);
       const uint32_t a_lbo = g.a_mn_major ? GEMM_CHUNK_BYTES : 16, b_lbo = g.b_mn_major ? GEMM_CHUNK_BYTES : 16;
       const uint32_t a_kstep = g.a_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;  // bytes per UMMA_K
       const uint32_t b_kstep = g.b_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;
@@ -245,10 +265,11 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       GemmWork w;
-      for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
+      for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
         if (!(ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, g.status, 2))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t idesc = w.bn == BN ? idesc_full : make_idesc_f16(GEMM_BM, w.bn, g.a_mn_major, g.b_mn_major, g.bf16);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(ok = mbar_wait(full_bar(stage), phase, g.status, 3))) break;
           tc_fence_after();
@@ -280,14 +301,14 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     uint32_t acc_phase = 0;
     bool ok = true;
     GemmWork w;
-    for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
+    for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
       const long long t = w.t;
       const int b = (int)(t / tiles_per_batch);
       const long long r = t - (long long)b * tiles_per_batch;
       int tn, tm;
       tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
       const int row = tm * GEMM_BM + quarter * 32 + lane;
-      const int n0 = tn * BN;
+      const int n0 = tn * BN + w.sub * w.bn;
       if (!(ok = mbar_wait(tmem_full_bar(acc), acc_phase, g.status, 4))) break;
       tc_fence_after();
       unsigned short *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
@@ -327,7 +348,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < BN && finish; c += 32) {
+      for (int c = 0; c < w.bn && finish; c += 32) {
         uint32_t v[32];
         // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
         // (beta != 0) are requested before the tensor-memory load is waited for, four 128-bit loads in flight per lane.
@@ -781,7 +802,7 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   else ok = encode_operand(&ta, bf, p.a_ptr, p.k, p.m, eff_batch_a, p.a.rs, p.a.stride, GEMM_BK, GEMM_BM);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for A");
   if (b_mn) ok = encode_operand(&tb, bf, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
-  else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
+  else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, 64);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B");
 
   GemmKernelArgs g;
@@ -817,6 +838,8 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   g.kb_per_slice = 0;
   g.split_ws = op->st.split_ws;
   g.split_tickets = op->st.split_tickets;
+  g.tail_w = 0;
+  g.tail_count = 0;
   {
     const long long sms = op->base.sm_count;
     const long long rem = tiles % sms;
@@ -844,6 +867,30 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
         }
       }
     }
+    // Short K, a partial last wave and no K split: cut the remainder tiles along N instead.  A piece `w` columns wide costs
+    // w / BN of a tile time, times what narrow MMAs lose to shared-memory bandwidth (128 x 128: ~1.15, 128 x 64: ~1.45);
+    // taken when the remainder then costs clearly less than the whole tile time it costs otherwise.
+    if (BN == 256 && rem > 0 && g.split_g == 1 && tiles > sms && !comm) {
+      double best = 0.9;
+      int best_w = 0;
+      const int widths[2] = {128, 64};
+      const double penalty[2] = {1.15, 1.45};
+      for (int i = 0; i < 2; ++i) {
+        const long long pieces = rem * (BN / widths[i]);
+        const double cost = (double)((pieces + sms - 1) / sms) * widths[i] / BN * penalty[i];
+        if (cost < best) {
+          best = cost;
+          best_w = widths[i];
+        }
+      }
+      if (best_w) {
+        g.normal_tiles = tiles - rem;
+        g.normal_iters = (int)(g.normal_tiles / sms);
+        g.split_r = (int)rem;
+        g.tail_w = best_w;
+        g.tail_count = (int)(rem * (BN / best_w));
+      }
+    }
   }
   ops_mat_mul *mop = const_cast<ops_mat_mul *>(op);
   FusedArArgs fa;
@@ -867,7 +914,7 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
     gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
     return check_launch("mat_mul+all_reduce(tcgen05)");
   }
-  const unsigned launch_grid = g.split_g > 1 ? (unsigned)op->base.sm_count : grid;
+  const unsigned launch_grid = (g.split_g > 1 || g.tail_w > 0) ? (unsigned)op->base.sm_count : grid;
   const int slot = BN == 256 ? 0 : 1;
   if (!mop->st.attr_set[slot]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);

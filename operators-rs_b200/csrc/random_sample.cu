@@ -45,6 +45,7 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 template <class T> __device__ __forceinline__ uint32_t raw_bits(T v);
 template <> __device__ __forceinline__ uint32_t raw_bits<__half>(__half v) { return (uint32_t)__half_as_ushort(v); }
 template <> __device__ __forceinline__ uint32_t raw_bits<float>(float v) { return __float_as_uint(v); }
+template <> __device__ __forceinline__ uint32_t raw_bits<__nv_bfloat16>(__nv_bfloat16 v) { return (uint32_t)__bfloat16_as_ushort(v); }
 
 // ------------------------------------------------------------------------------------------------
 // argmax
@@ -84,23 +85,21 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
   if (vec_ok) {
     const int vend = begin + ((end - begin) / PER) * PER;
     const int step = blockDim.x * PER;
-    int i = begin + threadIdx.x * PER;
-    for (; i + 3 * step < vend; i += 4 * step) {  // four independent 128-bit loads in flight per thread
+    // batches of four independent 128-bit loads per thread, every load of a batch issued before the first value is used
+    // (a CTA's share of a row is a few vectors per thread: one trip to DRAM instead of one per vector)
+    for (int i0 = begin + threadIdx.x * PER; i0 < vend; i0 += 4 * step) {
       uint4 raw[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) raw[u] = ld_stream_16(x + i + u * step);
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * step < vend) raw[u] = ld_stream_16(x + i0 + u * step);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const T *e = reinterpret_cast<const T *>(&raw[u]);
+        if (i0 + u * step < vend) {
+          const T *e = reinterpret_cast<const T *>(&raw[u]);
 #pragma unroll
-        for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i + u * step + j);
+          for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i0 + u * step + j);
+        }
       }
-    }
-    for (; i < vend; i += step) {
-      const uint4 raw = ld_stream_16(x + i);
-      const T *e = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-      for (int j = 0; j < PER; ++j) visit(to_f32(e[j]), i + j);
     }
     for (int k = vend + threadIdx.x; k < end; k += blockDim.x) visit(to_f32(x[k]), k);
   } else {
@@ -215,6 +214,7 @@ __device__ __forceinline__ int block_excl_scan(int v, int *scratch, int *total) 
 template <class T> struct KeyBits;
 template <> struct KeyBits<__half> { static constexpr int bits = 16; };
 template <> struct KeyBits<float> { static constexpr int bits = 32; };
+template <> struct KeyBits<__nv_bfloat16> { static constexpr int bits = 16; };
 
 // sort key: ascending key = descending value.  f16 rows get 16-bit keys (4 radix passes), f32 rows 32-bit.
 template <class T> __device__ __forceinline__ uint32_t sort_key(T v);
@@ -225,7 +225,18 @@ template <> __device__ __forceinline__ uint32_t sort_key<__half>(__half v) {
   const uint32_t k = (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
   return (~k) & 0xffffu;
 }
+template <> __device__ __forceinline__ uint32_t sort_key<__nv_bfloat16>(__nv_bfloat16 v) {  // same sign-magnitude layout as f16
+  uint32_t h = __bfloat16_as_ushort(v);
+  if ((h & 0x7fffu) == 0) h = 0;  // -0 -> +0
+  const uint32_t k = (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+  return (~k) & 0xffffu;
+}
 template <class T> __device__ __forceinline__ float key_value(uint32_t key);
+template <> __device__ __forceinline__ float key_value<__nv_bfloat16>(uint32_t key) {
+  const uint32_t k = (~key) & 0xffffu;
+  const uint32_t h = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
+  return __uint_as_float(h << 16);
+}
 template <> __device__ __forceinline__ float key_value<float>(uint32_t key) { return key_to_float(~key); }
 template <> __device__ __forceinline__ float key_value<__half>(uint32_t key) {
   const uint32_t k = (~key) & 0xffffu;
@@ -233,20 +244,10 @@ template <> __device__ __forceinline__ float key_value<__half>(uint32_t key) {
   return __half2float(__ushort_as_half((unsigned short)h));
 }
 
+// maximum of a row over the whole CTA (NaNs ignored), 128-bit loads when the row is 16-byte aligned
 template <class T>
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restrict__ logits, long long row_stride, int n,
-                                                                float temperature, float top_p, unsigned long long top_k,
-                                                                const float *__restrict__ seeds, float seed_scalar,
-                                                                char *__restrict__ ws, long long ws_row_bytes, KVPair *out) {
-  __shared__ SampleShared sh;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int row = blockIdx.x;
-  const T *x = byte_off(logits, (long long)row * row_stride);
-  uint2 *buf_a = reinterpret_cast<uint2 *>(ws + (long long)row * ws_row_bytes);
-  uint2 *buf_b = buf_a + n;
-  const float seed = seeds ? seeds[row] : seed_scalar;
-
-  // ---- S1: row maximum --------------------------------------------------------------------------
+__device__ __forceinline__ float sample_row_max(const T *__restrict__ x, int n, float *red) {
+  const int tid = threadIdx.x;
   float mx = -INFINITY;
   {
     constexpr int PER = 16 / (int)sizeof(T);
@@ -275,7 +276,20 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restr
       for (int i = tid; i < n; i += SAMPLE_THREADS) mx = fmaxf(mx, to_f32(x[i]));
     }
   }
-  mx = block_max(mx, sh.red_f);
+  return block_max(mx, red);
+}
+
+// The sampling path for any element type and row length: order the kept prefix with a stable radix sort in the row's
+// workspace, then the exact prefix sums.  One CTA of SAMPLE_THREADS threads per row.
+template <class T>
+__device__ void sample_sort_body(SampleShared &sh, const T *__restrict__ x, int n, float temperature, float top_p, unsigned long long top_k,
+                                 float seed, char *__restrict__ ws_row, KVPair *out_row) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint2 *buf_a = reinterpret_cast<uint2 *>(ws_row);
+  uint2 *buf_b = buf_a + n;
+
+  // ---- S1: row maximum --------------------------------------------------------------------------
+  const float mx = sample_row_max(x, n, sh.red_f);
 
   // ---- S2: keep (in index order) every element that can still move the sum ----------------------
   if (tid == 0) sh.kept = 0;
@@ -315,8 +329,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restr
       int best = 0;
       for (int i = 1; i < n; ++i)
         if (!(to_f32(x[best]) > to_f32(x[i]))) best = i;
-      out[row].idx = (unsigned)best;
-      out[row].val = raw_bits(from_f32<T>(1.f));
+      out_row->idx = (unsigned)best;
+      out_row->val = raw_bits(from_f32<T>(1.f));
     }
     return;
   }
@@ -520,8 +534,397 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restr
   block_excl_scan(below, sh.scan_i, &total);
   if (tid == 0) {
     const int j = total < M ? total : M - 1;
-    out[row].idx = src[j].y;
-    out[row].val = raw_bits(from_f32<T>(C[j]));
+    out_row->idx = src[j].y;
+    out_row->val = raw_bits(from_f32<T>(C[j]));
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const T *__restrict__ logits, long long row_stride, int n,
+                                                                float temperature, float top_p, unsigned long long top_k,
+                                                                const float *__restrict__ seeds, float seed_scalar,
+                                                                char *__restrict__ ws, long long ws_row_bytes, KVPair *out) {
+  __shared__ SampleShared sh;
+  const int row = blockIdx.x;
+  sample_sort_body<T>(sh, byte_off(logits, (long long)row * row_stride), n, temperature, top_p, top_k, seeds ? seeds[row] : seed_scalar,
+                      ws + (long long)row * ws_row_bytes, out + row);
+}
+
+// ------------------------------------------------------------------------------------------------
+// seeded sampling of 16-bit logits: counting sort by value
+//
+// The cumulative sums of the CPU loop depend on the sorted VALUES only, and a 16-bit type has at most 65536 of them.  So
+// instead of ordering tens of thousands of (value, index) pairs, the kept prefix is counted into a histogram over the value
+// keys (shared memory, one bin per representable value below the row maximum), and the serial f32 prefix sum is
+// reproduced over RUNS of equal terms: inside one binade of the running sum every add of the term e is the integer update
+// S += round_half_even(e / ulp), so m adds of the same e have a closed form (the first add may depend on the parity of S,
+// after a tie the sum is even and the increment is constant), runs compose associatively as (delta if S even, delta if S
+// odd) pairs, and one block-wide scan gives the sum after every bin.  A run that reaches the next binade is finished by
+// its owner thread (one hardware add per binade it crosses), then the scan restarts behind it with the doubled ulp.
+// The index of the chosen element — the r-th of its value in index order — is found by one more pass over the row.
+// Rows whose kept values span more bins than fit fall back to the sort above.
+// ------------------------------------------------------------------------------------------------
+constexpr int HIST_BPT = 49;  // bins per thread: odd, so that the threads' walks over their bins hit 32 different shared-memory banks
+constexpr int HIST_BINS = HIST_BPT * SAMPLE_THREADS;  // 50176 value bins: 196 KB of counters
+constexpr long long BINADE = 1ll << 24;
+
+struct HistState {
+  int thr;        // last kept bin (-1: nothing can be ordered)
+  int overflow;   // a kept element lies beyond the histogram
+  int i0;         // first bin whose sums are not final yet
+  long long rem0; // adds of bin i0 still to do
+  float s;        // running sum in front of bin i0
+  int cross;      // first bin in which the running sum leaves its binade
+  int q_bin;      // answers of the position / threshold queries
+  long long q_off;
+  float q_val;
+};
+
+__device__ __forceinline__ void split_term(float e, float u_inv, long long &q, bool &tie) {
+  const float a = e * u_inv;  // exact power-of-two scaling, a < 2^24
+  const float fl = floorf(a);
+  const float r = a - fl;     // exact
+  q = (long long)fl + (r > 0.5f ? 1 : 0);
+  tie = r == 0.5f;
+}
+// m >= 1 adds of the same term inside one binade, as (increment if the integer sum is even, increment if it is odd)
+__device__ __forceinline__ Pair64 run_pair(long long q, bool tie, long long m) {
+  const long long d2 = q + ((tie && (q & 1)) ? 1 : 0);  // after a tie add the sum is even: from then on the increment is constant
+  Pair64 p;
+  p.d0 = q + ((tie && (q & 1)) ? 1 : 0) + (m - 1) * d2;
+  p.d1 = q + ((tie && !(q & 1)) ? 1 : 0) + (m - 1) * d2;
+  return p;
+}
+// c after m serial f32 adds of e (c >= 1, 0 < e <= 1): closed form inside a binade, one hardware add at each crossing
+__device__ float advance_sum(float c, float e, long long m) {
+  while (m > 0) {
+    const int ex = (int)((__float_as_uint(c) >> 23) & 0xffu) - 127;
+    const float u = __uint_as_float((uint32_t)(ex - 23 + 127) << 23);
+    const float u_inv = __uint_as_float((uint32_t)(23 - ex + 127) << 23);
+    long long S = (long long)(c * u_inv);
+    long long q;
+    bool tie;
+    split_term(e, u_inv, q, tie);
+    const long long d1 = q + ((tie && ((S + q) & 1)) ? 1 : 0);
+    if (S + d1 >= BINADE) {  // this very add reaches the next binade
+      c = __fadd_rn(c, e);
+      --m;
+      continue;
+    }
+    S += d1;
+    --m;
+    if (m > 0) {
+      const long long d2 = q + ((tie && (q & 1)) ? 1 : 0);
+      if (d2 == 0) {
+        m = 0;  // nothing moves the sum any more
+      } else {
+        const long long room = (BINADE - 1 - S) / d2;  // further adds that stay inside the binade
+        const long long k = m < room ? m : room;
+        S += k * d2;
+        m -= k;
+      }
+    }
+    c = (float)S * u;
+    if (m > 0) {
+      c = __fadd_rn(c, e);
+      --m;
+    }
+  }
+  return c;
+}
+
+template <class T>
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_hist_kernel(const T *__restrict__ logits, long long row_stride, int n,
+                                                                     float temperature, float top_p, unsigned long long top_k,
+                                                                     const float *__restrict__ seeds, float seed_scalar,
+                                                                     char *__restrict__ ws, long long ws_row_bytes, KVPair *out) {
+  extern __shared__ __align__(16) unsigned int hist[];  // HIST_BINS counters
+  __shared__ SampleShared sh;
+  __shared__ HistState hs;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;
+  const T *x = byte_off(logits, (long long)row * row_stride);
+  char *ws_row = ws + (long long)row * ws_row_bytes;
+  float *E = reinterpret_cast<float *>(ws_row);  // term of every non-empty bin
+  float *C = E + HIST_BINS;                      // running sum behind every bin
+  const float seed = seeds ? seeds[row] : seed_scalar;
+  KVPair *out_row = out + row;
+  constexpr int PER = 16 / (int)sizeof(T);
+  const bool vec_ok = (((uintptr_t)x) & 15) == 0;
+
+  // ---- S1: row maximum, kept range in key space ------------------------------------------------------
+  const float mx = sample_row_max(x, n, sh.red_f);
+  for (int i = tid; i < HIST_BINS / 4; i += SAMPLE_THREADS) reinterpret_cast<uint4 *>(hist)[i] = make_uint4(0, 0, 0, 0);
+  const uint32_t key0 = sort_key<T>(from_f32<T>(mx));
+  if (tid == 0) {
+    // keep(v) = (v - max) / t >= KEEP_ARG is monotone in v, so the kept values are the keys key0 .. key0 + thr
+    auto keep = [&](uint32_t key) { return __fdiv_rn(__fsub_rn(key_value<T>(key), mx), temperature) >= KEEP_ARG; };
+    int thr = -1;
+    if (keep(key0)) {
+      const uint32_t kinf = sort_key<T>(from_f32<T>(-INFINITY));
+      int lo = 0, hi = (int)(kinf - key0) + 1;  // keep(lo) holds, keep(hi) does not (-inf is never kept)
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (keep(key0 + (uint32_t)mid)) lo = mid;
+        else hi = mid;
+      }
+      thr = lo;
+    }
+    hs.thr = thr;
+    hs.overflow = 0;
+  }
+  __syncthreads();
+  const int thr = hs.thr;
+  if (thr < 0) {
+    // Nothing can be ordered (every logit -inf, or a +inf makes x - max NaN): the argmax rule with the mass 1 as value,
+    // as in the sort path.
+    if (tid == 0) {
+      int best = 0;
+      for (int i = 1; i < n; ++i)
+        if (!(to_f32(x[best]) > to_f32(x[i]))) best = i;
+      out_row->idx = (unsigned)best;
+      out_row->val = raw_bits(from_f32<T>(1.f));
+    }
+    return;
+  }
+  const int nbins = thr + 1 < HIST_BINS ? thr + 1 : HIST_BINS;
+
+  // ---- S2: histogram of the kept values -----------------------------------------------------------------
+  {
+    auto count = [&](T v) {
+      const uint32_t b = sort_key<T>(v) - key0;  // wraps for values above the maximum (NaN patterns): never kept
+      if (b <= (uint32_t)thr) {
+        if (b < (uint32_t)HIST_BINS) atomicAdd(&hist[b], 1u);
+        else hs.overflow = 1;
+      }
+    };
+    if (vec_ok) {
+      const int nv = n / PER;
+      for (int v0 = tid; v0 < nv; v0 += 4 * SAMPLE_THREADS) {
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * SAMPLE_THREADS < nv) raw[u] = ld_global_16(reinterpret_cast<const uint4 *>(x) + v0 + u * SAMPLE_THREADS);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * SAMPLE_THREADS < nv) {
+            const T *e = reinterpret_cast<const T *>(&raw[u]);
+#pragma unroll
+            for (int j = 0; j < PER; ++j) count(e[j]);
+          }
+      }
+      for (int i = nv * PER + tid; i < n; i += SAMPLE_THREADS) count(x[i]);
+    } else {
+      for (int i = tid; i < n; i += SAMPLE_THREADS) count(x[i]);
+    }
+  }
+  __syncthreads();
+  if (hs.overflow) {  // kept values beyond the histogram: order them the long way
+    __syncthreads();
+    sample_sort_body<T>(sh, x, n, temperature, top_p, top_k, seed, ws_row, out_row);
+    return;
+  }
+
+  // ---- S3: the term of every non-empty bin; adds per thread ------------------------------------------
+  const float x0 = key_value<T>(key0);
+  for (int b = tid; b < nbins; b += SAMPLE_THREADS)
+    if (hist[b]) E[b] = (float)exp((double)__fdiv_rn(__fsub_rn(key_value<T>(key0 + (uint32_t)b), x0), temperature));
+  const int b_lo = tid * HIST_BPT, b_hi = min(nbins, b_lo + HIST_BPT);
+  // the maximum itself is position 0 with sum 1; every other kept element is one add
+  auto adds_of = [&](int b) -> long long { return (long long)hist[b] - (b == 0 ? 1 : 0); };
+  int own = 0;
+  for (int b = b_lo; b < b_hi; ++b) own += (int)adds_of(b);
+  int total_adds;
+  const int pre = block_excl_scan(own, sh.scan_i, &total_adds);  // (also makes E visible to the whole CTA)
+  const long long M = (long long)total_adds + 1;                 // kept elements
+
+  // ---- S4: the running sum behind every bin ----------------------------------------------------------
+  if (tid == 0) {
+    hs.i0 = 0;
+    hs.rem0 = adds_of(0);
+    hs.s = 1.f;
+  }
+  __syncthreads();
+  while (true) {
+    const int i0 = hs.i0;
+    if (i0 >= nbins) break;
+    const long long rem0 = hs.rem0;
+    const float s = hs.s;
+    const int ex = (int)((__float_as_uint(s) >> 23) & 0xffu) - 127;   // s in [2^ex, 2^(ex+1))
+    const float u = __uint_as_float((uint32_t)(ex - 23 + 127) << 23);  // ulp of s
+    const float u_inv = __uint_as_float((uint32_t)(23 - ex + 127) << 23);
+    const long long S = (long long)(s * u_inv);  // exact integer in [2^23, 2^24)
+    if (tid == 0) hs.cross = 0x7fffffff;
+    // this thread's bins as one composed pair
+    Pair64 mine{0, 0};
+    for (int b = max(b_lo, i0); b < b_hi; ++b) {
+      const long long m = b == i0 ? rem0 : (long long)hist[b];
+      if (m > 0) {
+        long long q;
+        bool tie;
+        split_term(E[b], u_inv, q, tie);
+        mine = compose(mine, run_pair(q, tie, m));
+      }
+    }
+    // exclusive scan of the threads' pairs (compose is associative, not commutative)
+    Pair64 inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      Pair64 t = shfl_up_pair(inc, o);
+      if (lane >= o) inc = compose(t, inc);
+    }
+    __syncthreads();  // scan_p may still be read from the previous pass; hs.cross is reset
+    if (lane == 31) sh.scan_p[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      Pair64 w = sh.scan_p[lane];
+      Pair64 winc = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        Pair64 t = shfl_up_pair(winc, o);
+        if (lane >= o) winc = compose(t, winc);
+      }
+      Pair64 wex = shfl_up_pair(winc, 1);
+      if (lane == 0) wex = Pair64{0, 0};
+      sh.scan_p[lane] = wex;
+    }
+    __syncthreads();
+    Pair64 lane_ex = shfl_up_pair(inc, 1);
+    if (lane == 0) lane_ex = Pair64{0, 0};
+    const Pair64 before = compose(sh.scan_p[warp], lane_ex);
+    long long St = S + ((S & 1) ? before.d1 : before.d0);
+    // second walk: the sum behind every bin, until a run leaves the binade
+    long long cross_S = 0;
+    for (int b = max(b_lo, i0); b < b_hi; ++b) {
+      const long long m = b == i0 ? rem0 : (long long)hist[b];
+      if (m > 0) {
+        long long q;
+        bool tie;
+        split_term(E[b], u_inv, q, tie);
+        const Pair64 p = run_pair(q, tie, m);
+        const long long S2 = St + ((St & 1) ? p.d1 : p.d0);
+        if (S2 >= BINADE) {
+          atomicMin(&hs.cross, b);
+          cross_S = St;
+          break;  // everything behind is recomputed with the next ulp
+        }
+        St = S2;
+      }
+      C[b] = (float)St * u;
+    }
+    __syncthreads();
+    const int cross = hs.cross;
+    if (cross == 0x7fffffff) break;
+    if (cross >= b_lo && cross < b_hi) {
+      // the owner finishes the crossing run through as many binades as it takes (its own walk stopped exactly there,
+      // and no earlier bin crossed, so cross_S is the true sum in front of the run)
+      const long long m = cross == i0 ? rem0 : (long long)hist[cross];
+      const float c = advance_sum((float)cross_S * u, E[cross], m);
+      C[cross] = c;
+      hs.s = c;
+      hs.i0 = cross + 1;
+      hs.rem0 = cross + 1 < nbins ? (long long)hist[cross + 1] : 0;
+    }
+    __syncthreads();
+  }
+  __syncthreads();
+
+  // ---- S5: thresholds, the chosen position, its value and index ---------------------------------------
+  const float total = C[nbins - 1];
+  // sum at sorted position `pos` (block-wide): 1 at position 0, else the (pos)-th add
+  auto locate = [&](long long pos) {
+    if (pos == 0) {
+      if (tid == 0) {
+        hs.q_bin = 0;
+        hs.q_off = -1;  // the maximum itself: rank 0 of bin 0
+        hs.q_val = 1.f;
+      }
+    } else {
+      const long long t = pos - 1;
+      if (t >= pre && t < (long long)pre + own) {
+        long long running = pre;
+        for (int b = b_lo; b < b_hi; ++b) {
+          const long long m = adds_of(b);
+          if (t < running + m) {
+            const long long a = t - running;
+            hs.q_bin = b;
+            hs.q_off = a;
+            hs.q_val = advance_sum(b == 0 ? 1.f : C[b - 1], E[b], a + 1);
+            break;
+          }
+          running += m;
+        }
+      }
+    }
+    __syncthreads();
+  };
+  const unsigned long long kk = (top_k < (unsigned long long)n ? top_k : (unsigned long long)n) - 1ull;
+  float pk = total;
+  if (kk < (unsigned long long)M) {
+    locate((long long)kk);
+    pk = hs.q_val;
+  }
+  __syncthreads();
+  const float pp = __fmul_rn(total, top_p);
+  const float plimit = __fmul_rn(seed, fminf(pk, pp));
+  if (1.f >= plimit) {
+    locate(0);
+  } else {
+    int below = 0;
+    for (int b = b_lo; b < b_hi; ++b) below += (C[b] < plimit) ? 1 : 0;
+    int bstar;
+    block_excl_scan(below, sh.scan_i, &bstar);  // sums behind the bins never decrease: the count is the first bin that reaches plimit
+    if (bstar >= nbins) {
+      locate(M - 1);  // (cannot happen for seed < 1: the last sum is the largest)
+    } else {
+      if (bstar >= b_lo && bstar < b_hi) {
+        const long long m = adds_of(bstar);
+        const float c_before = bstar == 0 ? 1.f : C[bstar - 1], e = E[bstar];
+        long long lo = -1, hi = m - 1;  // sum after add hi reaches plimit, after add lo it does not
+        while (hi - lo > 1) {
+          const long long mid = (lo + hi) >> 1;
+          if (advance_sum(c_before, e, mid + 1) >= plimit) hi = mid;
+          else lo = mid;
+        }
+        hs.q_bin = bstar;
+        hs.q_off = hi;
+        hs.q_val = advance_sum(c_before, e, hi + 1);
+      }
+      __syncthreads();
+    }
+  }
+  const int q_bin = hs.q_bin;
+  const long long rank = hs.q_off + (q_bin == 0 ? 1 : 0);  // among the elements of that value, in index order
+  const float cj = hs.q_val;
+  const uint32_t want = key0 + (uint32_t)q_bin;
+  // the rank-th element with that value: every thread counts a contiguous piece of the row, then the piece holding it is walked
+  int piece = (n + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  piece = (piece + 7) & ~7;
+  const long long p_lo = (long long)tid * piece;
+  const int i_lo = p_lo < n ? (int)p_lo : n, i_hi = p_lo + piece < n ? (int)(p_lo + piece) : n;
+  int hits = 0;
+  if (vec_ok) {
+    int i = i_lo;
+    for (; i + PER <= i_hi; i += PER) {
+      const uint4 raw = ld_global_16(x + i);
+      const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) hits += sort_key<T>(e[j]) == want ? 1 : 0;
+    }
+    for (; i < i_hi; ++i) hits += sort_key<T>(x[i]) == want ? 1 : 0;
+  } else {
+    for (int i = i_lo; i < i_hi; ++i) hits += sort_key<T>(x[i]) == want ? 1 : 0;
+  }
+  int all_hits;
+  const int before_me = block_excl_scan(hits, sh.scan_i, &all_hits);
+  if (rank >= before_me && rank < (long long)before_me + hits) {
+    long long left = rank - before_me;
+    for (int i = i_lo; i < i_hi; ++i)
+      if (sort_key<T>(x[i]) == want && left-- == 0) {
+        out_row->idx = (unsigned)i;
+        out_row->val = raw_bits(from_f32<T>(cj));
+        break;
+      }
   }
 }
 
@@ -551,7 +954,7 @@ static usz sample_ws_row(usz n) { return (n * 16 + 255) / 256 * 256; }
 static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const void *logits, isz row_stride, void *kv_out,
                        const ops_sample_args &cfg, const float *seeds_dev, float seed_scalar, void *ws, usz ws_len,
                        ArgmaxScratch *arg_scratch, usz arg_rows, cudaStream_t s) {
-  if (dt != OPS_DT_F16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "random_sample: f16 or f32 logits expected");
+  if (dt != OPS_DT_F16 && dt != OPS_DT_BF16 && dt != OPS_DT_F32) return fail(OPS_TYPE_NOT_SUPPORT, "random_sample: f16, bf16 or f32 logits expected");
   if (rows == 0) return OPS_OK;
   if (n == 0) return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: empty logits");
   if (n > 0x7fffffffu / 16 || rows > 0x7fffffu) return fail(OPS_SHAPE_NOT_SUPPORT, "random_sample: shape too large");
@@ -574,6 +977,8 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
     const unsigned grid = (unsigned)(rows * split);
     if (dt == OPS_DT_F16)
       argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half *)logits, row_stride, (int)n, (int)split, scratch, (KVPair *)kv_out);
+    else if (dt == OPS_DT_BF16)
+      argmax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)logits, row_stride, (int)n, (int)split, scratch, (KVPair *)kv_out);
     else
       argmax_kernel<float><<<grid, 256, 0, s>>>((const float *)logits, row_stride, (int)n, (int)split, scratch, (KVPair *)kv_out);
     return check_launch("random_sample(argmax)");
@@ -585,14 +990,35 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
   if (ws_len < need || !ws) return need_workspace(need);
   if (!aligned(ws, 16)) return fail(OPS_ARGS_NOT_SUPPORT, "random_sample: workspace must be 16-byte aligned");
   const float top_p = cfg.top_p > 1.f ? 1.f : cfg.top_p;
-  if (dt == OPS_DT_F16)
-    sample_kernel<__half><<<(unsigned)rows, SAMPLE_THREADS, 0, s>>>((const __half *)logits, row_stride, (int)n, cfg.temperature, top_p,
-                                                                    (unsigned long long)cfg.top_k, seeds_dev, seed_scalar, (char *)ws,
-                                                                    (long long)per_row, (KVPair *)kv_out);
-  else
-    sample_kernel<float><<<(unsigned)rows, SAMPLE_THREADS, 0, s>>>((const float *)logits, row_stride, (int)n, cfg.temperature, top_p,
-                                                                   (unsigned long long)cfg.top_k, seeds_dev, seed_scalar, (char *)ws,
-                                                                   (long long)per_row, (KVPair *)kv_out);
+  // 16-bit logits in rows long enough for their workspace to hold the per-bin arrays take the counting-sort kernel
+  const bool hist_path = dt != OPS_DT_F32 && per_row >= (usz)HIST_BINS * 2 * sizeof(float);
+  if (hist_path) {
+    constexpr int smem = HIST_BINS * (int)sizeof(unsigned int);
+    static bool attr_set[2][64];  // [type][device]: the opt-in to 196 KB of dynamic shared memory, once per device
+    const int ti = dt == OPS_DT_F16 ? 0 : 1, di = base.device & 63;
+    if (!attr_set[ti][di]) {
+      cudaError_t e = ti == 0 ? cudaFuncSetAttribute(sample_hist_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                              : cudaFuncSetAttribute(sample_hist_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "random_sample: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      attr_set[ti][di] = true;
+    }
+    if (dt == OPS_DT_F16)
+      sample_hist_kernel<__half><<<(unsigned)rows, SAMPLE_THREADS, smem, s>>>((const __half *)logits, row_stride, (int)n, cfg.temperature, top_p,
+                                                                              (unsigned long long)cfg.top_k, seeds_dev, seed_scalar, (char *)ws,
+                                                                              (long long)per_row, (KVPair *)kv_out);
+    else
+      sample_hist_kernel<__nv_bfloat16><<<(unsigned)rows, SAMPLE_THREADS, smem, s>>>((const __nv_bfloat16 *)logits, row_stride, (int)n, cfg.temperature,
+                                                                                     top_p, (unsigned long long)cfg.top_k, seeds_dev, seed_scalar,
+                                                                                     (char *)ws, (long long)per_row, (KVPair *)kv_out);
+    return check_launch("random_sample(sample, counting sort)");
+  }
+#define OPS_SAMPLE_SORT(T)                                                                                                                   \
+  sample_kernel<T><<<(unsigned)rows, SAMPLE_THREADS, 0, s>>>((const T *)logits, row_stride, (int)n, cfg.temperature, top_p, (unsigned long long)cfg.top_k, \
+                                                            seeds_dev, seed_scalar, (char *)ws, (long long)per_row, (KVPair *)kv_out)
+  if (dt == OPS_DT_F16) OPS_SAMPLE_SORT(__half);
+  else if (dt == OPS_DT_BF16) OPS_SAMPLE_SORT(__nv_bfloat16);
+  else OPS_SAMPLE_SORT(float);
+#undef OPS_SAMPLE_SORT
   return check_launch("random_sample(sample)");
 }
 

@@ -30,3 +30,16 @@ def error_collector(got, ref64, abs_thr=F16_EPS, rel_thr=0.0):
 def assert_reference_rule(got, ref64, rel_thr, what=""):
     out, cnt = error_collector(got, ref64, F16_EPS, rel_thr)
     assert out * 1000 <= cnt, f"{what}: {out}/{cnt} outliers under the reference's rule (rel {rel_thr})"
+
+
+def assert_close_scaled(got, ref, tol=1e-2, what=""):
+    """BASELINE's max-abs budget for values of magnitude O(1), widened in proportion where the reference value is large:
+    |got - ref| <= tol * max(1, |ref| / 4).  The residual stream of a decoder layer reaches |x| ~ 10, where ONE f16 ulp is
+    already 7.8e-3; two implementations that round at different points differ by two ulps there (1.6e-2) while agreeing
+    to 5e-3 wherever |x| < 4."""
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    g, r = got.astype(np.float64), ref.astype(np.float64)
+    assert np.isfinite(g).all(), f"{what}: non-finite output"
+    excess = np.abs(g - r) / np.maximum(1.0, np.abs(r) / 4.0)
+    worst = float(excess.max()) if excess.size else 0.0
+    assert worst <= tol, f"{what}: scaled max-abs {worst} > {tol} (raw max-abs {float(np.abs(g - r).max())})"

@@ -10,7 +10,8 @@ heads, dh 128, ffn 14336) and is compared with the oracle's chain of the restate
 Also here: the gate|up and down projections and the causal softmax at their full config-2/3 sizes, checked on
 sampled rows (rows of a product and of a softmax are independent, so the oracle only needs the sampled ones).
 
-Tolerance everywhere: max-abs 1e-2 on f16 outputs (BASELINE's budget; one f16 ulp is 2e-3 at |x| in [2,4)).
+Tolerance: max-abs 1e-2 on f16 outputs (BASELINE's budget; one f16 ulp is 2e-3 at |x| in [2,4)); where outputs grow
+beyond |x| = 4 (the residual stream, the twice-accumulated down projection) the budget widens in proportion to |x|.
 """
 import importlib
 
@@ -19,7 +20,7 @@ import pytest
 import torch
 
 import __graft_entry__ as graft
-from helpers import assert_close
+from helpers import assert_close, assert_close_scaled
 
 pytestmark = pytest.mark.gpu
 
@@ -54,13 +55,14 @@ def test_decoder_layer_full_width_matches_oracle_chain(pkg, orc, dev, tokens):
     torch.cuda.synchronize()
     assert layer.mat_mul.status() == 0 and layer.attention.status() == 0
     ref = orc.decoder_layer(x_host, np.arange(tokens, dtype=np.uint32), [{k: v.cpu().numpy() for k, v in w.items()}], CFG3)
-    # the residual stream has |x| up to ~5: one f16 ulp there is 4e-3, two roundings apart at most
-    assert_close(out.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens")
+    # the residual stream reaches |x| ~ 10, where one f16 ulp is 7.8e-3: the 1e-2 budget holds for |x| < 4 and widens in
+    # proportion above (see assert_close_scaled)
+    assert_close_scaled(out.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens")
     # a second pass over the same buffers (the chain updates the stream in place; scratch is reused)
     x.copy_(torch.from_numpy(x_host))
     out2 = layer.forward(x, pos)
     torch.cuda.synchronize()
-    assert_close(out2.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens, second pass")
+    assert_close_scaled(out2.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens, second pass")
 
 
 def _sample_rows(n, count, seed):

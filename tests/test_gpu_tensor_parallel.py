@@ -50,6 +50,13 @@ def _rank_main(rank, world, port, out_dir):
     handles = [None] * world
     dist.all_gather_object(handles, comm.p2p_export(4096 * 4096 * 2))
     comm.p2p_attach(handles)
+    # a second communicator: the stream of the second row chunk of the pipelined layer tail
+    ids = [pkg.Comm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    comm2 = pkg.Comm(rank, rank, world, ids[0])
+    handles = [None] * world
+    dist.all_gather_object(handles, comm2.p2p_export(T_LAYER * CFG["d"] * 2))
+    comm2.p2p_attach(handles)
     op = pkg.AllReduce(comm)
     results = {}
     for T in (1, 64, 4096):
@@ -69,7 +76,42 @@ def _rank_main(rank, world, port, out_dir):
         torch.cuda.synchronize()
         results[f"ar_{T}_auto"] = dst.cpu().numpy()
         assert torch.equal(src.cpu(), torch.from_numpy(part))
+        # dst <- dst + sum(src) with src in the zero-copy region: the residual (same on every rank) enters the sum first
+        resid = synth.normal(0xB2000099 + T, (T, 4096), 1.0).astype(np.float16)
+        direct = comm.p2p_direct(torch.float16)[: T * 4096].view(T, 4096)
+        for rep in range(2):
+            direct.copy_(torch.from_numpy(part).to(dev))
+            acc = torch.from_numpy(resid).to(dev)
+            op.launch_add(pkg.AllReduceArgs.of(acc, direct))
+            torch.cuda.synchronize()
+        results[f"ar_{T}_add"] = acc.cpu().numpy()
+        # and with a staged (ordinary) source buffer
+        acc = torch.from_numpy(resid).to(dev)
+        op.launch_add(pkg.AllReduceArgs.of(acc, torch.from_numpy(part).to(dev)))
+        torch.cuda.synchronize()
+        results[f"ar_{T}_add_staged"] = acc.cpu().numpy()
     assert comm.p2p_status() == 0
+    # replayed launches: the peer-to-peer kernels keep their launch counter on the device, so a CUDA graph holding three
+    # one-shot all_reduces can be replayed (every rank replays the same sequence)
+    op.set_algo(pkg.ALL_REDUCE_P2P_ONE_SHOT)
+    gsrc = torch.from_numpy((synth.normal(0xB20000AA + rank, (64, 4096), 1.0) / np.sqrt(world)).astype(np.float16)).to(dev)
+    gdst = [torch.zeros_like(gsrc) for _ in range(3)]
+    op.launch(pkg.AllReduceArgs.of(gdst[0], gsrc))  # warm-up outside the capture
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream(dev)
+    cg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(cg, stream=side):
+        for i in range(3):
+            op.launch(pkg.AllReduceArgs.of(gdst[i], gsrc))
+    for rep in range(3):
+        for t_ in gdst:
+            t_.zero_()
+        cg.replay()
+        torch.cuda.synchronize()
+    results["ar_graph_replay"] = torch.stack(gdst).cpu().numpy()
+    assert comm.p2p_status() == 0
+    op.set_algo(pkg.ALL_REDUCE_AUTO)
     # broadcast from the last rank (bytes), in place on the root and out of place elsewhere
     bc = pkg.Broadcast(comm)
     payload = torch.full((1000,), rank + 1, dtype=torch.int32, device=dev)
@@ -98,17 +140,22 @@ def _rank_main(rank, world, port, out_dir):
         assert mm.status() == 0 and comm.p2p_status() == 0
         assert torch.equal(c_ref, c_fused), f"fused mat_mul+all_reduce differs (rep {rep})"
     results["fused_gemm_ar"] = c_fused.cpu().numpy()
-    for name, algo, fused in (("nccl", pkg.ALL_REDUCE_NCCL, False), ("p2p", pkg.ALL_REDUCE_P2P_ONE_SHOT, False), ("fused", pkg.ALL_REDUCE_AUTO, True)):
-        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comm=comm, tp=world, rank=rank, all_reduce_algo=algo, fused_all_reduce=fused)
+    layer_mod.DecoderLayer.DIRECT_MIN_BYTES = 1 << 16  # let the small test layer take the zero-copy exchange
+    for name, algo, fused, direct, pipe in (("nccl", pkg.ALL_REDUCE_NCCL, False, False, 1), ("p2p", pkg.ALL_REDUCE_P2P_ONE_SHOT, False, False, 1),
+                                            ("fused", pkg.ALL_REDUCE_AUTO, True, False, 1), ("direct", pkg.ALL_REDUCE_AUTO, False, True, 1),
+                                            ("pipelined", pkg.ALL_REDUCE_AUTO, False, True, 2)):
+        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comms=[comm, comm2], tp=world, rank=rank, all_reduce_algo=algo, fused_all_reduce=fused,
+                                     direct=direct, pipeline=pipe)
         x = torch.from_numpy(synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)).to(dev)
         pos = torch.arange(T_LAYER, dtype=torch.int32, device=dev).view(torch.uint32)
         out = lay.forward(x, pos)
         torch.cuda.synchronize()
         results[f"layer_{name}"] = out.cpu().numpy()
-    assert comm.p2p_status() == 0
+    assert comm.p2p_status() == 0 and comm2.p2p_status() == 0
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
     dist.barrier()
     del op, lay
+    comm2.destroy()
     comm.destroy()
     dist.destroy_process_group()
 
@@ -134,13 +181,28 @@ def test_all_reduce_and_tp_layer(tmp_path, orc, synth, world):
             assert float(np.abs(outs[0].astype(np.float32) - ref.astype(np.float32)).max()) <= 1e-2, (T, name)
             if name in ("one_shot", "two_shot"):
                 np.testing.assert_array_equal(outs[0].view(np.uint16), acc.astype(np.float16).view(np.uint16))
+        resid = synth.normal(0xB2000099 + T, (T, 4096), 1.0).astype(np.float16)
+        acc = resid.astype(np.float32)
+        for p_ in parts:  # the residual first, then the ranks in order, one rounding
+            acc = (acc + p_.astype(np.float32)).astype(np.float32)
+        for name in ("add", "add_staged"):
+            outs = [res[r][f"ar_{T}_{name}"] for r in range(world)]
+            for o in outs:
+                np.testing.assert_array_equal(o.view(np.uint16), acc.astype(np.float16).view(np.uint16))
+    gparts = [(synth.normal(0xB20000AA + r, (64, 4096), 1.0) / np.sqrt(world)).astype(np.float16) for r in range(world)]
+    gacc = np.zeros((64, 4096), np.float32)
+    for p_ in gparts:
+        gacc = (gacc + p_.astype(np.float32)).astype(np.float32)
+    for r in range(world):
+        for i in range(3):
+            np.testing.assert_array_equal(res[r]["ar_graph_replay"][i].view(np.uint16), gacc.astype(np.float16).view(np.uint16))
     for r in range(world):
         assert (res[r]["broadcast"] == world).all()
     layer = importlib.import_module(graft.PKG_NAME + ".layer")
     cfg = layer.LayerConfig(**CFG)
     x = synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)
     emu = orc.decoder_layer(x, np.arange(T_LAYER, dtype=np.uint32), [layer.shard_weights(_weights(synth), r, world, cfg) for r in range(world)], CFG)
-    for name in ("nccl", "p2p", "fused"):
+    for name in ("nccl", "p2p", "fused", "direct", "pipelined"):
         outs = [res[r][f"layer_{name}"] for r in range(world)]
         for o in outs[1:]:
             np.testing.assert_array_equal(o.view(np.uint16), outs[0].view(np.uint16))

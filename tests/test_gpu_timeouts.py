@@ -34,5 +34,11 @@ def test_missing_peer_times_out_cleanly(pkg, dev, algo_name):
     pkg.RmsNorm(0).launch(pkg.RmsNormArgs.of(y, torch.full((8, 256), 2.0, dtype=torch.float16, device=dev), w, 0.0))
     torch.cuda.synchronize()
     np.testing.assert_allclose(y.float().cpu().numpy(), 1.0, atol=1e-3)
+    # the first failure sticks until the communicator is reset; after the reset a new time-out is reported afresh
+    comm.p2p_reset()
+    assert comm.p2p_status() == 0
+    op.launch(pkg.AllReduceArgs.of(x, x))
+    torch.cuda.synchronize()
+    assert comm.p2p_status() == code
     del op
     comm.destroy()
