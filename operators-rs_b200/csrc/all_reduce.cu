@@ -187,6 +187,16 @@ __global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_c
 //           nothing is staged; peers are read at that offset of their direct regions.
 //   ADD:    dst <- dst + sum over ranks of src: the old value of dst (identical on every rank, e.g. a replicated residual
 //           stream) enters the f32 sum of the part this rank reduces, first, before rank 0's partial.
+// The kernel is kept light on purpose — 256 threads, at most 64 registers each — so that one of its CTAs fits on an SM
+// beside a CTA of the persistent tensor-core GEMM: an exchange on one stream then really overlaps a projection on another.
+constexpr int P2P_TWO_SHOT_THREADS = 256;
+
+template <bool DIRECT>
+__device__ __forceinline__ const uint4 *two_shot_in(const P2PKernelArgs &a, int q, unsigned int parity, unsigned long long direct_off) {
+  char *pb = a.peers[q];
+  return reinterpret_cast<const uint4 *>(DIRECT ? region_direct(pb, a.region_bytes) + direct_off : region_in(pb, a.region_bytes, parity));
+}
+
 template <class T, bool DIRECT, bool ADD>
 __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                               long long vecs, long long part_vecs, unsigned long long direct_off) {
@@ -223,13 +233,12 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
   {
     const long long base = (long long)a.rank * part_vecs;
     const long long stop = min(s_hi, vecs - base);
-    const uint4 *pin[MAX_RANKS];
+    for (long long v = s_lo + threadIdx.x; v < stop; v += blockDim.x) {
+      uint4 raw[MAX_RANKS], old = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int q = 0; q < MAX_RANKS; ++q) {
-      char *pb = a.peers[q < a.size ? q : 0];
-      pin[q] = reinterpret_cast<const uint4 *>(DIRECT ? region_direct(pb, a.region_bytes) + direct_off : region_in(pb, a.region_bytes, parity)) + base;
-    }
-    auto reduce_one = [&](long long v, uint4 old, const uint4 (&raw)[MAX_RANKS]) {
+      for (int q = 0; q < MAX_RANKS; ++q)
+        if (q < a.size) raw[q] = ld_peer_16(two_shot_in<DIRECT>(a, q, parity, direct_off) + base + v);
+      if constexpr (ADD) old = dst[base + v];
       float acc[Acc8<T>::N] = {};
       if constexpr (ADD) Acc8<T>::add(acc, old);
 #pragma unroll
@@ -238,32 +247,6 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
       const uint4 r = Acc8<T>::pack(acc);
       mine_out[v] = r;
       dst[base + v] = r;
-    };
-    long long v = s_lo + threadIdx.x;
-    if (a.size <= 4) {  // few ranks: two vectors per peer in flight per thread
-      for (; v + blockDim.x < stop; v += 2 * blockDim.x) {
-        uint4 r0[MAX_RANKS], r1[MAX_RANKS], o0 = make_uint4(0, 0, 0, 0), o1 = o0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if (q < a.size) {
-            r0[q] = ld_peer_16(pin[q] + v);
-            r1[q] = ld_peer_16(pin[q] + v + blockDim.x);
-          }
-        if constexpr (ADD) {
-          o0 = dst[base + v];
-          o1 = dst[base + v + blockDim.x];
-        }
-        reduce_one(v, o0, r0);
-        reduce_one(v + blockDim.x, o1, r1);
-      }
-    }
-    for (; v < stop; v += blockDim.x) {
-      uint4 raw[MAX_RANKS], old = make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int q = 0; q < MAX_RANKS; ++q)
-        if (q < a.size) raw[q] = ld_peer_16(pin[q] + v);
-      if constexpr (ADD) old = dst[base + v];
-      reduce_one(v, old, raw);
     }
   }
   __threadfence_system();
@@ -273,51 +256,30 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
     st_release_sys(&pf->reduced[a.rank][blockIdx.x], epoch);
   }
   if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 3)) return;
-  // gather the other parts: one vector from every peer in flight per thread and trip (two with four ranks or fewer)
-  {
-    const uint4 *pout[MAX_RANKS];
-    long long gbase[MAX_RANKS], gstop[MAX_RANKS];
+  // gather the other parts: one vector from every peer in flight per thread and trip
+  for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x) {
+    uint4 raw[MAX_RANKS];
 #pragma unroll
-    for (int i = 0; i < MAX_RANKS; ++i) {
-      const int q = (a.rank + 1 + i) % a.size;  // rank r starts at peer r+1: spreads the load over the links
-      pout[i] = reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity));
-      gbase[i] = (long long)q * part_vecs;
-      gstop[i] = min(s_hi, vecs - gbase[i]);
-    }
-    long long v = s_lo + threadIdx.x;
-    if (a.size <= 4) {
-      for (; v + blockDim.x < s_hi; v += 2 * blockDim.x) {
-        uint4 r0[3], r1[3];
-#pragma unroll
-        for (int i = 0; i < 3; ++i)
-          if (i < a.size - 1) {
-            if (v < gstop[i]) r0[i] = ld_peer_16(pout[i] + v);
-            if (v + blockDim.x < gstop[i]) r1[i] = ld_peer_16(pout[i] + v + blockDim.x);
-          }
-#pragma unroll
-        for (int i = 0; i < 3; ++i)
-          if (i < a.size - 1) {
-            if (v < gstop[i]) dst[gbase[i] + v] = r0[i];
-            if (v + blockDim.x < gstop[i]) dst[gbase[i] + v + blockDim.x] = r1[i];
-          }
+    for (int i = 0; i < MAX_RANKS - 1; ++i)
+      if (i < a.size - 1) {
+        int q = a.rank + 1 + i;  // rank r starts at peer r+1: spreads the load over the links
+        if (q >= a.size) q -= a.size;
+        if ((long long)q * part_vecs + v < vecs) raw[i] = ld_peer_16(reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity)) + v);
       }
-    }
-    for (; v < s_hi; v += blockDim.x) {
-      uint4 raw[MAX_RANKS];
 #pragma unroll
-      for (int i = 0; i < MAX_RANKS - 1; ++i)
-        if (i < a.size - 1 && v < gstop[i]) raw[i] = ld_peer_16(pout[i] + v);
-#pragma unroll
-      for (int i = 0; i < MAX_RANKS - 1; ++i)
-        if (i < a.size - 1 && v < gstop[i]) dst[gbase[i] + v] = raw[i];
-    }
+    for (int i = 0; i < MAX_RANKS - 1; ++i)
+      if (i < a.size - 1) {
+        int q = a.rank + 1 + i;
+        if (q >= a.size) q -= a.size;
+        if ((long long)q * part_vecs + v < vecs) dst[(long long)q * part_vecs + v] = raw[i];
+      }
   }
 }
 
 template <class T, bool DIRECT, bool ADD>
-__global__ void __launch_bounds__(512) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
-                                                                  uint4 *__restrict__ dst, long long vecs, long long part_vecs,
-                                                                  unsigned long long direct_off) {
+__global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS, 4) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+                                                                                      uint4 *__restrict__ dst, long long vecs, long long part_vecs,
+                                                                                      unsigned long long direct_off) {
   const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
   two_shot_body<T, DIRECT, ADD>(a, epoch, src, dst, vecs, part_vecs, direct_off);
   __syncthreads();
@@ -599,7 +561,7 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     all_reduce_one_shot_kernel<T><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
   } else {
     const long long part = (vecs + c->size - 1) / c->size;
-    long long ctas = (part + 511) / 512;
+    long long ctas = (part + 2 * P2P_TWO_SHOT_THREADS - 1) / (2 * P2P_TWO_SHOT_THREADS);
     if (ctas > c->sm_count) ctas = c->sm_count;  // every CTA must be resident: same-index CTAs of different ranks wait for each other
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
@@ -608,7 +570,7 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     const bool in_direct = (const char *)src >= direct && (const char *)src + bytes <= direct + c->region_bytes;
     const unsigned long long off = in_direct ? (unsigned long long)((const char *)src - direct) : 0ull;
 #define OPS_TWO_SHOT(DIRECT, ADD) \
-  all_reduce_two_shot_kernel<T, DIRECT, ADD><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part, off)
+  all_reduce_two_shot_kernel<T, DIRECT, ADD><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part, off)
     if (in_direct && add) OPS_TWO_SHOT(true, true);
     else if (in_direct) OPS_TWO_SHOT(true, false);
     else if (add) OPS_TWO_SHOT(false, true);

@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 //   warps 12-15   correction: O lives in tensor memory and accumulates across blocks; when a row maximum moved, these warps
 //                 rescale that tile's O (tcgen05.ld, multiply, tcgen05.st) while the softmax warps are busy with the
 //                 exponentials, and at the end they divide by the row sums and store o.
-// Registers are redistributed after start-up (setmaxnreg): the softmax threads get the 184 they need for a whole row.
+// Registers are redistributed after start-up (setmaxnreg): the softmax threads get the 176 they need for a whole row.
 // Every mbarrier wait is bounded; a wait that runs out records its code and every role unwinds to the common teardown.
 constexpr int FP_BM = 128;        // rows per q tile
 constexpr int FP_BN = 128;        // keys per block
@@ -614,7 +614,7 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ softmax: one thread per q row
-    setmaxnreg_inc<184>();
+    setmaxnreg_inc<176>();
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
@@ -655,9 +655,15 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       mx = chunk_max(s1, kv0 + 32, mx);
       mx = chunk_max(s2, kv0 + 64, mx);
       mx = chunk_max(s3, kv0 + 96, mx);
+      // Lazy rescaling: the reference point m of the exponentials only follows the row maximum when that has moved by more
+      // than 2^8 — until then the probabilities are taken relative to the older, smaller m (they stay below 256, exact in
+      // the 16-bit operand; the f32 row sum and O carry the same factor, which cancels in o = O / l).  Rescaling O costs
+      // a round trip through tensor memory on the critical path of every block; this way it happens a few times per row.
       const float m_raw = fmaxf(m, mx * g.scale_log2);
-      const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // a row with nothing visible yet: keep the arithmetic finite
-      const float alpha = fp_ex2(m - m_new);                 // 0 on the first block (m = -inf)
+      const bool move = m_raw > m + 8.f;                     // also true on the first block (m = -inf)
+      const float m_next = move ? m_raw : m;
+      const float m_new = m_next == -INFINITY ? 0.f : m_next;  // a row with nothing visible yet: keep the arithmetic finite
+      const float alpha = move ? fp_ex2(m - m_new) : 1.f;    // 0 on the first block
       alpha_s[t * FP_BM + row_in_tile] = alpha;
       __syncwarp();
       if (lane == 0) mbar_arrive(alpha_full(t));
@@ -687,14 +693,14 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(t));
       l = fmaf(l, alpha, rowsum);
-      m = m_new;
+      m = m_next;
     }
     l_s[t * FP_BM + row_in_tile] = l;
     __syncwarp();
     if (lane == 0) mbar_arrive(l_full(t));
   } else {
     // ------------------------------------------------------------------ correction and output (warps 12..15)
-    setmaxnreg_dec<80>();
+    setmaxnreg_dec<96>();
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
@@ -711,13 +717,18 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
             tc_fence_after();
             const uint32_t to = tmem_base + lane_addr + o_col(t);
 #pragma unroll 1
-            for (int c = 0; c < FP_DH; c += 32) {
-              uint32_t v[32];
-              tmem_ld_32x32(to + (uint32_t)c, v);
+            for (int c = 0; c < FP_DH; c += 64) {  // two loads per round trip to tensor memory
+              uint32_t v0[32], v1[32];
+              tmem_ld_32x32(to + (uint32_t)c, v0);
+              tmem_ld_32x32(to + (uint32_t)c + 32u, v1);
               tmem_wait_ld();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * a);
-              tmem_st_32x32(to + (uint32_t)c, v);
+              for (int e = 0; e < 32; ++e) {
+                v0[e] = __float_as_uint(__uint_as_float(v0[e]) * a);
+                v1[e] = __float_as_uint(__uint_as_float(v1[e]) * a);
+              }
+              tmem_st_32x32(to + (uint32_t)c, v0);
+              tmem_st_32x32(to + (uint32_t)c + 32u, v1);
             }
             tmem_wait_st();
           }
@@ -736,31 +747,35 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       const float inv = __frcp_rn(l_s[t * FP_BM + row_in_tile]);
       const uint32_t to = tmem_base + lane_addr + o_col(t);
       unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss;
-#pragma unroll 1
-      for (int c = 0; c < FP_DH; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(to + (uint32_t)c, v);
-        tmem_wait_ld();
-        if (q_row < g.seq) {
-          if (g.vec_store) {
+      auto store32 = [&](const uint32_t (&v)[32], int c) {
+        if (q_row >= g.seq) return;
+        if (g.vec_store) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 out;
-              out.x = fp_pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv, g.bf16);
-              out.y = fp_pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, g.bf16);
-              out.z = fp_pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, g.bf16);
-              out.w = fp_pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, g.bf16);
-              st_global_16(orow + c + q4 * 8, out);
-            }
-          } else {
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 out;
+            out.x = fp_pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv, g.bf16);
+            out.y = fp_pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, g.bf16);
+            out.z = fp_pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, g.bf16);
+            out.w = fp_pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, g.bf16);
+            st_global_16(orow + c + q4 * 8, out);
+          }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const uint32_t pr = fp_pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv, g.bf16);
-              orow[c + e] = (unsigned short)(pr & 0xffffu);
-              orow[c + e + 1] = (unsigned short)(pr >> 16);
-            }
+          for (int e = 0; e < 32; e += 2) {
+            const uint32_t pr = fp_pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv, g.bf16);
+            orow[c + e] = (unsigned short)(pr & 0xffffu);
+            orow[c + e + 1] = (unsigned short)(pr >> 16);
           }
         }
+      };
+#pragma unroll 1
+      for (int c = 0; c < FP_DH; c += 64) {  // two loads per round trip to tensor memory
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(to + (uint32_t)c, v0);
+        tmem_ld_32x32(to + (uint32_t)c + 32u, v1);
+        tmem_wait_ld();
+        store32(v0, c);
+        store32(v1, c + 32);
       }
     }
   }

@@ -169,7 +169,8 @@ template <int BN> struct GemmCfg {
 template <int BN, bool FUSED>
 __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ GemmKernelArgs g, const __grid_constant__ FusedArArgs fa) {
+                            const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ GemmKernelArgs g,
+                            const __grid_constant__ FusedArArgs fa) {
   typedef GemmCfg<BN> Cfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (g.tail_w > 0) tma_prefetch_desc(&tmap_b64);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -242,8 +244,10 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           }
           if (g.b_mn_major) {
             for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
-          } else {  // 64 rows of 128 swizzled bytes per box: stacked boxes give the layout of one tall box
-            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), k0, n0 + 64 * c, bb);
+          } else if (w.bn == BN) {
+            tma_load_3d(sb, &tmap_b, full_bar(stage), k0, n0, bb);  // one box BN rows tall
+          } else {  // a narrow piece: boxes of 64 rows (of 128 swizzled bytes), stacked they give the layout of one tall box
+            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b64, full_bar(stage), k0, n0 + 64 * c, bb);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -802,8 +806,11 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   else ok = encode_operand(&ta, bf, p.a_ptr, p.k, p.m, eff_batch_a, p.a.rs, p.a.stride, GEMM_BK, GEMM_BM);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for A");
   if (b_mn) ok = encode_operand(&tb, bf, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
-  else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, 64);
+  else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B");
+  CUtensorMap tb64 = tb;  // K-major B in boxes of 64 rows: what the narrow pieces of a remainder wave load (MN-major B already travels so)
+  if (!b_mn && !encode_operand(&tb64, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, 64))
+    return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B (narrow boxes)");
 
   GemmKernelArgs g;
   g.d = (unsigned short *)p.d_ptr;
@@ -911,7 +918,7 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
       if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
       mop->st.attr_set[slot] = true;
     }
-    gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
+    gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tb64, g, fa);
     return check_launch("mat_mul+all_reduce(tcgen05)");
   }
   const unsigned launch_grid = (g.split_g > 1 || g.tail_w > 0) ? (unsigned)op->base.sm_count : grid;
@@ -921,7 +928,7 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     mop->st.attr_set[slot] = true;
   }
-  gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
+  gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tb64, g, fa);
   return check_launch("mat_mul(tcgen05)");
 }
 

