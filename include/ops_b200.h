@@ -193,7 +193,7 @@ int ops_rearrange_plan(const ops_rearrange_args *args, ptrdiff_t *out, size_t ca
  * mat_mul — mat_mul::Args (operators/src/mat_mul/args.rs:11-20); replaces
  * mat_mul::common_cpu::Operator (operators/src/mat_mul/common_cpu/mod.rs:9-107).
  * C <- beta*C + alpha*A*B, rank 2 or 3 (one batch dim, batch 1 broadcasts), every matrix with a
- * unit stride in one of its two dims.  f16 runs on tcgen05 tensor cores with f32 accumulation.
+ * unit stride in one of its two dims.  f16 and bf16 run on tcgen05 tensor cores with f32 accumulation.
  * ------------------------------------------------------------------------------------------- */
 typedef struct ops_mat_mul ops_mat_mul;
 typedef struct {
@@ -210,6 +210,9 @@ void ops_mat_mul_destroy(ops_mat_mul *op);
 /* 0, or which bounded wait inside the tensor-core kernel ran out (1 producer, 2/3 issuer, 4 epilogue).
  * Synchronises the device: for tests and post-mortems.  No counterpart in the crate. */
 int ops_mat_mul_status(const ops_mat_mul *op);
+/* The first failure sticks, and the output of a launch that set the status is undefined.  _status_reset clears the word
+ * and the handle's internal arrival counters (synchronises the device).  No counterpart in the crate. */
+int ops_mat_mul_status_reset(ops_mat_mul *op);
 
 /* ---------------------------------------------------------------------------------------------
  * attention — attention::Args (operators/src/attention/args.rs:10-24); replaces
@@ -234,6 +237,7 @@ enum { OPS_ATTENTION_CHAIN = 0, OPS_ATTENTION_FUSED = 1, OPS_ATTENTION_FUSED_ONE
 int ops_attention_create(int device, ops_attention **out);
 int ops_attention_set_algo(ops_attention *op, int algo); /* default OPS_ATTENTION_FUSED (falls back to the chain when a layout rules it out) */
 int ops_attention_status(const ops_attention *op);      /* 0, or the code of a bounded wait that ran out; synchronises; no counterpart in the crate */
+int ops_attention_status_reset(ops_attention *op);      /* clears it (and the handle's arrival counters); outputs of the failed launch are undefined */
 int ops_attention_scheme(ops_attention *op, const ops_attention_args *args, size_t max_ws, size_t *ws_out);
 int ops_attention_launch(const ops_attention *op, const ops_attention_args *args, void *ws, size_t ws_len, void *stream);
 void ops_attention_destroy(ops_attention *op);
@@ -263,7 +267,7 @@ void ops_attention_kv_cached_destroy(ops_attention_kv_cached *op);
 /* ---------------------------------------------------------------------------------------------
  * random_sample — random_sample::Args, SampleArgs (operators/src/random_sample/args.rs:9-84);
  * replaces random_sample::common_cpu::Operator (operators/src/random_sample/common_cpu/mod.rs:11-144).
- * One row of logits (f16 or f32, contiguous) -> one KVPair {u32 idx, u32 val-bits}.
+ * One row of logits (f16, bf16 or f32, contiguous) -> one KVPair {u32 idx, u32 val-bits}.
  * argmax when temperature == 0 or top_k == 1 (last index among equal maxima, val = the logit);
  * otherwise seeded sampling where `seed` is the caller's uniform draw in [0,1) and val = the
  * cumulative mass at the chosen entry converted to the logit type.

@@ -580,6 +580,9 @@ class MatMul(Operator):
     def status(self):
         return lib().ops_mat_mul_status(self._h)
 
+    def status_reset(self):
+        _check(lib().ops_mat_mul_status_reset(self._h), False)
+
 
 class Attention(Operator):
     NAME = "attention"
@@ -589,6 +592,9 @@ class Attention(Operator):
 
     def status(self):
         return lib().ops_attention_status(self._h)
+
+    def status_reset(self):
+        _check(lib().ops_attention_status_reset(self._h), False)
 
 
 class AttentionKvCached(Operator):
@@ -750,7 +756,8 @@ EXPORTS = [
     *[f"ops_{op}_{fn}" for op in ("rms_norm", "rope", "fused_softmax", "swiglu", "rearrange", "mat_mul", "attention",
                                   "attention_kv_cached", "random_sample", "all_reduce", "broadcast", "add", "add_rows")
       for fn in ("create", "scheme", "launch", "destroy")],
-    "ops_rope_build_pos", "ops_rearrange_plan", "ops_mat_mul_status", "ops_attention_set_algo", "ops_attention_status",
+    "ops_rope_build_pos", "ops_rearrange_plan", "ops_mat_mul_status", "ops_mat_mul_status_reset", "ops_attention_set_algo", "ops_attention_status",
+    "ops_attention_status_reset",
     "ops_attention_kv_cached_set_algo", "ops_sample_args_new", "ops_random_sample_build_indices",
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",

@@ -203,6 +203,18 @@ OPS_API int ops_attention_status(const ops_attention *op) {
   return v;
 }
 
+// Counterpart of ops_mat_mul_status_reset for the attention kernels: status word, the split-KV arrival counters and the
+// handle's own mat_mul.
+OPS_API int ops_attention_status_reset(ops_attention *op) {
+  if (!op) return fail(OPS_ARGS_NOT_SUPPORT, "null handle");
+  cudaSetDevice(op->base.device);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemset(op->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess && op->decode_tickets) e = cudaMemset(op->decode_tickets, 0, attention_decode_ticket_bytes());
+  if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention status reset: %s", cudaGetErrorString(e));
+  return ops_mat_mul_status_reset(op->mat_mul);
+}
+
 // attention::Operator::scheme (operators/src/attention/operator.rs:45-134): with static nh, seq, att,
 // dh the need is q_size + att_size (sub-operators need nothing), cut greedily to max_ws.
 OPS_API int ops_attention_scheme(ops_attention *op, const ops_attention_args *args, size_t max_ws, size_t *ws_out) {

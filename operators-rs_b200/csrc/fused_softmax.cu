@@ -60,7 +60,9 @@ __global__ void __launch_bounds__(256) softmax_f16_reg_kernel(const __grid_const
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         if (c0 + e < limit) {
-          const float ex = expf(__fsub_rn(to_f32(xv[i].h[e]), mx));
+          // special-function-unit exponential (relative error ~2^-22, far below the 16-bit rounding that follows): with
+          // libm-grade expf the register kernel is bound by instruction issue, not by HBM
+          const float ex = __expf(__fsub_rn(to_f32(xv[i].h[e]), mx));
           xv[i].h[e] = from_f32<E>(ex);
           sum += ex;
         }

@@ -70,9 +70,6 @@ struct GemmKernelArgs {
   int kb_per_slice;
   float *split_ws;         // [grid][128][BN] f32
   unsigned int *split_tickets;  // [split_r][4] arrivals per 32-row quarter, self-resetting
-  // Or (short K): the remainder tiles are cut along N into pieces `tail_w` columns wide (128 or 64), `tail_count` of them
-  // in all, dealt out round-robin after the whole tiles: the last wave then costs a fraction of a tile time per CTA.
-  int tail_w, tail_count;
 };
 
 // GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
@@ -117,30 +114,13 @@ struct GemmWork {
   long long t;
   int kb0, kb1;
   int slice;  // -1: whole tile
-  int sub;    // column piece of a remainder tile cut along N (0 when the tile is whole)
-  int bn;     // columns of this unit
 };
 
 // Work unit number `it` of this CTA: whole tiles strided by the grid, then at most one K-slice of a remainder tile.
-template <int BN>
 __device__ __forceinline__ bool gemm_work(const GemmKernelArgs &g, int it, int num_kb, GemmWork &w) {
   const long long t = blockIdx.x + (long long)it * gridDim.x;
-  w.sub = 0;
-  w.bn = BN;
   if (t < g.normal_tiles) {
     w.t = t;
-    w.kb0 = 0;
-    w.kb1 = num_kb;
-    w.slice = -1;
-    return true;
-  }
-  if (g.tail_w > 0) {
-    const long long u = (long long)blockIdx.x + (long long)(it - g.normal_iters) * gridDim.x;
-    if (it < g.normal_iters || u >= g.tail_count) return false;
-    const int per = BN / g.tail_w;
-    w.t = g.normal_tiles + u / per;
-    w.sub = (int)(u % per);
-    w.bn = g.tail_w;
     w.kb0 = 0;
     w.kb1 = num_kb;
     w.slice = -1;
@@ -159,8 +139,8 @@ __device__ __forceinline__ bool gemm_work(const GemmKernelArgs &g, int it, int n
 template <int BN> struct GemmCfg {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two >= 32
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int TMEM_COLS = BN == 128 ? 256 : 512;  // two accumulators of BN columns, rounded up to a power of two
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES + 256;            // after the barriers
   static constexpr int EPI_BYTES = 4 * 32 * GEMM_EPI_LD * 4;               // one 32 x 32 f32 transposition pad per epilogue warp
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
@@ -169,8 +149,7 @@ template <int BN> struct GemmCfg {
 template <int BN, bool FUSED>
 __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ GemmKernelArgs g,
-                            const __grid_constant__ FusedArArgs fa) {
+                            const __grid_constant__ GemmKernelArgs g, const __grid_constant__ FusedArArgs fa) {
   typedef GemmCfg<BN> Cfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -204,7 +183,6 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (g.tail_w > 0) tma_prefetch_desc(&tmap_b64);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -222,18 +200,17 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       GemmWork w;
-      for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
+      for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
         const long long t = w.t;
         const int b = (int)(t / tiles_per_batch);
         const long long r = t - (long long)b * tiles_per_batch;
         int tn, tm;
         tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
-        const int m0 = tm * GEMM_BM, n0 = tn * BN + w.sub * w.bn;
+        const int m0 = tm * GEMM_BM, n0 = tn * BN;
         const int ba = g.a_batched ? b : 0, bb = g.b_batched ? b : 0;
-        const int b_chunks = w.bn / 64;  // B travels in boxes of 64 rows (K-major) / 64 columns (MN-major)
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, g.status, 1))) break;
-          mbar_arrive_expect_tx(full_bar(stage), GEMM_A_BYTES + b_chunks * GEMM_CHUNK_BYTES);
+          mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES, sb = sa + GEMM_A_BYTES;
           const int k0 = kb * GEMM_BK;
           if (g.a_mn_major) {
@@ -243,11 +220,10 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
             tma_load_3d(sa, &tmap_a, full_bar(stage), k0, m0, ba);
           }
           if (g.b_mn_major) {
-            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
-          } else if (w.bn == BN) {
-            tma_load_3d(sb, &tmap_b, full_bar(stage), k0, n0, bb);  // one box BN rows tall
-          } else {  // a narrow piece: boxes of 64 rows (of 128 swizzled bytes), stacked they give the layout of one tall box
-            for (int c = 0; c < b_chunks; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b64, full_bar(stage), k0, n0 + 64 * c, bb);
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * GEMM_CHUNK_BYTES, &tmap_b, full_bar(stage), n0 + 64 * c, k0, bb);
+          } else {
+            tma_load_3d(sb, &tmap_b, full_bar(stage), k0, n0, bb);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -259,7 +235,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_full = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major, g.bf16);
+      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, g.a_mn_major, g.b_mn_major, g.bf16);
       const uint32_t a_lbo = g.a_mn_major ? GEMM_CHUNK_BYTES : 16, b_lbo = g.b_mn_major ? GEMM_CHUNK_BYTES : 16;
       const uint32_t a_kstep = g.a_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;  // bytes per UMMA_K
       const uint32_t b_kstep = g.b_mn_major ? GEMM_UMMA_K * 128 : GEMM_UMMA_K * 2;
@@ -269,11 +245,10 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       GemmWork w;
-      for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
+      for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
         if (!(ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, g.status, 2))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        const uint32_t idesc = w.bn == BN ? idesc_full : make_idesc_f16(GEMM_BM, w.bn, g.a_mn_major, g.b_mn_major, g.bf16);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(ok = mbar_wait(full_bar(stage), phase, g.status, 3))) break;
           tc_fence_after();
@@ -305,14 +280,14 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     uint32_t acc_phase = 0;
     bool ok = true;
     GemmWork w;
-    for (int it = 0; ok && gemm_work<BN>(g, it, num_kb, w); ++it) {
+    for (int it = 0; ok && gemm_work(g, it, num_kb, w); ++it) {
       const long long t = w.t;
       const int b = (int)(t / tiles_per_batch);
       const long long r = t - (long long)b * tiles_per_batch;
       int tn, tm;
       tile_coords(g.tiles_m, g.tiles_n, g.group_m, r, tm, tn);
       const int row = tm * GEMM_BM + quarter * 32 + lane;
-      const int n0 = tn * BN + w.sub * w.bn;
+      const int n0 = tn * BN;
       if (!(ok = mbar_wait(tmem_full_bar(acc), acc_phase, g.status, 4))) break;
       tc_fence_after();
       unsigned short *drow = g.d + (long long)b * g.d_bs + (long long)row * g.ldd;
@@ -352,7 +327,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < w.bn && finish; c += 32) {
+      for (int c = 0; c < BN && finish; c += 32) {
         uint32_t v[32];
         // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
         // (beta != 0) are requested before the tensor-memory load is waited for, four 128-bit loads in flight per lane.
@@ -777,7 +752,7 @@ static bool tma_ok(const void *ptr, usz outer, usz batch, isz outer_stride_el, i
 
 struct GemmState {
   int *status_dev = nullptr;
-  bool attr_set[4] = {false, false, false, false};
+  bool attr_set[5] = {false, false, false, false, false};
   // scratch of the remainder-wave K split, owned by the handle (launch never allocates): one 128 x 256 f32 partial per
   // CTA and the arrival counters, which every launch leaves at zero again.  One stream at a time per handle.
   float *split_ws = nullptr;
@@ -795,6 +770,21 @@ struct ops_mat_mul {
 
 namespace ops {
 
+// Time of a product with tiles `bn` columns wide, in units of one 128 x 256 tile: whole waves plus what the partial last
+// wave costs (a whole tile time, or a K slice of it plus the reduction when the K split below would take it).
+static double gemm_cost(const GemmProblem &p, int bn, long long sms, bool can_split) {
+  const long long tiles = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + bn - 1) / bn) * (long long)p.batch;
+  const long long rem = tiles % sms;
+  const int num_kb = (int)((p.k + GEMM_BK - 1) / GEMM_BK);
+  double tail = rem > 0 ? 1.0 : 0.0;
+  if (rem > 0 && can_split && sms <= GEMM_SPLIT_MAX_UNITS) {
+    int G = (int)std::min<long long>(sms / rem, GEMM_SPLIT_MAX_SLICES);
+    G = std::min(G, num_kb / 4);
+    if (G >= 2 && (long long)(G - 1) * num_kb >= 90LL * G) tail = 1.0 / G + 45.0 / num_kb;
+  }
+  return ((double)(tiles / sms) + tail) * bn / 256.0;
+}
+
 template <int BN>
 static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn, bool b_mn, usz eff_batch_a, usz eff_batch_b, float alpha,
                           float beta, cudaStream_t s, ops_comm *comm = nullptr) {
@@ -808,9 +798,6 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   if (b_mn) ok = encode_operand(&tb, bf, p.b_ptr, p.n, p.k, eff_batch_b, p.b.rs, p.b.stride, 64, GEMM_BK);
   else ok = encode_operand(&tb, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, BN);
   if (!ok) return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B");
-  CUtensorMap tb64 = tb;  // K-major B in boxes of 64 rows: what the narrow pieces of a remainder wave load (MN-major B already travels so)
-  if (!b_mn && !encode_operand(&tb64, bf, p.b_ptr, p.k, p.n, eff_batch_b, p.b.cs, p.b.stride, GEMM_BK, 64))
-    return fail(OPS_EXECUTION_FAILED, "mat_mul: cuTensorMapEncodeTiled failed for B (narrow boxes)");
 
   GemmKernelArgs g;
   g.d = (unsigned short *)p.d_ptr;
@@ -845,8 +832,6 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   g.kb_per_slice = 0;
   g.split_ws = op->st.split_ws;
   g.split_tickets = op->st.split_tickets;
-  g.tail_w = 0;
-  g.tail_count = 0;
   {
     const long long sms = op->base.sm_count;
     const long long rem = tiles % sms;
@@ -874,34 +859,11 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
         }
       }
     }
-    // Short K, a partial last wave and no K split: cut the remainder tiles along N instead.  A piece `w` columns wide costs
-    // w / BN of a tile time, times what narrow MMAs lose to shared-memory bandwidth (128 x 128: ~1.15, 128 x 64: ~1.45);
-    // taken when the remainder then costs clearly less than the whole tile time it costs otherwise.
-    if (BN == 256 && rem > 0 && g.split_g == 1 && tiles > sms && !comm) {
-      double best = 0.9;
-      int best_w = 0;
-      const int widths[2] = {128, 64};
-      const double penalty[2] = {1.15, 1.45};
-      for (int i = 0; i < 2; ++i) {
-        const long long pieces = rem * (BN / widths[i]);
-        const double cost = (double)((pieces + sms - 1) / sms) * widths[i] / BN * penalty[i];
-        if (cost < best) {
-          best = cost;
-          best_w = widths[i];
-        }
-      }
-      if (best_w) {
-        g.normal_tiles = tiles - rem;
-        g.normal_iters = (int)(g.normal_tiles / sms);
-        g.split_r = (int)rem;
-        g.tail_w = best_w;
-        g.tail_count = (int)(rem * (BN / best_w));
-      }
-    }
   }
   ops_mat_mul *mop = const_cast<ops_mat_mul *>(op);
   FusedArArgs fa;
   memset(&fa, 0, sizeof(fa));
+  if constexpr (BN != 192)  // (the fused kernel's cross-rank warps assume a power-of-two tile width)
   if (comm) {
     // fused all_reduce: whole tiles only (no K split), every CTA resident, flags for every (tile, quarter)
     g.normal_tiles = tiles;
@@ -918,17 +880,17 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
       if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
       mop->st.attr_set[slot] = true;
     }
-    gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tb64, g, fa);
+    gemm_f16_tcgen05_kernel<BN, true><<<grid, GEMM_FUSED_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
     return check_launch("mat_mul+all_reduce(tcgen05)");
   }
-  const unsigned launch_grid = (g.split_g > 1 || g.tail_w > 0) ? (unsigned)op->base.sm_count : grid;
-  const int slot = BN == 256 ? 0 : 1;
+  const unsigned launch_grid = g.split_g > 1 ? (unsigned)op->base.sm_count : grid;
+  const int slot = BN == 256 ? 0 : (BN == 128 ? 1 : 4);
   if (!mop->st.attr_set[slot]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     mop->st.attr_set[slot] = true;
   }
-  gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tb64, g, fa);
+  gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
   return check_launch("mat_mul(tcgen05)");
 }
 
@@ -978,8 +940,13 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
       // narrower tiles (and the K split above them) spread the weight stream over the machine
       const long long tiles256 = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + 255) / 256) * (long long)p.batch;
       const bool narrow = p.n <= 128 || (p.m <= 64 && tiles256 * 4 <= op->base.sm_count);
-      if (!narrow) return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
-      return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+      if (narrow) return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+      // 256- or 192-column tiles, whichever leaves the smaller bill once the partial last wave is counted: a wave costs a
+      // tile time whatever its fill, a tile time goes with the tile width, and the narrower tile moves ~11 % more operand
+      // bytes per flop (priced at 4 %)
+      if (gemm_cost(p, 192, op->base.sm_count, op->st.split_ws != nullptr) * 1.04 < gemm_cost(p, 256, op->base.sm_count, op->st.split_ws != nullptr))
+        return launch_tcgen05<192>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
+      return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
     }
   }
   if (comm) return fail(OPS_ARGS_NOT_SUPPORT, "mat_mul_all_reduce: f16 operands with k > 0 expected");
@@ -1043,6 +1010,18 @@ OPS_API int ops_mat_mul_status(const ops_mat_mul *op) {
   cudaSetDevice(op->base.device);
   if (cudaMemcpy(&v, op->st.status_dev, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   return v;
+}
+
+// After a bounded wait has run out the status word sticks and the arrival counters of the K split may be left non-zero:
+// this puts the handle back (synchronises the device first).  The output of the launch that timed out is undefined.
+OPS_API int ops_mat_mul_status_reset(ops_mat_mul *op) {
+  if (!op) return fail(OPS_ARGS_NOT_SUPPORT, "null handle");
+  cudaSetDevice(op->base.device);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemset(op->st.status_dev, 0, sizeof(int));
+  if (e == cudaSuccess && op->st.split_tickets) e = cudaMemset(op->st.split_tickets, 0, (size_t)GEMM_SPLIT_MAX_UNITS * 4 * sizeof(unsigned int));
+  if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul status reset: %s", cudaGetErrorString(e));
+  return OPS_OK;
 }
 
 OPS_API int ops_mat_mul_scheme(ops_mat_mul *op, const ops_mat_mul_args *args, size_t max_ws, size_t *ws_out) {

@@ -42,3 +42,21 @@ def test_missing_peer_times_out_cleanly(pkg, dev, algo_name):
     assert comm.p2p_status() == code
     del op
     comm.destroy()
+
+
+def test_status_reset_keeps_handles_usable(pkg, dev):
+    # the reset entry points clear the status word and the internal arrival counters; a handle that was never in trouble
+    # must come out of them unchanged (the time-out itself cannot be provoked for these kernels without faulting a GPU)
+    mm, att = pkg.MatMul(0), pkg.Attention(0)
+    a = torch.randn(300, 8192, device=dev).half()
+    b = (torch.randn(8192, 700, device=dev) * 0.01).half()
+    c = torch.empty(300, 700, dtype=torch.float16, device=dev)
+    mm.launch(pkg.MatMulArgs.of(c, 0.0, a, b, 1.0))
+    torch.cuda.synchronize()
+    first = c.clone()
+    mm.status_reset()
+    att.status_reset()
+    assert mm.status() == 0 and att.status() == 0
+    mm.launch(pkg.MatMulArgs.of(c, 0.0, a, b, 1.0))
+    torch.cuda.synchronize()
+    assert torch.equal(first, c) and mm.status() == 0
