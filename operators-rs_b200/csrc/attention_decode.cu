@@ -1,13 +1,22 @@
 // attention_decode.cu — attention for a handful of query tokens over a long KV range (decode steps of
 // attention_kv_cached: seq = 1..2 new tokens against a cache of hundreds or thousands of keys).
 //
-// Same function as attention::Operator (operators/src/attention/operator.rs:136-277) for shapes where the
-// tensor cores have nothing to chew on: group * seq <= 8 query rows per kv head.  The work is reading K and
-// V once — E * 2 * nkvh * att * dh bytes, HBM-bound — so the key range of every kv head is split over many
-// CTAs ("flash decoding"): each CTA streams its slice of K and V with 128-bit loads (half a warp per key
-// row), keeps a running max / sum / output per query row in registers, and parks (m, l, o) in a scratch
-// buffer owned by the operator handle; the last CTA of a kv head to finish merges the slices and writes o.
-// The q rows of one GQA group share every K/V load.
+// Same function as attention::Operator (operators/src/attention/operator.rs:136-277) for shapes where a 128-row
+// tcgen05 tile has nothing to chew on: group * seq <= 8 query rows per kv head.  The work is reading K and V once —
+// E * 2 * nkvh * att * dh bytes, HBM-bound — so the key range of every kv head is split over many CTAs ("flash
+// decoding"): a CTA takes 128 keys at a time, 16 per warp, every warp issuing all of its K and V loads (sixteen
+// 128-bit loads per lane, 64 KB in flight per CTA) before touching the first.  The arithmetic rides on warp-level
+// m16n8k16 MMAs so that the instruction stream stays far below the load stream:
+//   S[16 x 8 keys]   = Q[16 rows (8 used) x 16 dh] . K^T      A = q rows (registers), B = K straight from global
+//   O^T[16 dh x 8]   = V^T[16 dh x 16 keys] . P^T[16 keys x 8] B = the S fragments of two key tiles, exponentiated
+// Both contractions are invariant under a permutation of the contracted index, so a lane's 128-bit load of a K row
+// (8 consecutive dh) serves as the B fragments of two k-steps without any shuffle, and the V^T fragments are byte
+// permutes of four 128-bit loads of V rows.  Running max / sum per query row stay in registers; the 8 warps meet in
+// shared memory, the CTA parks (m, l, o) in a scratch buffer owned by the operator handle, and the last CTA of a kv
+// head to finish merges the splits and writes o.  The q rows of one GQA group share every K/V load.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "common.h"
 #include "device_utils.cuh"
 #include "internal.h"
@@ -16,7 +25,8 @@ namespace ops {
 
 constexpr int DEC_THREADS = 256;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int DEC_MAX_ROWS = 8;
+constexpr int DEC_MAX_ROWS = 8;           // the n extent of the MMA
+constexpr int DEC_KEYS_PER_STEP = DEC_WARPS * 16;
 constexpr int DEC_MAX_SPLITS = 64;
 constexpr int DEC_MAX_KV_HEADS = 1024;  // arrival counters in the handle's scratch
 
@@ -26,10 +36,9 @@ struct DecodeArgs {
   long long q_sh, q_ss, k_sh, k_ss, v_sh, v_ss, o_sh, o_ss;  // element strides: head, row (dh contiguous)
   int group, seq, att, rows;  // rows = group * seq
   int causal;
-  int bf16;                   // elements are bf16 (else f16)
   int splits, keys_per_split;
   float scale_log2;
-  float *partial;          // [nkvh][splits][rows][DH + 2]
+  float *partial;          // [nkvh][splits][8][DH + 2]
   unsigned int *tickets;   // [nkvh], self-resetting
 };
 
@@ -38,150 +47,205 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float dec_to_f32(unsigned short b, int bf) {
-  return bf ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+template <bool BF>
+__device__ __forceinline__ unsigned short dec_from_f32(float v) {
+  return BF ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
 }
-__device__ __forceinline__ unsigned short dec_from_f32(float v, int bf) {
-  return bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+template <bool BF>
+__device__ __forceinline__ uint32_t dec_pack(float lo, float hi) {
+  if (BF) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&t);
+  }
+  __half2 t = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&t);
 }
+// d += a . b, one warp, m16n8k16, f32 accumulate
+template <bool BF>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (BF)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-// DH = 64 or 128.  A key row is DH/8 lanes wide (8 elements per lane); LPK = lanes per key.
-template <int DH, int ROWS>
-__global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __grid_constant__ DecodeArgs a) {
-  constexpr int LPK = DH / 8;              // 16 or 8 lanes per key row
-  constexpr int KPW = 32 / LPK;            // keys per warp per step
-  constexpr int GROUPS = DEC_THREADS / LPK;  // key rows in flight per CTA step
-  __shared__ float q_s[ROWS][DH];
+// DH = 64 or 128.  Lane = (g, c) = (lane / 4, lane % 4), the row / column-pair coordinates of the MMA fragments.
+//   QK^T:  A[m = q row][k]: a0 = Q[g][slots 2c,2c+1], a2 = Q[g][slots 2c+8,2c+9]; rows 8..15 (a1, a3) are zero.
+//          B[k][n = key g of the tile]: b0, b1 = the same slots of K[key g].  Slot s of k-step t is column
+//          32*(t/2) + 8c + 4*(t%2) + {0,1 | 2,3}: the four words of ONE 128-bit load of K[key g][32*(t/2) + 8c ..] are
+//          (b0, b1) of k-step t = even and (b0, b1) of k-step t + 1.
+//          C: c0, c1 = S[row g][keys 2c, 2c+1 of the tile].
+//   PV:    B[k = key][n = row g] = P[g][keys 2c,2c+1 | 2c+8,2c+9] = the exponentiated c0, c1 of key tiles 0 and 1.
+//          A[m][k = key]: m-tile i of half hh, m = g -> dh 64hh + 8g + 2i, m = g + 8 -> dh 64hh + 8g + 2i + 1: word i
+//          of the 128-bit loads V[key][64hh + 8g ..] of keys 2c, 2c+1 (a0 = low halves, a1 = high halves) and of keys
+//          2c+8, 2c+9 (a2, a3).
+//          C: c0, c1 = O[rows 2c, 2c+1][dh of m = g], c2, c3 = the same rows at dh + 1.
+template <int DH, bool BF>
+__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const __grid_constant__ DecodeArgs a) {
+  constexpr int ROWS = DEC_MAX_ROWS;
+  constexpr int CH = DH / 32;   // 128-bit loads per K row per lane
+  constexpr int HH = DH / 64;   // 64-wide halves of a V row
+  __shared__ __align__(16) unsigned short q_s[ROWS][DH];
   __shared__ float red_m[DEC_WARPS][ROWS], red_l[DEC_WARPS][ROWS];
-  __shared__ float red_o[DEC_WARPS][ROWS][DH];  // 32 KB at most
+  __shared__ __align__(16) float red_o[DEC_WARPS][ROWS][DH];  // 32 KB at most
   __shared__ unsigned int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane / LPK, li = lane % LPK;  // which key of the warp step, which 8-column slice of dh
+  const int g = lane >> 2, c = lane & 3;
   const int off = a.att - a.seq;
-  const int bf = a.bf16;
 
-  // q rows of this kv head, pre-scaled into the exp2 domain
+  const int k_begin = split * a.keys_per_split, k_end = min(a.att, k_begin + a.keys_per_split);
+  const unsigned short *kbase = a.k + (long long)kvh * a.k_sh + c * 8;
+  const unsigned short *vbase = a.v + (long long)kvh * a.v_sh + g * 8;
+
+  uint4 kq[2][CH], vq[HH][4];
+  // keys kb .. kb+15 of this warp; rows past k_end re-read the last row and are masked
+  auto issue_k = [&](int kb) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int key = min(kb + j * 8 + g, k_end - 1);
+      const unsigned short *kr = kbase + (long long)key * a.k_ss;
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch) kq[j][ch] = __ldcs(reinterpret_cast<const uint4 *>(kr + ch * 32));
+    }
+  };
+  auto issue_v = [&](int kb) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int key = min(kb + 2 * c + (j & 1) + (j >> 1) * 8, k_end - 1);
+      const unsigned short *vr = vbase + (long long)key * a.v_ss;
+#pragma unroll
+      for (int hh = 0; hh < HH; ++hh) vq[hh][j] = __ldcs(reinterpret_cast<const uint4 *>(vr + hh * 64));
+    }
+  };
+  int kb = k_begin + warp * 16;
+  if (kb < k_end) {  // in flight while q is staged
+    issue_k(kb);
+    issue_v(kb);
+  }
+
   for (int i = threadIdx.x; i < ROWS * DH; i += DEC_THREADS) {
-    const int r = i / DH, c = i - r * DH;
-    float val = 0.f;
+    const int r = i / DH, col = i - r * DH;
+    unsigned short val = 0;
     if (r < a.rows) {
       const int gi = r / a.seq, si = r - gi * a.seq;
-      val = dec_to_f32(a.q[(long long)(kvh * a.group + gi) * a.q_sh + (long long)si * a.q_ss + c], bf) * a.scale_log2;
+      val = a.q[(long long)(kvh * a.group + gi) * a.q_sh + (long long)si * a.q_ss + col];
     }
-    q_s[r][c] = val;
+    q_s[r][col] = val;
   }
   __syncthreads();
-  float qr[ROWS][8];
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) qr[r][e] = q_s[r][li * 8 + e];
-  int lim[ROWS];
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    const int si = r % a.seq;
-    lim[r] = r < a.rows ? (a.causal ? min(a.att - 1, off + si) : a.att - 1) : -1;
-  }
+  // q fragments are re-read from shared memory at every use (volatile: hoisting them would cost 16 registers that the
+  // loads in flight need)
+  const volatile uint4 *q_frag = reinterpret_cast<const volatile uint4 *>(&q_s[g][c * 8]);
+  const int lim = g < a.rows ? (a.causal ? min(a.att - 1, off + g % a.seq) : a.att - 1) : -1;  // last visible key of row g
 
-  float m[ROWS], l[ROWS], o[ROWS][8];
+  float m = -INFINITY, l = 0.f;   // row g: m is common to the four lanes of a row, l is this lane's share
+  float o[HH][4][4];
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    m[r] = -INFINITY;
-    l[r] = 0.f;
+  for (int hh = 0; hh < HH; ++hh)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[r][e] = 0.f;
-  }
-  const int k_begin = split * a.keys_per_split, k_end = min(a.att, k_begin + a.keys_per_split);
-  const unsigned short *kbase = a.k + (long long)kvh * a.k_sh + li * 8;
-  const unsigned short *vbase = a.v + (long long)kvh * a.v_sh + li * 8;
-  // Keys are taken eight steps at a time: the sixteen 128-bit loads of a batch (K and V of eight key rows per lane) are
-  // all issued before the first is used, so a CTA pays the DRAM latency once per 128 keys, not once per 16.
-  constexpr int UN = 8;
-  for (int kb0 = k_begin + warp * KPW; kb0 < k_end; kb0 += GROUPS * UN) {  // warp-uniform trip count: the shuffles need every lane
-    uint4 kq[UN], vq[UN];
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int key = kb0 + u * GROUPS + sub;
-      const int kload = key < k_end ? key : k_end - 1;
-      kq[u] = __ldcs(reinterpret_cast<const uint4 *>(kbase + (long long)kload * a.k_ss));
-      vq[u] = __ldcs(reinterpret_cast<const uint4 *>(vbase + (long long)kload * a.v_ss));
-    }
+      for (int e = 0; e < 4; ++e) o[hh][i][e] = 0.f;
+
+  for (; kb < k_end; kb += DEC_KEYS_PER_STEP) {  // warp-uniform
+    float s[2][4];
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int key = kb0 + u * GROUPS + sub;
-      const bool valid = key < k_end;
-      Vec8<unsigned short> kk, vv;
-      kk.u = kq[u];
-      vv.u = vq[u];
-      float kf[8], vf[8];
+    for (int j = 0; j < 2; ++j) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        kf[e] = dec_to_f32(kk.h[e], bf);
-        vf[e] = dec_to_f32(vv.h[e], bf);
-      }
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) s = fmaf(qr[r][e], kf[e], s);
-#pragma unroll
-        for (int d = LPK / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // stays inside the LPK-lane group
-        if (valid && key <= lim[r]) {
-          const float m_new = fmaxf(m[r], s);
-          const float alpha = ex2f(m[r] - m_new), p = ex2f(s - m_new);
-          l[r] = fmaf(l[r], alpha, p);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[r][e] = fmaf(o[r][e], alpha, p * vf[e]);
-          m[r] = m_new;
-        }
+      for (int ch = 0; ch < CH; ++ch) {
+        const uint32_t q0 = q_frag[ch * 4].x, q1 = q_frag[ch * 4].y, q2 = q_frag[ch * 4].z, q3 = q_frag[ch * 4].w;
+        mma16816<BF>(s[j], q0, 0u, q1, 0u, kq[j][ch].x, kq[j][ch].y);
+        mma16816<BF>(s[j], q2, 0u, q3, 0u, kq[j][ch].z, kq[j][ch].w);
       }
     }
+    const bool more = kb + DEC_KEYS_PER_STEP < k_end;
+    if (more) issue_k(kb + DEC_KEYS_PER_STEP);  // the K registers are free again
+    // scores of row g at keys kb + 8j + 2c + {0,1}
+    float sv[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = kb + j * 8 + 2 * c + e;
+        const float x = (key < k_end && key <= lim) ? s[j][e] * a.scale_log2 : -INFINITY;
+        sv[j * 2 + e] = x;
+        mx = fmaxf(mx, x);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = ex2f(m - m_use);
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) p[e] = ex2f(sv[e] - m_use);
+    l = fmaf(l, alpha, (p[0] + p[1]) + (p[2] + p[3]));
+    m = m_new;
+    const uint32_t pb0 = dec_pack<BF>(p[0], p[1]), pb1 = dec_pack<BF>(p[2], p[3]);
+    // the accumulators of this lane belong to rows 2c and 2c + 1
+    const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * c) << 2), al1 = __shfl_sync(0xffffffffu, alpha, (2 * c + 1) << 2);
+#pragma unroll
+    for (int hh = 0; hh < HH; ++hh)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[hh][i][0] *= al0;
+        o[hh][i][1] *= al1;
+        o[hh][i][2] *= al0;
+        o[hh][i][3] *= al1;
+        const uint32_t w0 = word_of(vq[hh][0], i), w1 = word_of(vq[hh][1], i), w2 = word_of(vq[hh][2], i), w3 = word_of(vq[hh][3], i);
+        mma16816<BF>(o[hh][i], __byte_perm(w0, w1, 0x5410), __byte_perm(w0, w1, 0x7632), __byte_perm(w2, w3, 0x5410),
+                     __byte_perm(w2, w3, 0x7632), pb0, pb1);
+      }
+    if (more) issue_v(kb + DEC_KEYS_PER_STEP);
   }
 
-  // merge the key groups of one warp with shuffles (common max, rescaled sums), then the warps through shared memory
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    float mm = m[r];
-#pragma unroll
-    for (int d = LPK; d < 32; d <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, d));
-    const float sc = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - mm);
-    float lr = l[r] * sc;
-#pragma unroll
-    for (int d = LPK; d < 32; d <<= 1) lr += __shfl_xor_sync(0xffffffffu, lr, d);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float ov = o[r][e] * sc;
-#pragma unroll
-      for (int d = LPK; d < 32; d <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, d);
-      o[r][e] = ov;
-    }
-    m[r] = mm;
-    l[r] = lr;
-    if (lane == 0) red_m[warp][r] = mm;
-  }
+  // the 8 warps meet in shared memory: common max per row, rescaled sums
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (c == 0) red_m[warp][g] = m;
   __syncthreads();
-#pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
+  {
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, red_m[w][r]);
-    const float sc = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - mm);
-    if (lane == 0) red_l[warp][r] = l[r] * sc;
-    if (sub == 0) {
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, red_m[w][g]);
+    if (c == 0) red_l[warp][g] = m == -INFINITY ? 0.f : l * ex2f(m - mm);
+    float sc[2];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) red_o[warp][r][li * 8 + e] = o[r][e] * sc;
+    for (int e = 0; e < 2; ++e) {
+      const int r = 2 * c + e;
+      float mr = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) mr = fmaxf(mr, red_m[w][r]);
+      const float mw = red_m[warp][r];
+      sc[e] = mw == -INFINITY ? 0.f : ex2f(mw - mr);
     }
+#pragma unroll
+    for (int hh = 0; hh < HH; ++hh)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = hh * 64 + g * 8 + 2 * i;
+        *reinterpret_cast<float2 *>(&red_o[warp][2 * c][col]) = make_float2(o[hh][i][0] * sc[0], o[hh][i][2] * sc[0]);
+        *reinterpret_cast<float2 *>(&red_o[warp][2 * c + 1][col]) = make_float2(o[hh][i][1] * sc[1], o[hh][i][3] * sc[1]);
+      }
   }
   __syncthreads();
   // park (m, l, o) of this split
   float *part = a.partial + (((long long)kvh * a.splits + split) * ROWS) * (DH + 2);
-  for (int i = threadIdx.x; i < ROWS * DH; i += DEC_THREADS) {
-    const int r = i / DH, c = i - r * DH;
+  for (int i = threadIdx.x; i < a.rows * DH; i += DEC_THREADS) {
+    const int r = i / DH, col = i - r * DH;
     float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) acc += red_o[w][r][c];
-    part[r * (DH + 2) + 2 + c] = acc;
+    for (int w = 0; w < DEC_WARPS; ++w) acc += red_o[w][r][col];
+    part[r * (DH + 2) + 2 + col] = acc;
   }
   if (threadIdx.x < ROWS) {
     const int r = threadIdx.x;
@@ -229,27 +293,27 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const __g
   }
   __syncthreads();
   for (int i = threadIdx.x; i < a.rows * DH; i += DEC_THREADS) {
-    const int r = i / DH, c = i - r * DH;
-    const float *col = pall + (long long)r * (DH + 2) + 2 + c;
+    const int r = i / DH, col = i - r * DH;
+    const float *colp = pall + (long long)r * (DH + 2) + 2 + col;
     float num = 0.f;
     int sp = 0;
     for (; sp + 16 <= a.splits; sp += 16) {  // sixteen loads in flight
       float v[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
+      for (int u = 0; u < 16; ++u) v[u] = __ldcg(colp + (long long)(sp + u) * ROWS * (DH + 2));
 #pragma unroll
       for (int u = 0; u < 16; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
     }
     for (; sp + 4 <= a.splits; sp += 4) {
       float v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = __ldcg(col + (long long)(sp + u) * ROWS * (DH + 2));
+      for (int u = 0; u < 4; ++u) v[u] = __ldcg(colp + (long long)(sp + u) * ROWS * (DH + 2));
 #pragma unroll
       for (int u = 0; u < 4; ++u) num = fmaf(v[u], w_s[r][sp + u], num);
     }
-    for (; sp < a.splits; ++sp) num = fmaf(__ldcg(col + (long long)sp * ROWS * (DH + 2)), w_s[r][sp], num);
+    for (; sp < a.splits; ++sp) num = fmaf(__ldcg(colp + (long long)sp * ROWS * (DH + 2)), w_s[r][sp], num);
     const int gi = r / a.seq, si = r - gi * a.seq;
-    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + c] = dec_from_f32(num / den_s[r], bf);
+    a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + col] = dec_from_f32<BF>(num / den_s[r]);
   }
 }
 
@@ -281,7 +345,7 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.k = (const unsigned short *)a->k_base;
   g.v = (const unsigned short *)a->v_base;
   g.o = (unsigned short *)a->o_base;
-  g.bf16 = a->q_layout.dt == OPS_DT_BF16;
+  const bool bf16 = a->q_layout.dt == OPS_DT_BF16;
   g.q_sh = sq[0] / 2; g.q_ss = sq[1] / 2;
   g.k_sh = sk[0] / 2; g.k_ss = sk[1] / 2;
   g.v_sh = sv[0] / 2; g.v_ss = sv[1] / 2;
@@ -291,31 +355,30 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.att = (int)att;
   g.rows = g.group * g.seq;
   g.causal = a->mask == OPS_MASK_CAUSAL;
-  const int row_slots = g.rows <= 4 ? 4 : 8;
-  // about one 256-thread CTA per SM, at least 256 keys each (16 steps of 16 key rows), and partials that fit the scratch
-  // buffer; few splits keep the merge by the last CTA of a kv head short
-  usz splits = ((usz)base.sm_count + nkvh - 1) / nkvh;
-  splits = std::min<usz>(splits, (att + 255) / 256);
+  // about two 256-thread CTAs per SM (both resident: every load of the launch is in flight at once), whole 128-key
+  // steps per CTA, and partials that fit the scratch buffer; few splits keep the merge by the last CTA of a kv head short
+  usz splits = (2 * (usz)base.sm_count + nkvh - 1) / nkvh;
+  splits = std::min<usz>(splits, (att + DEC_KEYS_PER_STEP - 1) / DEC_KEYS_PER_STEP);
   splits = std::min<usz>(splits, DEC_MAX_SPLITS);
-  const usz per_split = nkvh * (usz)row_slots * (dh + 2) * sizeof(float);
+  const usz per_split = nkvh * (usz)DEC_MAX_ROWS * (dh + 2) * sizeof(float);
   splits = std::min<usz>(splits, attention_decode_scratch_bytes() / per_split);
   if (splits < 1) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: too many kv heads for the decode scratch buffer");
-  g.splits = (int)splits;
-  g.keys_per_split = (int)((att + splits - 1) / splits);
+  const usz steps = (att + DEC_KEYS_PER_STEP - 1) / DEC_KEYS_PER_STEP;
+  g.keys_per_split = (int)((steps + splits - 1) / splits) * DEC_KEYS_PER_STEP;
   g.splits = (int)((att + g.keys_per_split - 1) / g.keys_per_split);
   const float inv_sqrt = 1.f / sqrtf((float)dh);
-  const float alpha = g.bf16 ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
+  const float alpha = bf16 ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
   g.scale_log2 = alpha * 1.4426950408889634f;
   g.partial = scratch;
   g.tickets = tickets;
   cudaSetDevice(base.device);
   dim3 grid((unsigned)nkvh, (unsigned)g.splits);
   if (dh == 128) {
-    if (row_slots == 4) attention_decode_kernel<128, 4><<<grid, DEC_THREADS, 0, s>>>(g);
-    else attention_decode_kernel<128, 8><<<grid, DEC_THREADS, 0, s>>>(g);
+    if (bf16) attention_decode_kernel<128, true><<<grid, DEC_THREADS, 0, s>>>(g);
+    else attention_decode_kernel<128, false><<<grid, DEC_THREADS, 0, s>>>(g);
   } else {
-    if (row_slots == 4) attention_decode_kernel<64, 4><<<grid, DEC_THREADS, 0, s>>>(g);
-    else attention_decode_kernel<64, 8><<<grid, DEC_THREADS, 0, s>>>(g);
+    if (bf16) attention_decode_kernel<64, true><<<grid, DEC_THREADS, 0, s>>>(g);
+    else attention_decode_kernel<64, false><<<grid, DEC_THREADS, 0, s>>>(g);
   }
   return check_launch("attention(decode)");
 }

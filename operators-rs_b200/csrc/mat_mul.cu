@@ -47,6 +47,7 @@ constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
 constexpr int GEMM_SPLIT_MAX_UNITS = 160;          // CTAs that may hold a K-slice partial (>= SM count)
 constexpr int GEMM_SPLIT_MAX_SLICES = 8;
+constexpr int GEMM_SPLIT_COST_KB = 16;             // what cutting a remainder tile along K costs, in k-blocks of tile time
 constexpr int GEMM_EPI_LD = 36;                    // padded row length (words) of the epilogue's shared-memory pad: conflict-free both ways
 
 struct GemmKernelArgs {
@@ -63,13 +64,14 @@ struct GemmKernelArgs {
   int group_m;           // tile raster: m-tiles walked in groups of this many (>= tiles_m: plain m-fastest order)
   int *status;
   // Remainder wave: the tiles beyond the last full wave are cut along K into `split_g` slices, one (tile, slice) unit
-  // per CTA; partial sums meet in `split_ws` (f32) and the last slice to arrive finishes the tile.
+  // per CTA; partial sums meet in `split_ws` (f32); once all slices of a tile are there, slice s finishes the 32-column
+  // chunks j with j mod split_g == s (a reduce-scatter: every slice reads one tile's worth of partials, none reads G).
   long long normal_tiles;  // tiles computed whole (a multiple of the grid when split_g > 1)
   int normal_iters;        // normal_tiles / grid
   int split_r, split_g;    // remainder tiles, slices per tile (1 = no split)
   int kb_per_slice;
-  float *split_ws;         // [grid][128][BN] f32
-  unsigned int *split_tickets;  // [split_r][4] arrivals per 32-row quarter, self-resetting
+  float *split_ws;         // [grid][4 quarters][BN/32 chunks][8][32 lanes] float4: a lane's 128-bit stores of one step are contiguous
+  unsigned int *split_tickets;  // [split_r][4][2] arrivals and departures per 32-row quarter, self-resetting
 };
 
 // GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
@@ -139,7 +141,7 @@ __device__ __forceinline__ bool gemm_work(const GemmKernelArgs &g, int it, int n
 template <int BN> struct GemmCfg {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
   static constexpr int TMEM_COLS = BN == 128 ? 256 : 512;  // two accumulators of BN columns, rounded up to a power of two
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES + 256;            // after the barriers
   static constexpr int EPI_BYTES = 4 * 32 * GEMM_EPI_LD * 4;               // one 32 x 32 f32 transposition pad per epilogue warp
@@ -295,13 +297,16 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
       unsigned short *wrow = drow;
       if constexpr (FUSED) wrow = reinterpret_cast<unsigned short *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa_epoch & 1u)) + (long long)row * g.n;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-      // K-slice of a remainder tile: park the f32 partial; the last of the tile's slices to arrive (per 32-row quarter)
-      // adds all of them up in slice order and takes over as if it had computed the whole tile
+      // K-slice of a remainder tile: park the f32 partial, wait (bounded) until every slice of the tile has parked its
+      // own, then finish this slice's share of the column chunks from the sum of all of them, taken in slice order
+      // whoever does the adding.  Every CTA of the grid is resident (cooperative launch), so the wait cannot starve.
       bool finish = true;
-      float *part_row = nullptr;
+      const float4 *part_q = nullptr;  // this quarter's partial of slice 0 of the tile
+      unsigned int *ticket = nullptr;
       if (!FUSED && w.slice >= 0) {
         const int tile_r = (int)(t - g.normal_tiles);
-        part_row = g.split_ws + ((long long)blockIdx.x * GEMM_BM + quarter * 32 + lane) * BN;
+        constexpr int QUARTER_F4 = (BN / 32) * 8 * 32;
+        float4 *mine = reinterpret_cast<float4 *>(g.split_ws) + ((long long)blockIdx.x * 4 + quarter) * QUARTER_F4 + lane;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t v[32];
@@ -310,24 +315,32 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           if (row < g.m) {  // rows outside C are never read back
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<uint4 *>(part_row + c + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              mine[((c >> 5) * 8 + q) * 32] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                                           __uint_as_float(v[4 * q + 3]));
           }
         }
         __threadfence();
         __syncwarp();
-        unsigned int ticket = 0;
-        if (lane == 0) ticket = atomicAdd(&g.split_tickets[tile_r * 4 + quarter], 1u);
-        ticket = __shfl_sync(0xffffffffu, ticket, 0);
-        finish = ticket == (unsigned)(g.split_g - 1);
-        if (finish) {
-          __threadfence();
-          if (lane == 0) g.split_tickets[tile_r * 4 + quarter] = 0;  // ready for the next launch
-          // first slice of this tile lives in unit tile_r * split_g
-          part_row = g.split_ws + (((long long)tile_r * g.split_g) * GEMM_BM + quarter * 32 + lane) * BN;
+        ticket = g.split_tickets + (tile_r * 4 + quarter) * 2;
+        int there = 1;
+        if (lane == 0) {
+          atomicAdd(ticket, 1u);
+          const unsigned long long t0 = globaltimer_ns();
+          while (ld_acquire_gpu(ticket) < (unsigned)g.split_g) {
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+              atomicCAS(g.status, 0, 6);
+              there = 0;
+              break;
+            }
+          }
         }
+        there = __shfl_sync(0xffffffffu, there, 0);
+        finish = ok = there != 0;
+        part_q = reinterpret_cast<const float4 *>(g.split_ws) + (((long long)tile_r * g.split_g) * 4 + quarter) * QUARTER_F4 + lane;
       }
 #pragma unroll 1
       for (int c = 0; c < BN && finish; c += 32) {
+        if (!FUSED && w.slice >= 0 && (c >> 5) % g.split_g != w.slice) continue;  // another slice's chunk (warp-uniform)
         uint32_t v[32];
         // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
         // (beta != 0) are requested before the tensor-memory load is waited for, four 128-bit loads in flight per lane.
@@ -349,35 +362,35 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
           tmem_wait_ld();
         } else {
           float sum[32];
-          if (row >= g.m) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) sum[e] = 0.f;
-          } else if (g.split_g == 2) {  // the common case: both slices' 16 loads are in flight together
-            float4 f0[8], f1[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              f0[q] = __ldcg(reinterpret_cast<const float4 *>(part_row + c) + q);
-              f1[q] = __ldcg(reinterpret_cast<const float4 *>(part_row + (long long)GEMM_BM * BN + c) + q);
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              sum[4 * q] = f0[q].x + f1[q].x;
-              sum[4 * q + 1] = f0[q].y + f1[q].y;
-              sum[4 * q + 2] = f0[q].z + f1[q].z;
-              sum[4 * q + 3] = f0[q].w + f1[q].w;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) sum[e] = 0.f;
-            for (int sl = 0; sl < g.split_g; ++sl) {
-              const float *src = part_row + (long long)sl * GEMM_BM * BN + c;
+          for (int e = 0; e < 32; ++e) sum[e] = 0.f;
+          if (row < g.m) {
+            constexpr long long UNIT_F4 = 4LL * (BN / 32) * 8 * 32;  // one slice further
+            const float4 *src = part_q + (c >> 5) * 8 * 32;
+            // two slices at a time: sixteen 128-bit loads in flight, added in slice order
+            for (int sl = 0; sl < g.split_g; sl += 2) {
+              const bool two = sl + 1 < g.split_g;
+              float4 f0[8], f1[8];
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
-                const float4 f = __ldcg(reinterpret_cast<const float4 *>(src) + q);
-                sum[4 * q] += f.x;
-                sum[4 * q + 1] += f.y;
-                sum[4 * q + 2] += f.z;
-                sum[4 * q + 3] += f.w;
+                f0[q] = __ldcg(src + sl * UNIT_F4 + q * 32);
+                if (two) f1[q] = __ldcg(src + (sl + 1) * UNIT_F4 + q * 32);
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                sum[4 * q] += f0[q].x;
+                sum[4 * q + 1] += f0[q].y;
+                sum[4 * q + 2] += f0[q].z;
+                sum[4 * q + 3] += f0[q].w;
+              }
+              if (two) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  sum[4 * q] += f1[q].x;
+                  sum[4 * q + 1] += f1[q].y;
+                  sum[4 * q + 2] += f1[q].z;
+                  sum[4 * q + 3] += f1[q].w;
+                }
               }
             }
           }
@@ -442,6 +455,13 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
               }
             }
           }
+        }
+      }
+      if (!FUSED && ticket != nullptr && finish && lane == 0) {
+        // the last slice to leave puts both counters back to zero for the next launch (every slice has seen the arrivals)
+        if (atomicAdd(ticket + 1, 1u) == (unsigned)(g.split_g - 1)) {
+          ticket[0] = 0;
+          ticket[1] = 0;
         }
       }
       tc_fence_before();
@@ -752,7 +772,7 @@ static bool tma_ok(const void *ptr, usz outer, usz batch, isz outer_stride_el, i
 
 struct GemmState {
   int *status_dev = nullptr;
-  bool attr_set[5] = {false, false, false, false, false};
+  bool attr_set[4] = {false, false, false, false};
   // scratch of the remainder-wave K split, owned by the handle (launch never allocates): one 128 x 256 f32 partial per
   // CTA and the arrival counters, which every launch leaves at zero again.  One stream at a time per handle.
   float *split_ws = nullptr;
@@ -769,21 +789,6 @@ struct ops_mat_mul {
 };
 
 namespace ops {
-
-// Time of a product with tiles `bn` columns wide, in units of one 128 x 256 tile: whole waves plus what the partial last
-// wave costs (a whole tile time, or a K slice of it plus the reduction when the K split below would take it).
-static double gemm_cost(const GemmProblem &p, int bn, long long sms, bool can_split) {
-  const long long tiles = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + bn - 1) / bn) * (long long)p.batch;
-  const long long rem = tiles % sms;
-  const int num_kb = (int)((p.k + GEMM_BK - 1) / GEMM_BK);
-  double tail = rem > 0 ? 1.0 : 0.0;
-  if (rem > 0 && can_split && sms <= GEMM_SPLIT_MAX_UNITS) {
-    int G = (int)std::min<long long>(sms / rem, GEMM_SPLIT_MAX_SLICES);
-    G = std::min(G, num_kb / 4);
-    if (G >= 2 && (long long)(G - 1) * num_kb >= 90LL * G) tail = 1.0 / G + 45.0 / num_kb;
-  }
-  return ((double)(tiles / sms) + tail) * bn / 256.0;
-}
 
 template <int BN>
 static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn, bool b_mn, usz eff_batch_a, usz eff_batch_b, float alpha,
@@ -839,14 +844,14 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
     if (rem > 0 && op->st.split_ws && sms <= GEMM_SPLIT_MAX_UNITS) {
       int G = (int)std::min<long long>(sms / rem, GEMM_SPLIT_MAX_SLICES);
       G = std::min(G, num_kb / 4);  // at least four k-blocks per slice
-      // Splitting costs a fixed ~20 us (f32 partials through L2, a second pipeline fill), about 45 k-blocks of tile time;
-      // it pays when the tile time it removes from the tail, (1 - 1/G) * num_kb k-blocks, is clearly larger.
-      // Measured on the config-3 layer: +9 % on the K = 14336 down projection, a loss on the K = 4096 ones.
+      // Splitting costs a few microseconds (one tile of f32 partials out to L2 and one back per CTA, a second pipeline
+      // fill), priced at GEMM_SPLIT_COST_KB k-blocks of tile time; it pays when the tile time it removes from the tail,
+      // (1 - 1/G) * num_kb k-blocks, is larger.
       // A machine that is less than half full (skinny decode-time products: a few tiles, each streaming a whole weight
       // panel) is a different case: there the split is what puts every SM on the HBM stream, and the partials are small
       // (rows beyond m are neither written nor read).
       const bool underfilled = tiles * 2 <= sms && p.m <= 64;
-      if (G >= 2 && !underfilled && (long long)(G - 1) * num_kb < 90LL * G) G = 1;
+      if (G >= 2 && !underfilled && (long long)(G - 1) * num_kb < (long long)GEMM_SPLIT_COST_KB * G) G = 1;
       if (G >= 2) {
         const int per = (num_kb + G - 1) / G;
         G = (num_kb + per - 1) / per;  // drop empty slices
@@ -863,7 +868,6 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
   ops_mat_mul *mop = const_cast<ops_mat_mul *>(op);
   FusedArArgs fa;
   memset(&fa, 0, sizeof(fa));
-  if constexpr (BN != 192)  // (the fused kernel's cross-rank warps assume a power-of-two tile width)
   if (comm) {
     // fused all_reduce: whole tiles only (no K split), every CTA resident, flags for every (tile, quarter)
     g.normal_tiles = tiles;
@@ -884,11 +888,19 @@ static int launch_tcgen05(const ops_mat_mul *op, const GemmProblem &p, bool a_mn
     return check_launch("mat_mul+all_reduce(tcgen05)");
   }
   const unsigned launch_grid = g.split_g > 1 ? (unsigned)op->base.sm_count : grid;
-  const int slot = BN == 256 ? 0 : (BN == 128 ? 1 : 4);
+  const int slot = BN == 256 ? 0 : 1;
   if (!mop->st.attr_set[slot]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     mop->st.attr_set[slot] = true;
+  }
+  if (g.split_g > 1) {
+    // the slices of a tile wait for one another: a cooperative launch makes the whole grid resident before any CTA runs
+    void *params[] = {(void *)&ta, (void *)&tb, (void *)&g, (void *)&fa};
+    cudaError_t e = cudaLaunchCooperativeKernel((const void *)gemm_f16_tcgen05_kernel<BN, false>, dim3(launch_grid), dim3(GEMM_THREADS), params,
+                                                (size_t)Cfg::SMEM_BYTES, s);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul: cooperative launch failed: %s", cudaGetErrorString(e));
+    return check_launch("mat_mul(tcgen05, K-split remainder)");
   }
   gemm_f16_tcgen05_kernel<BN, false><<<launch_grid, GEMM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, g, fa);
   return check_launch("mat_mul(tcgen05)");
@@ -941,11 +953,6 @@ int mat_mul_enqueue_impl(const ops_mat_mul *op, const ops_mat_mul_args *args, cu
       const long long tiles256 = (long long)((p.m + GEMM_BM - 1) / GEMM_BM) * (long long)((p.n + 255) / 256) * (long long)p.batch;
       const bool narrow = p.n <= 128 || (p.m <= 64 && tiles256 * 4 <= op->base.sm_count);
       if (narrow) return launch_tcgen05<128>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
-      // 256- or 192-column tiles, whichever leaves the smaller bill once the partial last wave is counted: a wave costs a
-      // tile time whatever its fill, a tile time goes with the tile width, and the narrower tile moves ~11 % more operand
-      // bytes per flop (priced at 4 %)
-      if (gemm_cost(p, 192, op->base.sm_count, op->st.split_ws != nullptr) * 1.04 < gemm_cost(p, 256, op->base.sm_count, op->st.split_ws != nullptr))
-        return launch_tcgen05<192>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
       return launch_tcgen05<256>(op, p, a_mn, b_mn, ea, eb, alpha, beta, s);
     }
   }
@@ -982,7 +989,7 @@ OPS_API int ops_mat_mul_create(int device, ops_mat_mul **out) {
     delete h;
     return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot allocate the status word");
   }
-  const size_t ws_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * GEMM_BM * 256 * sizeof(float), tk_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * 4 * sizeof(unsigned int);
+  const size_t ws_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * GEMM_BM * 256 * sizeof(float), tk_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * 8 * sizeof(unsigned int);
   if (cudaMalloc(&h->st.split_ws, ws_bytes) != cudaSuccess || cudaMalloc(&h->st.split_tickets, tk_bytes) != cudaSuccess ||
       cudaMemset(h->st.split_tickets, 0, tk_bytes) != cudaSuccess) {
     cudaGetLastError();  // without the scratch the kernel simply runs its last wave unsplit
@@ -1019,7 +1026,7 @@ OPS_API int ops_mat_mul_status_reset(ops_mat_mul *op) {
   cudaSetDevice(op->base.device);
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemset(op->st.status_dev, 0, sizeof(int));
-  if (e == cudaSuccess && op->st.split_tickets) e = cudaMemset(op->st.split_tickets, 0, (size_t)GEMM_SPLIT_MAX_UNITS * 4 * sizeof(unsigned int));
+  if (e == cudaSuccess && op->st.split_tickets) e = cudaMemset(op->st.split_tickets, 0, (size_t)GEMM_SPLIT_MAX_UNITS * 8 * sizeof(unsigned int));
   if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul status reset: %s", cudaGetErrorString(e));
   return OPS_OK;
 }

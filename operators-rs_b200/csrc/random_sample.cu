@@ -21,6 +21,8 @@
 //             exp is evaluated in double and rounded to f32 (= the correctly rounded f32 exp).
 //
 // HBM-bound on paper (rows * n * sizeof(T) bytes read); argmax splits a row over several CTAs.
+#include <cooperative_groups.h>
+
 #include <mutex>
 
 #include "common.h"
@@ -56,19 +58,13 @@ struct ArgmaxScratch {          // per row; all zero between launches (the CTA t
   unsigned int tickets;         // CTAs of this row that have finished
 };
 
+// Scans elements [begin, end) of row x with the whole CTA.  Thread 0 returns the CTA's best (ordered value << 32 | index
+// over non-NaN elements, 0 if none) and 1 + the index of its last NaN (0 if none).
 template <class T>
-__global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logits, long long row_stride, int n, int split,
-                                                     ArgmaxScratch *scratch, KVPair *out) {
-  __shared__ unsigned long long s_best[8];
-  __shared__ unsigned int s_nan[8];
-  const int row = blockIdx.x / split, part = blockIdx.x - row * split;
-  const T *x = byte_off(logits, (long long)row * row_stride);
-  int chunk = (n + split - 1) / split;
-  chunk = (chunk + 7) & ~7;
-  const int begin = part * chunk, end = min(n, begin + chunk);
-
+__device__ __forceinline__ void argmax_scan(const T *x, int begin, int end, unsigned long long *s_best, unsigned int *s_nan,
+                                            unsigned long long &best_out, unsigned int &nan_out) {
   // per thread: running (value, index) with ">=" so that the later of equal values wins (+0 and -0 compare equal);
-  // NaNs are skipped here and only remembered (their last index), see the finish below
+  // NaNs are skipped here and only remembered (their last index), see argmax_finish
   float best_v = -INFINITY;
   int best_i = -1;
   unsigned int last_nan = 0;
@@ -82,18 +78,19 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
   };
   const bool vec_ok = (((uintptr_t)x) & 15) == 0;
   constexpr int PER = 16 / (int)sizeof(T);
+  constexpr int UN = 8;
   if (vec_ok) {
     const int vend = begin + ((end - begin) / PER) * PER;
     const int step = blockDim.x * PER;
-    // batches of four independent 128-bit loads per thread, every load of a batch issued before the first value is used
+    // batches of eight independent 128-bit loads per thread, every load of a batch issued before the first value is used
     // (a CTA's share of a row is a few vectors per thread: one trip to DRAM instead of one per vector)
-    for (int i0 = begin + threadIdx.x * PER; i0 < vend; i0 += 4 * step) {
-      uint4 raw[4];
+    for (int i0 = begin + threadIdx.x * PER; i0 < vend; i0 += UN * step) {
+      uint4 raw[UN];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < UN; ++u)
         if (i0 + u * step < vend) raw[u] = ld_stream_16(x + i0 + u * step);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < UN; ++u) {
         if (i0 + u * step < vend) {
           const T *e = reinterpret_cast<const T *>(&raw[u]);
 #pragma unroll
@@ -116,11 +113,53 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
     s_nan[threadIdx.x >> 5] = last_nan;
   }
   __syncthreads();
-  if (threadIdx.x != 0) return;
-  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
-    best = max(best, s_best[w]);
-    last_nan = max(last_nan, s_nan[w]);
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+      best = max(best, s_best[w]);
+      last_nan = max(last_nan, s_nan[w]);
+    }
   }
+  best_out = best;
+  nan_out = last_nan;
+}
+
+// One thread: the row's answer from its best non-NaN element and its last NaN.
+template <class T>
+__device__ __forceinline__ void argmax_finish(const T *x, int n, unsigned long long gbest, unsigned int gnan, KVPair *out) {
+  unsigned int idx;
+  if (gnan == 0) {
+    idx = (unsigned int)(gbest & 0xffffffffull);
+  } else {
+    // replay of the CPU loop from the last NaN on: the NaN is taken, then replaced by whatever follows
+    idx = gnan - 1;
+    for (unsigned int i = gnan; i < (unsigned)n; ++i)
+      if (!(to_f32(x[idx]) > to_f32(x[i]))) idx = i;
+  }
+  out->idx = idx;
+  out->val = raw_bits(x[idx]);
+}
+
+__device__ __forceinline__ void argmax_chunk(int n, int split, int part, int &begin, int &end) {
+  int chunk = (n + split - 1) / split;
+  chunk = (chunk + 7) & ~7;
+  begin = min(n, part * chunk);
+  end = min(n, begin + chunk);
+}
+
+// A row split over `split` CTAs that meet in global memory (any split, any number of rows).
+template <class T>
+__global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logits, long long row_stride, int n, int split,
+                                                     ArgmaxScratch *scratch, KVPair *out) {
+  __shared__ unsigned long long s_best[8];
+  __shared__ unsigned int s_nan[8];
+  const int row = blockIdx.x / split, part = blockIdx.x - row * split;
+  const T *x = byte_off(logits, (long long)row * row_stride);
+  int begin, end;
+  argmax_chunk(n, split, part, begin, end);
+  unsigned long long best;
+  unsigned int last_nan;
+  argmax_scan(x, begin, end, s_best, s_nan, best, last_nan);
+  if (threadIdx.x != 0) return;
   ArgmaxScratch *sc = scratch + row;
   if (best) atomicMax(&sc->best, best);
   if (last_nan) atomicMax(&sc->last_nan, last_nan);
@@ -131,17 +170,48 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ logit
   const unsigned long long gbest = atomicExch(&sc->best, 0ull);  // read and leave zero for the next launch
   const unsigned int gnan = atomicExch(&sc->last_nan, 0u);
   sc->tickets = 0;
-  unsigned int idx;
-  if (gnan == 0) {
-    idx = (unsigned int)(gbest & 0xffffffffull);
-  } else {
-    // replay of the CPU loop from the last NaN on: the NaN is taken, then replaced by whatever follows
-    idx = gnan - 1;
-    for (unsigned int i = gnan; i < (unsigned)n; ++i)
-      if (!(to_f32(x[idx]) > to_f32(x[i]))) idx = i;
+  argmax_finish(x, n, gbest, gnan, out + row);
+}
+
+// A row split over the eight CTAs of one thread-block cluster that meet in distributed shared memory: no scratch, no
+// atomics, no fences — the launch of a decode step's single row costs one pass over the row plus a cluster barrier.
+constexpr int ARGMAX_CLUSTER = 8;
+template <class T>
+__global__ void __cluster_dims__(ARGMAX_CLUSTER, 1, 1) __launch_bounds__(256)
+    argmax_cluster_kernel(const T *__restrict__ logits, long long row_stride, int n, KVPair *out) {
+  namespace cg = cooperative_groups;
+  __shared__ unsigned long long s_best[8];
+  __shared__ unsigned int s_nan[8];
+  __shared__ unsigned long long c_best;  // this CTA's result, read by the cluster's first CTA
+  __shared__ unsigned int c_nan;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int row = blockIdx.x / ARGMAX_CLUSTER, part = (int)cluster.block_rank();
+  const T *x = byte_off(logits, (long long)row * row_stride);
+  int begin, end;
+  argmax_chunk(n, ARGMAX_CLUSTER, part, begin, end);
+  unsigned long long best;
+  unsigned int last_nan;
+  argmax_scan(x, begin, end, s_best, s_nan, best, last_nan);
+  if (threadIdx.x == 0) {
+    c_best = best;
+    c_nan = last_nan;
   }
-  out[row].idx = idx;
-  out[row].val = raw_bits(x[idx]);
+  cluster.sync();
+  if (part == 0 && threadIdx.x < 32) {
+    unsigned long long b = 0;
+    unsigned int nn = 0;
+    if (threadIdx.x < ARGMAX_CLUSTER) {
+      b = *cluster.map_shared_rank(&c_best, threadIdx.x);
+      nn = *cluster.map_shared_rank(&c_nan, threadIdx.x);
+    }
+#pragma unroll
+    for (int o = ARGMAX_CLUSTER / 2; o > 0; o >>= 1) {
+      b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+      nn = max(nn, __shfl_xor_sync(0xffffffffu, nn, o));
+    }
+    if (threadIdx.x == 0) argmax_finish(x, n, b, nn, out + row);
+  }
+  cluster.sync();  // nobody leaves while its shared memory may still be read
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -961,6 +1031,18 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
   if (!logits || !kv_out) return fail(OPS_DYNAMIC_NOT_SUPPORT, "random_sample: null base pointer at launch");
   cudaSetDevice(base.device);
   if (is_argmax(cfg)) {
+    const usz row_bytes = n * dt_size(dt);
+    // Few rows of ordinary length (a decode step: one row of a 128k vocabulary): one cluster of eight CTAs per row
+    if (rows * ARGMAX_CLUSTER <= 4 * (usz)base.sm_count && row_bytes >= ((usz)32 << 10) && row_bytes <= ((usz)4 << 20)) {
+      const unsigned grid = (unsigned)(rows * ARGMAX_CLUSTER);
+      if (dt == OPS_DT_F16)
+        argmax_cluster_kernel<__half><<<grid, 256, 0, s>>>((const __half *)logits, row_stride, (int)n, (KVPair *)kv_out);
+      else if (dt == OPS_DT_BF16)
+        argmax_cluster_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)logits, row_stride, (int)n, (KVPair *)kv_out);
+      else
+        argmax_cluster_kernel<float><<<grid, 256, 0, s>>>((const float *)logits, row_stride, (int)n, (KVPair *)kv_out);
+      return check_launch("random_sample(argmax, cluster)");
+    }
     ArgmaxScratch *scratch = arg_scratch;
     if (!scratch || rows > arg_rows) {
       const usz need = argmax_ws(rows);
@@ -969,7 +1051,6 @@ static int launch_rows(const OpBase &base, uint32_t dt, usz rows, usz n, const v
       scratch = (ArgmaxScratch *)ws;
     }
     // split a row over several CTAs when there are few rows; keep >= 8 KiB per CTA
-    const usz row_bytes = n * dt_size(dt);
     usz split = (8 * (usz)base.sm_count + rows - 1) / rows;  // ~8 CTAs per SM keep enough loads in flight
     const usz max_split = (row_bytes + 8191) / 8192;
     if (split > max_split) split = max_split;
