@@ -74,10 +74,12 @@ def build(force=False, verbose=False):
             if log:
                 print(log)
     if force or _newer(LIB_PATH, objs):
-        r = subprocess.run([nvcc, "-ccbin", _host_cxx(), *ARCH_FLAGS, "-shared", "-o", LIB_PATH, *objs, "-ldl"],
+        tmp = LIB_PATH + ".partial"  # linked beside the target and renamed: a reader never sees a half-written library
+        r = subprocess.run([nvcc, "-ccbin", _host_cxx(), *ARCH_FLAGS, "-shared", "-o", tmp, *objs, "-ldl"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -14,6 +14,10 @@
 // permutes of four 128-bit loads of V rows.  Running max / sum per query row stay in registers; the 8 warps meet in
 // shared memory, the CTA parks (m, l, o) in a scratch buffer owned by the operator handle, and the last CTA of a kv
 // head to finish merges the splits and writes o.  The q rows of one GQA group share every K/V load.
+// When there are enough kv heads to fill the machine with 8 CTAs each, the 8 splits of a head form one thread-block
+// cluster (16 warps per CTA) and meet in distributed shared memory instead: no partials in global memory, no fence, no
+// arrival counter — a decode step over 4096 keys is short enough for those round trips to show.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -23,10 +27,10 @@
 
 namespace ops {
 
-constexpr int DEC_THREADS = 256;
-constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr int DEC_WARPS = 8;              // split kernel; the cluster kernel runs DEC_CLUSTER_WARPS
+constexpr int DEC_CLUSTER_WARPS = 16;
+constexpr int DEC_CLUSTER = 8;            // CTAs (key-range splits) per kv head in the cluster kernel
 constexpr int DEC_MAX_ROWS = 8;           // the n extent of the MMA
-constexpr int DEC_KEYS_PER_STEP = DEC_WARPS * 16;
 constexpr int DEC_MAX_SPLITS = 64;
 constexpr int DEC_MAX_KV_HEADS = 1024;  // arrival counters in the handle's scratch
 
@@ -85,14 +89,16 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i ==
 //          of the 128-bit loads V[key][64hh + 8g ..] of keys 2c, 2c+1 (a0 = low halves, a1 = high halves) and of keys
 //          2c+8, 2c+9 (a2, a3).
 //          C: c0, c1 = O[rows 2c, 2c+1][dh of m = g], c2, c3 = the same rows at dh + 1.
-template <int DH, bool BF>
-__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const __grid_constant__ DecodeArgs a) {
+template <int DH, bool BF, int WARPS, bool CLUSTER>
+__global__ void __launch_bounds__(WARPS * 32, CLUSTER ? 1 : 2) attention_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr int ROWS = DEC_MAX_ROWS;
   constexpr int CH = DH / 32;   // 128-bit loads per K row per lane
   constexpr int HH = DH / 64;   // 64-wide halves of a V row
+  constexpr int DEC_THREADS = WARPS * 32, DEC_WARPS = WARPS, DEC_KEYS_PER_STEP = WARPS * 16;
   __shared__ __align__(16) unsigned short q_s[ROWS][DH];
   __shared__ float red_m[DEC_WARPS][ROWS], red_l[DEC_WARPS][ROWS];
-  __shared__ __align__(16) float red_o[DEC_WARPS][ROWS][DH];  // 32 KB at most
+  extern __shared__ __align__(16) float red_o_raw[];  // [WARPS][ROWS][DH]: 32 or 64 KB
+  float (*red_o)[ROWS][DH] = reinterpret_cast<float (*)[ROWS][DH]>(red_o_raw);
   __shared__ unsigned int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -238,6 +244,59 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const 
       }
   }
   __syncthreads();
+  if constexpr (CLUSTER) {
+    // the CTA's own (m, l, o) into the first warp's slots, then the 8 CTAs of the kv head meet in distributed shared memory:
+    // CTA k of the cluster finishes output elements [k, k+1) * rows * DH / 8
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    for (int i = threadIdx.x; i < a.rows * DH; i += DEC_THREADS) {
+      const int r = i / DH, col = i - r * DH;
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) acc += red_o[w][r][col];
+      red_o[0][r][col] = acc;  // slot (0, r, col) is read by this thread only
+    }
+    float ls = 0.f, mm = -INFINITY;
+    if (threadIdx.x < ROWS) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        ls += red_l[w][threadIdx.x];
+        mm = fmaxf(mm, red_m[w][threadIdx.x]);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < ROWS) {
+      red_m[0][threadIdx.x] = mm;
+      red_l[0][threadIdx.x] = ls;
+    }
+    cluster.sync();
+    const int share = (a.rows * DH + DEC_CLUSTER - 1) / DEC_CLUSTER;
+    const int first = (int)cluster.block_rank() * share;
+    for (int i = first + threadIdx.x; i < min(first + share, a.rows * DH); i += DEC_THREADS) {
+      const int r = i / DH, col = i - r * DH;
+      float ms[DEC_CLUSTER], lsum[DEC_CLUSTER], ov[DEC_CLUSTER];
+#pragma unroll
+      for (int q = 0; q < DEC_CLUSTER; ++q) {  // 24 remote loads in flight
+        ms[q] = *cluster.map_shared_rank(&red_m[0][r], q);
+        lsum[q] = *cluster.map_shared_rank(&red_l[0][r], q);
+        ov[q] = *cluster.map_shared_rank(&red_o[0][r][col], q);
+      }
+      float top = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < DEC_CLUSTER; ++q) top = fmaxf(top, ms[q]);
+      float den = 0.f, num = 0.f;
+#pragma unroll
+      for (int q = 0; q < DEC_CLUSTER; ++q) {  // split order
+        const float w = ms[q] == -INFINITY ? 0.f : ex2f(ms[q] - top);
+        den = fmaf(lsum[q], w, den);
+        num = fmaf(ov[q], w, num);
+      }
+      const int gi = r / a.seq, si = r - gi * a.seq;
+      a.o[(long long)(kvh * a.group + gi) * a.o_sh + (long long)si * a.o_ss + col] = dec_from_f32<BF>(num / den);
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+    return;
+  }
   // park (m, l, o) of this split
   float *part = a.partial + (((long long)kvh * a.splits + split) * ROWS) * (DH + 2);
   for (int i = threadIdx.x; i < a.rows * DH; i += DEC_THREADS) {
@@ -355,30 +414,61 @@ int attention_decode_enqueue(const OpBase &base, const ops_attention_args *a, us
   g.att = (int)att;
   g.rows = g.group * g.seq;
   g.causal = a->mask == OPS_MASK_CAUSAL;
-  // about two 256-thread CTAs per SM (both resident: every load of the launch is in flight at once), whole 128-key
-  // steps per CTA, and partials that fit the scratch buffer; few splits keep the merge by the last CTA of a kv head short
-  usz splits = (2 * (usz)base.sm_count + nkvh - 1) / nkvh;
-  splits = std::min<usz>(splits, (att + DEC_KEYS_PER_STEP - 1) / DEC_KEYS_PER_STEP);
-  splits = std::min<usz>(splits, DEC_MAX_SPLITS);
-  const usz per_split = nkvh * (usz)DEC_MAX_ROWS * (dh + 2) * sizeof(float);
-  splits = std::min<usz>(splits, attention_decode_scratch_bytes() / per_split);
-  if (splits < 1) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: too many kv heads for the decode scratch buffer");
-  const usz steps = (att + DEC_KEYS_PER_STEP - 1) / DEC_KEYS_PER_STEP;
-  g.keys_per_split = (int)((steps + splits - 1) / splits) * DEC_KEYS_PER_STEP;
-  g.splits = (int)((att + g.keys_per_split - 1) / g.keys_per_split);
   const float inv_sqrt = 1.f / sqrtf((float)dh);
   const float alpha = bf16 ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
   g.scale_log2 = alpha * 1.4426950408889634f;
   g.partial = scratch;
   g.tickets = tickets;
   cudaSetDevice(base.device);
+  // Enough kv heads to put 8 CTAs each on a third of the machine or more, and a key range a CTA walks in a few steps:
+  // the splits of a head meet in cluster shared memory.
+  const usz cluster_step = (usz)DEC_CLUSTER_WARPS * 16;
+  if (nkvh * DEC_CLUSTER * 3 >= (usz)base.sm_count && nkvh <= 4096 && att <= (usz)DEC_CLUSTER * cluster_step * 16) {
+    const usz steps = (att + cluster_step - 1) / cluster_step;
+    g.keys_per_split = (int)(((steps + DEC_CLUSTER - 1) / DEC_CLUSTER) * cluster_step);
+    g.splits = DEC_CLUSTER;
+    void (*kern)(const DecodeArgs) = dh == 128 ? (bf16 ? attention_decode_kernel<128, true, DEC_CLUSTER_WARPS, true> : attention_decode_kernel<128, false, DEC_CLUSTER_WARPS, true>)
+                                               : (bf16 ? attention_decode_kernel<64, true, DEC_CLUSTER_WARPS, true> : attention_decode_kernel<64, false, DEC_CLUSTER_WARPS, true>);
+    const size_t smem = (size_t)DEC_CLUSTER_WARPS * DEC_MAX_ROWS * dh * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention(decode): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)nkvh, DEC_CLUSTER);
+    cfg.blockDim = dim3(DEC_CLUSTER_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = DEC_CLUSTER;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, g);
+    if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention(decode): cluster launch failed: %s", cudaGetErrorString(e));
+    return check_launch("attention(decode, cluster)");
+  }
+  // about two 256-thread CTAs per SM (both resident: every load of the launch is in flight at once), whole 128-key
+  // steps per CTA, and partials that fit the scratch buffer; few splits keep the merge by the last CTA of a kv head short
+  constexpr usz split_step = (usz)DEC_WARPS * 16;
+  usz splits = (2 * (usz)base.sm_count + nkvh - 1) / nkvh;
+  splits = std::min<usz>(splits, (att + split_step - 1) / split_step);
+  splits = std::min<usz>(splits, DEC_MAX_SPLITS);
+  const usz per_split = nkvh * (usz)DEC_MAX_ROWS * (dh + 2) * sizeof(float);
+  splits = std::min<usz>(splits, attention_decode_scratch_bytes() / per_split);
+  if (splits < 1) return fail(OPS_SHAPE_NOT_SUPPORT, "attention: too many kv heads for the decode scratch buffer");
+  const usz steps = (att + split_step - 1) / split_step;
+  g.keys_per_split = (int)((steps + splits - 1) / splits) * (int)split_step;
+  g.splits = (int)((att + g.keys_per_split - 1) / g.keys_per_split);
   dim3 grid((unsigned)nkvh, (unsigned)g.splits);
+  const size_t smem = (size_t)DEC_WARPS * DEC_MAX_ROWS * dh * sizeof(float);
   if (dh == 128) {
-    if (bf16) attention_decode_kernel<128, true><<<grid, DEC_THREADS, 0, s>>>(g);
-    else attention_decode_kernel<128, false><<<grid, DEC_THREADS, 0, s>>>(g);
+    if (bf16) attention_decode_kernel<128, true, DEC_WARPS, false><<<grid, DEC_WARPS * 32, smem, s>>>(g);
+    else attention_decode_kernel<128, false, DEC_WARPS, false><<<grid, DEC_WARPS * 32, smem, s>>>(g);
   } else {
-    if (bf16) attention_decode_kernel<64, true><<<grid, DEC_THREADS, 0, s>>>(g);
-    else attention_decode_kernel<64, false><<<grid, DEC_THREADS, 0, s>>>(g);
+    if (bf16) attention_decode_kernel<64, true, DEC_WARPS, false><<<grid, DEC_WARPS * 32, smem, s>>>(g);
+    else attention_decode_kernel<64, false, DEC_WARPS, false><<<grid, DEC_WARPS * 32, smem, s>>>(g);
   }
   return check_launch("attention(decode)");
 }

@@ -390,25 +390,28 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 // The fast path behind attention::Args (operators/src/attention/args.rs:10-24) for dh = 128: the same function as the
 // crate's composition (operators/src/attention/operator.rs:199-275) computed with online softmax, so HBM sees q, k, v and o
 // once.  What bounds a one-tile kernel on this machine is not the tensor pipe but the chain of hand-offs around the softmax
-// of each 128-key block; here one CTA owns TWO q tiles (256 rows of one head), each with its own softmax warpgroup, and the
-// tensor pipe always has the other tile's products to run while one tile's exponentials are in flight:
+// of each 128-key block; here one CTA owns TWO q tiles (256 rows of one head) and the tensor pipe always has the other
+// tile's products to run while one tile's exponentials are in flight:
 //
 //   warp 0        TMA producer: both q tiles once, then K and V blocks of 128 keys through two-stage rings;
 //   warp 1        tcgen05.mma issuer, in the order  PV(t0,j)  QK(t0,j+1)  PV(t1,j)  QK(t1,j+1)  ...  so that the two tiles
 //                 fall half a period apart;
-//   warps 4-7     softmax of tile 0, warps 8-11 of tile 1: ONE thread per q row.  It reads its whole S row from tensor memory
-//                 (128 registers), takes the maximum, publishes the rescaling factor, writes the probabilities back INTO
-//                 tensor memory as packed 16-bit pairs over the columns S occupied — the second product takes them from there
-//                 (A operand in tensor memory), no shared-memory round trip;
-//   warps 12-15   correction: O lives in tensor memory and accumulates across blocks; when a row maximum moved, these warps
-//                 rescale that tile's O (tcgen05.ld, multiply, tcgen05.st) while the softmax warps are busy with the
-//                 exponentials, and at the end they divide by the row sums and store o.
-// Registers are redistributed after start-up (setmaxnreg): the softmax threads get the 176 they need for a whole row.
-// Every mbarrier wait is bounded; a wait that runs out records its code and every role unwinds to the common teardown.
+//   warps 4-11    softmax of tile 0, warps 12-19 of tile 1: TWO threads per q row, one per half of the block's 128 keys
+//                 (a measured block period was the softmax of one tile plus that tile's two products; the softmax of a
+//                 single warp per scheduler runs at a third of an instruction per clock, so a second warp on the same
+//                 scheduler nearly halves it).  A thread reads its 64 S values from tensor memory, the two threads of a
+//                 row meet through shared memory and a 64-thread named barrier for the row maximum, and each writes its
+//                 probabilities back INTO tensor memory as packed 16-bit pairs over the first half of the columns its S
+//                 values occupied — the second product takes them from there (A operand in tensor memory).
+// O lives in tensor memory and accumulates across blocks.  Rescaling is lazy (see below), so it is rare; when a row maximum
+// of a warp has moved, that warp rescales its half of the O columns itself before it publishes the probabilities.  At the
+// end the same threads divide by the row sums and store o.
+// Registers are redistributed after start-up (setmaxnreg).  Every mbarrier wait is bounded; a wait that runs out records
+// its code and every role unwinds to the common teardown.
 constexpr int FP_BM = 128;        // rows per q tile
 constexpr int FP_BN = 128;        // keys per block
 constexpr int FP_DH = 128;
-constexpr int FP_THREADS = 512;   // 4 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1, correction
+constexpr int FP_THREADS = 640;   // 5 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0 (two), softmax tile 1 (two)
 constexpr int FP_TILE_BYTES = FP_BM * FP_DH * 2;  // one q tile, one K block or one V block: 32 KB
 
 struct PairAttnArgs {
@@ -419,7 +422,6 @@ struct PairAttnArgs {
   int pairs;             // q-tile pairs per head
   float scale_log2;      // alpha * log2(e)
   int vec_store;
-  int bf16;
   int *status;
 };
 
@@ -428,11 +430,11 @@ struct FpSmem {
   static constexpr int OFF_K = OFF_Q + 2 * FP_TILE_BYTES;  // 2 stages
   static constexpr int OFF_V = OFF_K + 2 * FP_TILE_BYTES;  // 2 stages
   static constexpr int OFF_BAR = OFF_V + 2 * FP_TILE_BYTES;
-  static constexpr int NUM_BARS = 22;
+  static constexpr int NUM_BARS = 16;
   static constexpr int OFF_TMEM_SLOT = OFF_BAR + NUM_BARS * 8;
-  static constexpr int OFF_ALPHA = OFF_TMEM_SLOT + 16;            // [2 tiles][128 rows] f32 rescaling factors of the current block
-  static constexpr int OFF_L = OFF_ALPHA + 2 * FP_BM * 4;         // [2 tiles][128 rows] f32 row sums
-  static constexpr int BYTES = OFF_L + 2 * FP_BM * 4 + 1024 /* alignment slack */;
+  static constexpr int OFF_MAX = OFF_TMEM_SLOT + 16;              // [2 tiles][2 halves][128 rows] f32: block maxima of a half row
+  static constexpr int OFF_L = OFF_MAX + 4 * FP_BM * 4;           // [2 tiles][2 halves][128 rows] f32: row sums of a half row
+  static constexpr int BYTES = OFF_L + 4 * FP_BM * 4 + 1024 /* alignment slack */;
 };
 
 __device__ __forceinline__ float fp_max3(float a, float b, float c) {
@@ -442,11 +444,12 @@ __device__ __forceinline__ float fp_max3(float a, float b, float c) {
 }
 __device__ __forceinline__ float fp_ex2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ uint32_t fp_pack(float lo, float hi, int bf) {
-  if (bf) {
+template <bool BF>
+__device__ __forceinline__ uint32_t fp_pack(float lo, float hi) {
+  if (BF) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
   }
@@ -454,6 +457,7 @@ __device__ __forceinline__ uint32_t fp_pack(float lo, float hi, int bf) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+template <bool BF>
 __global__ void __launch_bounds__(FP_THREADS, 1)
     attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ PairAttnArgs g) {
@@ -467,14 +471,11 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
   auto v_full = [&](int s) { return bar0 + 8u * (6 + s); };
   auto v_empty = [&](int s) { return bar0 + 8u * (8 + s); };
   auto s_full = [&](int t) { return bar0 + 8u * (10 + t); };      // S of tile t complete (tensor pipe -> softmax)
-  auto p_full = [&](int t) { return bar0 + 8u * (12 + t); };      // P of tile t written to tensor memory (softmax -> issuer)
-  auto alpha_full = [&](int t) { return bar0 + 8u * (14 + t); };  // rescaling factors of tile t published (softmax -> correction)
-  auto o_scaled = [&](int t) { return bar0 + 8u * (16 + t); };    // O of tile t rescaled (correction -> issuer)
-  auto o_final = [&](int t) { return bar0 + 8u * (18 + t); };     // last PV of tile t complete (tensor pipe -> correction)
-  auto l_full = [&](int t) { return bar0 + 8u * (20 + t); };      // row sums of tile t published (softmax -> correction)
+  auto p_full = [&](int t) { return bar0 + 8u * (12 + t); };      // P of tile t written, O rescaled if needed (softmax -> issuer)
+  auto o_final = [&](int t) { return bar0 + 8u * (14 + t); };     // last PV of tile t complete (tensor pipe -> softmax)
   const uint32_t tmem_slot = base + FpSmem::OFF_TMEM_SLOT;
   uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(base_ptr + FpSmem::OFF_TMEM_SLOT);
-  float *alpha_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_ALPHA);
+  float *max_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_MAX);
   float *l_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_L);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -502,11 +503,8 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       mbar_init(v_full(t), 1);
       mbar_init(v_empty(t), 1);
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 4);
-      mbar_init(alpha_full(t), 4);
-      mbar_init(o_scaled(t), 4);
+      mbar_init(p_full(t), 8);
       mbar_init(o_final(t), 1);
-      mbar_init(l_full(t), 4);
     }
     fence_barrier_init();
   }
@@ -523,7 +521,8 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  // tensor memory columns: S0 | S1 | O0 | O1, 128 each; P of a tile overwrites the first 64 columns of its S
+  // tensor memory columns: S0 | S1 | O0 | O1, 128 each; the P of keys [64h, 64h+64) of a tile overwrites columns
+  // [64h, 64h+32) of its S (the first half of what the thread that wrote it had read)
   auto s_col = [&](int t) { return (uint32_t)(t * 128); };
   auto o_col = [&](int t) { return (uint32_t)(256 + t * 128); };
 
@@ -557,8 +556,8 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       }
     } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
-      const uint32_t idesc_qk = make_idesc_f16(FP_BM, FP_BN, 0, 0, g.bf16);
-      const uint32_t idesc_pv = make_idesc_f16(FP_BM, FP_DH, 0, 1, g.bf16);
+      const uint32_t idesc_qk = make_idesc_f16(FP_BM, FP_BN, 0, 0, BF ? 1 : 0);
+      const uint32_t idesc_pv = make_idesc_f16(FP_BM, FP_DH, 0, 1, BF ? 1 : 0);
       bool ok = true;
       // S(t) = Q(t) K_b^T
       auto issue_qk = [&](int t, int b) -> bool {
@@ -581,10 +580,8 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
       // O(t) (+)= P(t) V_b, P from tensor memory
       auto issue_pv = [&](int t, int b) -> bool {
         const int s = b & 1;
-        const uint32_t ph = (uint32_t)(b & 1);
         if (!mbar_wait(v_full(s), (uint32_t)((b >> 1) & 1), g.status, 122)) return false;
-        if (!mbar_wait(p_full(t), ph, g.status, 123)) return false;
-        if (!mbar_wait(o_scaled(t), ph, g.status, 124)) return false;
+        if (!mbar_wait(p_full(t), (uint32_t)(b & 1), g.status, 123)) return false;
         tc_fence_after();
         const uint32_t va = base + FpSmem::OFF_V + s * FP_TILE_BYTES;
         const uint32_t d = tmem_base + o_col(t);
@@ -592,7 +589,8 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
 #pragma unroll
         for (int ks = 0; ks < FP_BN / 16; ++ks) {
           const uint64_t db = make_smem_desc_sw128(va + (ks >> 2) * (2 * 8192) + (ks & 3) * 2048, 8192, 1024);
-          umma_f16_ts(d, p + (uint32_t)(ks * 8), db, idesc_pv, (b != 0 || ks != 0) ? 1u : 0u);
+          // 16 keys = 8 packed columns; keys 64.. sit behind the second half row's S columns
+          umma_f16_ts(d, p + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), db, idesc_pv, (b != 0 || ks != 0) ? 1u : 0u);
         }
         if (b == nblk[t] - 1) umma_commit(o_final(t));
         const bool last_user = t == 1 || b >= nblk[1];
@@ -612,30 +610,36 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
         }
       }
     }
-  } else if (warp < 12) {
-    // ------------------------------------------------------------------ softmax: one thread per q row
-    setmaxnreg_inc<176>();
-    const int t = (warp - 4) >> 2;
-    const int quarter = warp & 3;
+  } else {
+    // ------------------------------------------------------------------ softmax, rescaling, output: two threads per q row
+    setmaxnreg_inc<104>();
+    const int idx = warp - 4;
+    const int t = idx >> 3;          // q tile
+    const int h = (idx >> 2) & 1;    // which 64 keys of a block, and which 64 columns of O
+    const int quarter = idx & 3;     // = warp & 3: tensor-memory lanes [32 * quarter, +32)
     const int row_in_tile = quarter * 32 + lane;
     const int q_row = q0 + t * FP_BM + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int limit = g.causal ? min(g.att - 1, off + q_row) : g.att - 1;  // last key this row may see
-    const int bf = g.bf16;
+    const int pair_bar = 1 + t * 4 + quarter;  // named barrier of the two warps that share these 32 rows
+    float *max_mine = max_s + (t * 2 + h) * FP_BM + row_in_tile, *max_other = max_s + (t * 2 + (h ^ 1)) * FP_BM + row_in_tile;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < nblk[t] && ok; ++j) {
-      const int kv0 = j * FP_BN;
-      if (!(ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 131))) break;
+    for (int j = 0; j < nblk[t]; ++j) {
+      const int kv0 = j * FP_BN + h * 64;
+      // After a wait has run out this thread only keeps its appointments at the named barrier (its partner may be in it)
+      if (ok) ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 131);
+      if (!ok) {
+        named_bar_sync(pair_bar, 64);
+        continue;
+      }
       tc_fence_after();
-      const uint32_t ta = tmem_base + lane_addr + s_col(t);
-      uint32_t s0[32], s1[32], s2[32], s3[32];
+      const uint32_t ta = tmem_base + lane_addr + s_col(t) + (uint32_t)(h * 64);
+      uint32_t s0[32], s1[32];
       tmem_ld_32x32(ta, s0);
       tmem_ld_32x32(ta + 32u, s1);
-      tmem_ld_32x32(ta + 64u, s2);
-      tmem_ld_32x32(ta + 96u, s3);
       tmem_wait_ld();
-      const bool need_mask = kv0 + FP_BN - 1 > limit;
+      const bool need_mask = kv0 + 63 > limit;
       auto chunk_max = [&](const uint32_t (&v)[32], int k0, float mx) -> float {
         if (need_mask) {
 #pragma unroll
@@ -651,25 +655,38 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
         }
         return fmaxf(m0, m1);
       };
-      float mx = chunk_max(s0, kv0, -INFINITY);
-      mx = chunk_max(s1, kv0 + 32, mx);
-      mx = chunk_max(s2, kv0 + 64, mx);
-      mx = chunk_max(s3, kv0 + 96, mx);
+      float mx = fmaxf(chunk_max(s0, kv0, -INFINITY), chunk_max(s1, kv0 + 32, -INFINITY));
+      // the other half of the row: its maximum over its 64 keys.  A slot is rewritten one block later, after the partner has
+      // published the probabilities of this block, i.e. after it has read the slot.
+      *max_mine = mx;
+      named_bar_sync(pair_bar, 64);
+      mx = fmaxf(mx, *max_other);
       // Lazy rescaling: the reference point m of the exponentials only follows the row maximum when that has moved by more
       // than 2^8 — until then the probabilities are taken relative to the older, smaller m (they stay below 256, exact in
       // the 16-bit operand; the f32 row sum and O carry the same factor, which cancels in o = O / l).  Rescaling O costs
-      // a round trip through tensor memory on the critical path of every block; this way it happens a few times per row.
+      // a round trip through tensor memory on the critical path of a block; this way it happens a few times per row.
       const float m_raw = fmaxf(m, mx * g.scale_log2);
       const bool move = m_raw > m + 8.f;                     // also true on the first block (m = -inf)
       const float m_next = move ? m_raw : m;
       const float m_new = m_next == -INFINITY ? 0.f : m_next;  // a row with nothing visible yet: keep the arithmetic finite
       const float alpha = move ? fp_ex2(m - m_new) : 1.f;    // 0 on the first block
-      alpha_s[t * FP_BM + row_in_tile] = alpha;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(alpha_full(t));
-      // probabilities -> tensor memory, packed pairs over the first 64 columns of this tile's S; row sum
-      float rowsum = 0.f;
-      auto emit = [&](const uint32_t (&v)[32], int c) {  // c = first key column (0..127) of these 32 values
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // some row maximum of these 32 rows moved: rescale this thread's 64 columns of O.  S of block j being complete says
+        // that PV of block j-1 has completed too (the tensor pipe retires in order), so O is stable.
+        const uint32_t to = tmem_base + lane_addr + o_col(t) + (uint32_t)(h * 64);
+#pragma unroll 1
+        for (int c = 0; c < 64; c += 16) {
+          uint32_t v[16];
+          tmem_ld_32x16(to + (uint32_t)c, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+          tmem_st_32x16(to + (uint32_t)c, v);
+        }
+      }
+      // probabilities -> tensor memory, packed pairs over the first 32 of this thread's 64 S columns; row sum
+      float rs0 = 0.f, rs1 = 0.f;
+      auto emit = [&](const uint32_t (&v)[32], int c) {  // c = first key (0 or 32) of these 32 values within the half row
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -679,103 +696,57 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
             if (kv0 + c + e > limit) p0 = 0.f;
             if (kv0 + c + e + 1 > limit) p1 = 0.f;
           }
-          rowsum += p0 + p1;
-          packed[e >> 1] = fp_pack(p0, p1, bf);
+          rs0 += p0;
+          rs1 += p1;
+          packed[e >> 1] = fp_pack<BF>(p0, p1);
         }
         tmem_st_32x16(ta + (uint32_t)(c >> 1), packed);
       };
       emit(s0, 0);
       emit(s1, 32);
-      emit(s2, 64);
-      emit(s3, 96);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(t));
-      l = fmaf(l, alpha, rowsum);
+      l = fmaf(l, alpha, rs0 + rs1);
       m = m_next;
     }
-    l_s[t * FP_BM + row_in_tile] = l;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(l_full(t));
-  } else {
-    // ------------------------------------------------------------------ correction and output (warps 12..15)
-    setmaxnreg_dec<96>();
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    bool ok = true;
-    for (int j = 0; j < nmax && ok; ++j) {
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (j >= nblk[t]) continue;
-        // s_full(t) of block j also tells that PV(t, j-1) has completed (the tensor pipe retires in order): O is stable
-        if (!(ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 140))) break;
-        if (!(ok = mbar_wait(alpha_full(t), (uint32_t)(j & 1), g.status, 141))) break;
-        if (j > 0) {
-          const float a = alpha_s[t * FP_BM + row_in_tile];
-          if (__any_sync(0xffffffffu, a != 1.f)) {  // some row maximum of these 32 rows moved: rescale their O
-            tc_fence_after();
-            const uint32_t to = tmem_base + lane_addr + o_col(t);
-#pragma unroll 1
-            for (int c = 0; c < FP_DH; c += 64) {  // two loads per round trip to tensor memory
-              uint32_t v0[32], v1[32];
-              tmem_ld_32x32(to + (uint32_t)c, v0);
-              tmem_ld_32x32(to + (uint32_t)c + 32u, v1);
-              tmem_wait_ld();
-#pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                v0[e] = __float_as_uint(__uint_as_float(v0[e]) * a);
-                v1[e] = __float_as_uint(__uint_as_float(v1[e]) * a);
-              }
-              tmem_st_32x32(to + (uint32_t)c, v0);
-              tmem_st_32x32(to + (uint32_t)c + 32u, v1);
-            }
-            tmem_wait_st();
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_scaled(t));
-      }
-    }
-    for (int t = 0; t < 2 && ok; ++t) {
-      if (nblk[t] == 0) continue;
-      if (!(ok = mbar_wait(o_final(t), 0, g.status, 142))) break;
-      if (!(ok = mbar_wait(l_full(t), 0, g.status, 143))) break;
+    // whole-row sum: both halves carry the same reference point
+    l_s[(t * 2 + h) * FP_BM + row_in_tile] = l;
+    named_bar_sync(pair_bar, 64);
+    l += l_s[(t * 2 + (h ^ 1)) * FP_BM + row_in_tile];
+    if (ok && nblk[t] > 0 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
       tc_fence_after();
-      const int q_row = q0 + t * FP_BM + row_in_tile;
-      const float inv = __frcp_rn(l_s[t * FP_BM + row_in_tile]);
-      const uint32_t to = tmem_base + lane_addr + o_col(t);
-      unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss;
+      const float inv = __frcp_rn(l);
+      const uint32_t to = tmem_base + lane_addr + o_col(t) + (uint32_t)(h * 64);
+      unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss + h * 64;
       auto store32 = [&](const uint32_t (&v)[32], int c) {
         if (q_row >= g.seq) return;
         if (g.vec_store) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint4 out;
-            out.x = fp_pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv, g.bf16);
-            out.y = fp_pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, g.bf16);
-            out.z = fp_pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, g.bf16);
-            out.w = fp_pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, g.bf16);
+            out.x = fp_pack<BF>(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
+            out.y = fp_pack<BF>(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
+            out.z = fp_pack<BF>(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
+            out.w = fp_pack<BF>(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
             st_global_16(orow + c + q4 * 8, out);
           }
         } else {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const uint32_t pr = fp_pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv, g.bf16);
+            const uint32_t pr = fp_pack<BF>(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
             orow[c + e] = (unsigned short)(pr & 0xffffu);
             orow[c + e + 1] = (unsigned short)(pr >> 16);
           }
         }
       };
 #pragma unroll 1
-      for (int c = 0; c < FP_DH; c += 64) {  // two loads per round trip to tensor memory
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32(to + (uint32_t)c, v0);
-        tmem_ld_32x32(to + (uint32_t)c + 32u, v1);
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(to + (uint32_t)c, v);
         tmem_wait_ld();
-        store32(v0, c);
-        store32(v1, c + 32);
+        store32(v, c);
       }
     }
   }
@@ -898,16 +869,17 @@ static int launch_pair(const OpBase &base, const ops_attention_args *a, usz nh, 
   const float alpha = bf ? __bfloat162float(__float2bfloat16_rn(inv_sqrt)) : __half2float(__float2half_rn(inv_sqrt));
   g.scale_log2 = alpha * 1.4426950408889634f;
   g.vec_store = aligned(a->o_base, 16) && so[0] % 16 == 0 && so[1] % 16 == 0;
-  g.bf16 = bf ? 1 : 0;
   g.status = status;
   cudaSetDevice(base.device);
   if (!*attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FpSmem::BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attention_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FpSmem::BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FpSmem::BYTES);
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention: cannot reserve %d bytes of shared memory: %s", FpSmem::BYTES, cudaGetErrorString(e));
     *attr_set = true;
   }
   const unsigned grid = (unsigned)(nh * (usz)g.pairs);
-  attention_pair_kernel<<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
+  if (bf) attention_pair_kernel<true><<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
+  else attention_pair_kernel<false><<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
   return check_launch("attention(fused, tile pair)");
 }
 

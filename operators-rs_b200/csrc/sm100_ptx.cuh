@@ -147,6 +147,9 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// barrier `id` (1..15; 0 is __syncthreads) over `threads` threads (a multiple of 32): every warp that takes part calls it
+__device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+
 // ---------------------------------------------------------------- register redistribution between warpgroups
 // Executed by every warp of a warpgroup (4 consecutive warps): gives registers back to the SM / takes more of them.
 template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
