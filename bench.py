@@ -6,7 +6,7 @@
 
 One "step" = one pass of the operator chain (rms_norm, mat_mul QKV, rope, attention, mat_mul O, [exchange],
 rms_norm, mat_mul gate|up, swiglu, mat_mul down, [exchange]) over one batch of synthetic tokens:
-  N = 1 : BASELINE config 3 (4096 tokens, d 4096, 32/8 heads, dh 128, ffn 14336, f16, random init);
+  N = 1 : benchmark config 3 (4096 tokens, d 4096, 32/8 heads, dh 128, ffn 14336, f16, random init);
   N > 1 : config 4, the same layer tensor-parallel over N GPUs with an f16 sum all_reduce of the [T, 4096] partials
           (total work fixed -> "scaling": "strong").
 `value`    device-timed (CUDA events on the launching stream, max over ranks), inputs resident in HBM.
@@ -22,11 +22,12 @@ rms_norm, mat_mul gate|up, swiglu, mat_mul down, [exchange]) over one batch of s
            rank 0's compared with the CPU oracle's chain on the same shards.
 `cpu_baseline` (rank 0, N = 1) and `--impl reference`: the CPU oracle — the restated common_cpu operators; the reference
            crate itself cannot be built without a Rust toolchain — on the SAME 4096-token layer, all host threads.
-`other_configs` per-operator numbers of BASELINE configs 1, 2, 5 (and 4's all_reduce sizes), stand-alone launches, beside
+`other_configs` per-operator numbers of benchmark configs 1, 2, 5 (and 4's all_reduce sizes), stand-alone launches, beside
            the library calls the reference's GPU backend makes for them (cuBLAS through torch.matmul, CUB's radix sort
            through torch.sort) timed the same way.
 """
 import argparse
+import atexit
 import json
 import os
 import statistics
@@ -40,7 +41,7 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as graft  # noqa: E402
 
 CFG = dict(d=4096, nh=32, nkvh=8, dh=128, ffn=14336, theta=5e5, eps=1e-5)
-WORKLOAD = "BASELINE config 3: Llama-3-8B-shaped decoder layer, 4096 tokens, d=4096, 32q/8kv heads, dh=128, ffn=14336, f16, random init"
+WORKLOAD = "benchmark config 3: Llama-3-8B-shaped decoder layer, 4096 tokens, d=4096, 32q/8kv heads, dh=128, ffn=14336, f16, random init"
 SEED = 0xB2000030
 PARITY_TOKENS = 512
 NOMINAL_F16_TFLOPS = 2250.0  # dense fp16 tensor peak of one B200 at clocks.max.sm
@@ -80,49 +81,99 @@ def measured_traffic():
     return None
 
 
+_POLLER = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+uuid = sys.argv[1]
+try:
+    h = nv.nvmlDeviceGetHandleByUUID(uuid) if uuid.startswith("GPU-") else nv.nvmlDeviceGetHandleByIndex(int(uuid))
+except Exception:
+    h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[2]))
+out = open(sys.argv[3], "w", buffering=1)
+out.write("max %d\n" % nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+while True:
+    try:
+        out.write("%.6f %d %.1f %d\n" % (time.monotonic(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                          nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+    except Exception:
+        pass
+    time.sleep(0.001)
+"""
+
+
 class ClockSampler:
-    """nvidia-smi clock/throttle samples taken DURING the timed regions."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons of one GPU DURING a timed region.  A child process polls NVML (read-only queries)
+    about every millisecond from the start of the run and stamps every sample with the system-wide monotonic clock; a
+    ClockSampler object is a window [construction, stop()) over that log.  (A thread in this process cannot do it: the
+    launch loop holds the interpreter lock.)"""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+    _proc, _path = None, None
+
+    @classmethod
+    def start_poller(cls, gpu_index):
+        if cls._proc is not None:
+            return
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            uuid = str(gpu_index)
+        f = tempfile.NamedTemporaryFile("w", suffix=".clocks", delete=False)
+        f.close()
+        cls._path = f.name
+        try:
+            cls._proc = subprocess.Popen([sys.executable, "-c", _POLLER, uuid, str(gpu_index), cls._path], stdout=subprocess.DEVNULL,
+                                         stderr=subprocess.DEVNULL)
+            atexit.register(cls.stop_poller)  # on every exit path of every rank
+        except OSError:
+            cls._proc = None
+
+    @classmethod
+    def stop_poller(cls):
+        if cls._proc is not None:
+            cls._proc.terminate()
+            try:
+                cls._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                cls._proc.kill()
+            cls._proc = None
+        if cls._path and os.path.exists(cls._path):
+            os.unlink(cls._path)
+        cls._path = None
 
     def __init__(self, gpu_index):
-        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self.proc = None
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
-                                          "-i", str(gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+        self.start_poller(gpu_index)
+        self.t0 = time.monotonic()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.out.flush()
-        self.out.seek(0)
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.out.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.out.name)
-        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+        t1 = time.monotonic()
+        sm, power, reasons, smax = [], [], set(), None
+        if self._path and os.path.exists(self._path):
+            time.sleep(0.005)  # the child writes line-buffered; let its last samples land
+            with open(self._path) as f:
+                for line in f:
+                    parts = line.split()
+                    if len(parts) == 2 and parts[0] == "max":
+                        smax = float(parts[1])
+                    if len(parts) != 4:
+                        continue
+                    try:
+                        t, c, w, r = float(parts[0]), float(parts[1]), float(parts[2]), int(parts[3])
+                    except ValueError:
+                        continue
+                    if self.t0 <= t <= t1:
+                        sm.append(c)
+                        power.append(w)
+                        for name, bit in self.REASONS:
+                            if r & bit:
+                                reasons.add(name)
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm),
+               "power_w_max": max(power) if power else None, "source": "NVML polled by a child process"}
+        if not sm:
+            out["reasons"] = ["no NVML sample fell inside the region"]
+        return out
 
 
 def make_weights(torch, device, cfg):
@@ -236,7 +287,7 @@ def sustained_leg(torch, local_rank, fn, flops, seconds, peaks):
 
 
 def extra_measurements(torch, pkg, device, peaks, comm, tp, dist, layer_mod, cfg, shard, rank, lane_comms):
-    """Per-operator numbers for the BASELINE configs the layer loop does not cover: config 1 (latency of the small
+    """Per-operator numbers for the benchmark configs the layer loop does not cover: config 1 (latency of the small
     chain), config 2 (attention prefill pieces, KV-cache write), config 3's memory-bound operators stand-alone, config 5
     (random_sample) on one GPU; config 4's all_reduce sizes and small batches under tensor parallelism.  CUDA events around
     back-to-back launches; inputs rotate through more than an L2 worth of buffers where a single copy would fit in L2."""
@@ -444,7 +495,7 @@ def main():
     ap.add_argument("--sustain-seconds", type=float, default=2.0)
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
     ap.add_argument("--no-direct", action="store_true", help="tensor parallel: stage the partials instead of the zero-copy exchange with the residual folded in")
-    ap.add_argument("--pipeline", type=int, default=2, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
+    ap.add_argument("--pipeline", type=int, default=1, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
     ap.add_argument("--overlap-chunks", type=int, default=1, help="token chunks of the row-parallel projections whose all_reduce overlaps the next chunk's GEMM")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -466,6 +517,7 @@ def main():
     assert tp == max(args.gpus, 1) or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    ClockSampler.start_poller(local_rank)  # long before the first timed region: its first samples take a moment
     comms = []
     dist = None
     pipeline = max(1, args.pipeline) if (tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct and args.overlap_chunks == 1) else 1
@@ -632,7 +684,7 @@ def main():
             scaled = float((diff / np.maximum(1.0, mag / 4.0)).max())
             parity = {"tokens": Tp, "max_abs": max_abs, "max_abs_where_ref_below_4": float(diff[mag < 4.0].max()), "max_abs_scaled": scaled,
                       "max_ref_magnitude": float(mag.max()), "tolerance": 2e-2,
-                      "rule": "|got - ref| <= 2e-2 * max(1, |ref| / 4).  Each operator alone meets BASELINE's 1e-2 (observed 2e-3, one f16 ulp); the "
+                      "rule": "|got - ref| <= 2e-2 * max(1, |ref| / 4).  Each operator alone meets the benchmark's 1e-2 (observed 2e-3, one f16 ulp); the "
                               "chain of ten sums those one-ulp differences through three more projections (4096/4096/14336 terms) and its residual "
                               "stream reaches |x| ~ 10-15, where one f16 ulp is already 7.8e-3",
                       "ok": bool(scaled <= 2e-2 and identical), "ranks_identical": identical,
@@ -735,6 +787,7 @@ def main():
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                                 "sample": f"one pass over the same {T}-token causal sequence through the full-width layer "
                                           f"({sec:.1f} s); restated common_cpu operators (the Rust crate cannot be built here)"}
+    ClockSampler.stop_poller()
     print(json.dumps(line), flush=True)
     if comm is not None:
         barrier()

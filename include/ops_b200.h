@@ -224,7 +224,14 @@ int ops_mat_mul_status_reset(ops_mat_mul *op);
  * 1 = one fused flash-attention kernel (no score matrix, no workspace, q left untouched); for dh = 128 a CTA owns two
  *     128-row q tiles whose softmax and tensor-core work interleave; 2 = the same with one q tile per CTA (the kernel
  *     dh = 64 always takes), kept selectable for comparison.
+ * The fused kernel uses the workspace for one thing only: with few heads (heads x ceil(seq / 256) below ~0.9 x the SM
+ * count, e.g. a tensor-parallel shard) and a 16-byte aligned workspace of at least
+ * nh * seq * OPS_ATTENTION_MAX_RUNS * OPS_ATTENTION_RUN_RECORD_BYTES bytes, the key blocks of every tile pair are cut into
+ * up to OPS_ATTENTION_MAX_RUNS runs computed by different CTAs and merged by a second kernel.  Without it (or with a
+ * smaller one) every CTA walks its whole key range; the result differs only in the last bit of the 16-bit output.
  * ------------------------------------------------------------------------------------------- */
+#define OPS_ATTENTION_MAX_RUNS 4
+#define OPS_ATTENTION_RUN_RECORD_BYTES 528 /* 128 f32 of unnormalised output + reference point + row sum, 16-byte aligned */
 typedef struct ops_attention ops_attention;
 typedef struct {
   ops_layout q_layout; void *q_base;

@@ -35,6 +35,7 @@ DYN_F32 = float("inf")
 MASK_NONE, MASK_CAUSAL = 0, 1
 REDUCE_SUM, REDUCE_PROD, REDUCE_MIN, REDUCE_MAX, REDUCE_MEAN = range(5)
 ATTENTION_CHAIN, ATTENTION_FUSED, ATTENTION_FUSED_ONE_TILE = 0, 1, 2
+ATTENTION_MAX_RUNS, ATTENTION_RUN_RECORD_BYTES = 4, 528  # OPS_ATTENTION_MAX_RUNS, OPS_ATTENTION_RUN_RECORD_BYTES
 ALL_REDUCE_AUTO, ALL_REDUCE_NCCL, ALL_REDUCE_P2P_ONE_SHOT, ALL_REDUCE_P2P_TWO_SHOT = range(4)
 COMM_ID_BYTES, COMM_P2P_HANDLE_BYTES = 128, 128
 

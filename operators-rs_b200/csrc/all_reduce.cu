@@ -141,9 +141,13 @@ template <> struct Acc8<float> {
 
 // One-shot: stage own input, tell the peers, wait for theirs, sum everything in rank order.
 // `vecs` = number of 16-byte vectors; CTA b owns vectors [b*per, (b+1)*per).
-template <class T>
+// P = compile-time bound on the group size (2, 4 or 8).  A thread keeps 8 peer loads in flight whatever the group size:
+// U = 8 / P vectors per trip, each requested from every rank before the first is consumed — with one peer a single
+// 16-byte load per thread and trip would leave an NVLink round trip (~2.5 us) mostly idle.
+template <class T, int P>
 __device__ __forceinline__ void one_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                               long long vecs) {
+  constexpr int U = 8 / P;
   const unsigned int parity = epoch & 1u;
   const long long per = (vecs + gridDim.x - 1) / gridDim.x;
   const long long lo = (long long)blockIdx.x * per, hi = min(vecs, lo + per);
@@ -157,27 +161,37 @@ __device__ __forceinline__ void one_shot_body(const P2PKernelArgs &a, unsigned i
   }
   const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
   if (!wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 1)) return;
-  const uint4 *pin[MAX_RANKS];
+  const uint4 *pin[P];
 #pragma unroll
-  for (int q = 0; q < MAX_RANKS; ++q) pin[q] = reinterpret_cast<const uint4 *>(region_in(a.peers[q < a.size ? q : 0], a.region_bytes, parity));
-  for (long long v = lo + threadIdx.x; v < hi; v += blockDim.x) {
-    uint4 raw[MAX_RANKS];  // all peers' copies requested before the first is consumed: one NVLink latency, not p
+  for (int q = 0; q < P; ++q) pin[q] = reinterpret_cast<const uint4 *>(region_in(a.peers[q < a.size ? q : 0], a.region_bytes, parity));
+  for (long long v0 = lo + threadIdx.x; v0 < hi; v0 += (long long)U * blockDim.x) {
+    uint4 raw[U][P];
 #pragma unroll
-    for (int q = 0; q < MAX_RANKS; ++q)
-      if (q < a.size) raw[q] = ld_peer_16(pin[q] + v);
-    float acc[Acc8<T>::N] = {};
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
 #pragma unroll
-    for (int q = 0; q < MAX_RANKS; ++q)
-      if (q < a.size) Acc8<T>::add(acc, raw[q]);
-    dst[v] = Acc8<T>::pack(acc);
+      for (int q = 0; q < P; ++q)
+        if (v < hi && q < a.size) raw[u][q] = ld_peer_16(pin[q] + v);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+      if (v < hi) {
+        float acc[Acc8<T>::N] = {};
+#pragma unroll
+        for (int q = 0; q < P; ++q)
+          if (q < a.size) Acc8<T>::add(acc, raw[u][q]);
+        dst[v] = Acc8<T>::pack(acc);
+      }
+    }
   }
 }
 
-template <class T>
+template <class T, int P>
 __global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
                                                                   uint4 *__restrict__ dst, long long vecs) {
   const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
-  one_shot_body<T>(a, epoch, src, dst, vecs);
+  one_shot_body<T, P>(a, epoch, src, dst, vecs);
   __syncthreads();
   if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
 }
@@ -187,8 +201,9 @@ __global__ void __launch_bounds__(512) all_reduce_one_shot_kernel(const __grid_c
 //           nothing is staged; peers are read at that offset of their direct regions.
 //   ADD:    dst <- dst + sum over ranks of src: the old value of dst (identical on every rank, e.g. a replicated residual
 //           stream) enters the f32 sum of the part this rank reduces, first, before rank 0's partial.
-// The kernel is kept light on purpose — 256 threads, at most 64 registers each — so that one of its CTAs fits on an SM
-// beside a CTA of the persistent tensor-core GEMM: an exchange on one stream then really overlaps a projection on another.
+//   P:      as for the one-shot kernel: 8 / P vectors per thread and trip, 8 peer loads in flight.
+// 256 threads per CTA so that one of its CTAs fits on an SM beside a CTA of the persistent tensor-core GEMM (192 threads,
+// ~35 K registers, nearly all the shared memory): an exchange on one stream can overlap a projection on another.
 constexpr int P2P_TWO_SHOT_THREADS = 256;
 
 template <bool DIRECT>
@@ -197,9 +212,10 @@ __device__ __forceinline__ const uint4 *two_shot_in(const P2PKernelArgs &a, int 
   return reinterpret_cast<const uint4 *>(DIRECT ? region_direct(pb, a.region_bytes) + direct_off : region_in(pb, a.region_bytes, parity));
 }
 
-template <class T, bool DIRECT, bool ADD>
+template <class T, bool DIRECT, bool ADD, int P>
 __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                               long long vecs, long long part_vecs, unsigned long long direct_off) {
+  constexpr int U = 8 / P;
   const unsigned int parity = epoch & 1u;
   const long long per = (part_vecs + gridDim.x - 1) / gridDim.x;
   const long long s_lo = (long long)blockIdx.x * per, s_hi = min(part_vecs, s_lo + per);
@@ -229,24 +245,39 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
   }
   const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
   if (!wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 2)) return;
-  // reduce my part, slice b: every peer's copy of a vector is requested before the first is consumed
+  // reduce my part, slice b: every peer's copy of U vectors is requested before the first is consumed
   {
     const long long base = (long long)a.rank * part_vecs;
     const long long stop = min(s_hi, vecs - base);
-    for (long long v = s_lo + threadIdx.x; v < stop; v += blockDim.x) {
-      uint4 raw[MAX_RANKS], old = make_uint4(0, 0, 0, 0);
+    const uint4 *pin[P];
 #pragma unroll
-      for (int q = 0; q < MAX_RANKS; ++q)
-        if (q < a.size) raw[q] = ld_peer_16(two_shot_in<DIRECT>(a, q, parity, direct_off) + base + v);
-      if constexpr (ADD) old = dst[base + v];
-      float acc[Acc8<T>::N] = {};
-      if constexpr (ADD) Acc8<T>::add(acc, old);
+    for (int q = 0; q < P; ++q) pin[q] = two_shot_in<DIRECT>(a, q < a.size ? q : 0, parity, direct_off) + base;
+    for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {
+      uint4 raw[U][P], old[U];
 #pragma unroll
-      for (int q = 0; q < MAX_RANKS; ++q)
-        if (q < a.size) Acc8<T>::add(acc, raw[q]);
-      const uint4 r = Acc8<T>::pack(acc);
-      mine_out[v] = r;
-      dst[base + v] = r;
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+#pragma unroll
+        for (int q = 0; q < P; ++q)
+          if (v < stop && q < a.size) raw[u][q] = ld_peer_16(pin[q] + v);
+        if constexpr (ADD) {
+          if (v < stop) old[u] = dst[base + v];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+        if (v < stop) {
+          float acc[Acc8<T>::N] = {};
+          if constexpr (ADD) Acc8<T>::add(acc, old[u]);
+#pragma unroll
+          for (int q = 0; q < P; ++q)
+            if (q < a.size) Acc8<T>::add(acc, raw[u][q]);
+          const uint4 r = Acc8<T>::pack(acc);
+          mine_out[v] = r;
+          dst[base + v] = r;
+        }
+      }
     }
   }
   __threadfence_system();
@@ -256,32 +287,40 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
     st_release_sys(&pf->reduced[a.rank][blockIdx.x], epoch);
   }
   if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 3)) return;
-  // gather the other parts: one vector from every peer in flight per thread and trip
-  for (long long v = s_lo + threadIdx.x; v < s_hi; v += blockDim.x) {
-    uint4 raw[MAX_RANKS];
+  // gather the other parts: U vectors from every peer in flight per thread and trip
+  for (long long v0 = s_lo + threadIdx.x; v0 < s_hi; v0 += (long long)U * blockDim.x) {
+    uint4 raw[U][P - 1];
 #pragma unroll
-    for (int i = 0; i < MAX_RANKS - 1; ++i)
-      if (i < a.size - 1) {
-        int q = a.rank + 1 + i;  // rank r starts at peer r+1: spreads the load over the links
-        if (q >= a.size) q -= a.size;
-        if ((long long)q * part_vecs + v < vecs) raw[i] = ld_peer_16(reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity)) + v);
-      }
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
 #pragma unroll
-    for (int i = 0; i < MAX_RANKS - 1; ++i)
-      if (i < a.size - 1) {
-        int q = a.rank + 1 + i;
-        if (q >= a.size) q -= a.size;
-        if ((long long)q * part_vecs + v < vecs) dst[(long long)q * part_vecs + v] = raw[i];
-      }
+      for (int i = 0; i < P - 1; ++i)
+        if (i < a.size - 1 && v < s_hi) {
+          int q = a.rank + 1 + i;  // rank r starts at peer r+1: spreads the load over the links
+          if (q >= a.size) q -= a.size;
+          if ((long long)q * part_vecs + v < vecs) raw[u][i] = ld_peer_16(reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity)) + v);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+#pragma unroll
+      for (int i = 0; i < P - 1; ++i)
+        if (i < a.size - 1 && v < s_hi) {
+          int q = a.rank + 1 + i;
+          if (q >= a.size) q -= a.size;
+          if ((long long)q * part_vecs + v < vecs) dst[(long long)q * part_vecs + v] = raw[u][i];
+        }
+    }
   }
 }
 
-template <class T, bool DIRECT, bool ADD>
-__global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS, 4) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
+template <class T, bool DIRECT, bool ADD, int P>
+__global__ void __maxnreg__(104) all_reduce_two_shot_kernel(const __grid_constant__ P2PKernelArgs a, const uint4 *__restrict__ src,
                                                                                       uint4 *__restrict__ dst, long long vecs, long long part_vecs,
                                                                                       unsigned long long direct_off) {
   const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
-  two_shot_body<T, DIRECT, ADD>(a, epoch, src, dst, vecs, part_vecs, direct_off);
+  two_shot_body<T, DIRECT, ADD, P>(a, epoch, src, dst, vecs, part_vecs, direct_off);
   __syncthreads();
   if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
 }
@@ -558,10 +597,12 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     if (ctas > 2 * c->sm_count) ctas = 2 * c->sm_count;
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
-    all_reduce_one_shot_kernel<T><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
+    if (c->size <= 2) all_reduce_one_shot_kernel<T, 2><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
+    else if (c->size <= 4) all_reduce_one_shot_kernel<T, 4><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
+    else all_reduce_one_shot_kernel<T, 8><<<(unsigned)ctas, 512, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs);
   } else {
     const long long part = (vecs + c->size - 1) / c->size;
-    long long ctas = (part + 2 * P2P_TWO_SHOT_THREADS - 1) / (2 * P2P_TWO_SHOT_THREADS);
+    long long ctas = (part + 4 * P2P_TWO_SHOT_THREADS - 1) / (4 * P2P_TWO_SHOT_THREADS);
     if (ctas > c->sm_count) ctas = c->sm_count;  // every CTA must be resident: same-index CTAs of different ranks wait for each other
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
@@ -569,13 +610,20 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     const char *direct = region_direct(c->peers[c->rank], c->region_bytes);
     const bool in_direct = (const char *)src >= direct && (const char *)src + bytes <= direct + c->region_bytes;
     const unsigned long long off = in_direct ? (unsigned long long)((const char *)src - direct) : 0ull;
-#define OPS_TWO_SHOT(DIRECT, ADD) \
-  all_reduce_two_shot_kernel<T, DIRECT, ADD><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part, off)
+#define OPS_TWO_SHOT_P(DIRECT, ADD, P) \
+  all_reduce_two_shot_kernel<T, DIRECT, ADD, P><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, (const uint4 *)src, (uint4 *)dst, vecs, part, off)
+#define OPS_TWO_SHOT(DIRECT, ADD)                          \
+  do {                                                     \
+    if (c->size <= 2) OPS_TWO_SHOT_P(DIRECT, ADD, 2);      \
+    else if (c->size <= 4) OPS_TWO_SHOT_P(DIRECT, ADD, 4); \
+    else OPS_TWO_SHOT_P(DIRECT, ADD, 8);                   \
+  } while (0)
     if (in_direct && add) OPS_TWO_SHOT(true, true);
     else if (in_direct) OPS_TWO_SHOT(true, false);
     else if (add) OPS_TWO_SHOT(false, true);
     else OPS_TWO_SHOT(false, false);
 #undef OPS_TWO_SHOT
+#undef OPS_TWO_SHOT_P
   }
   return check_launch("all_reduce(p2p)");
 }

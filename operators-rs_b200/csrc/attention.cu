@@ -138,7 +138,7 @@ int attention_enqueue(const ops_attention *op, const ops_attention_args *a, void
     return attention_decode_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->decode_scratch, op->decode_tickets, s);
   if (fused && a->q_base && a->k_base && a->v_base && a->o_base && attention_fused_supported(a, m.nh, m.nkvh, m.seq, m.att, m.dh)) {
     ops_attention *mop = const_cast<ops_attention *>(op);
-    return attention_fused_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->status_dev, mop->attr_set, s,
+    return attention_fused_enqueue(op->base, a, m.nh, m.nkvh, m.seq, m.att, m.dh, op->status_dev, mop->attr_set, ws, ws_len, s,
                                    op->algo == OPS_ATTENTION_FUSED_ONE_TILE);
   }
   return attention_chain(op, a, m, ws, ws_len, s);

@@ -408,6 +408,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 // end the same threads divide by the row sums and store o.
 // Registers are redistributed after start-up (setmaxnreg).  Every mbarrier wait is bounded; a wait that runs out records
 // its code and every role unwinds to the common teardown.
+//
+// Few heads (a tensor-parallel shard): heads x tile pairs CTAs would leave most SMs idle behind the longest causal pair, so
+// the key blocks of every pair are cut into `chunks` runs, one CTA each; a CTA then parks its unnormalised O (f32), its
+// reference point m and row sum l in the caller's workspace and `attention_combine_kernel` merges the runs of a row.
 constexpr int FP_BM = 128;        // rows per q tile
 constexpr int FP_BN = 128;        // keys per block
 constexpr int FP_DH = 128;
@@ -423,7 +427,32 @@ struct PairAttnArgs {
   float scale_log2;      // alpha * log2(e)
   int vec_store;
   int *status;
+  int chunks;            // runs of key blocks per tile pair (1: the CTA finishes its rows itself)
+  float *partial;        // chunks > 1: [head][q row][chunk][FP_PART_LD] = O (128 f32, unnormalised), m, l
 };
+constexpr int FP_PART_LD = FP_DH + 4;  // 16-byte aligned records
+
+// key blocks of q tile `t` of pair `pair` (all of them), and the run [jb0, jb0 + len) chunk `chunk` of the pair takes
+struct FpRange {
+  int nblk[2];  // blocks of each tile inside the run
+  int jb0;
+};
+__host__ __device__ __forceinline__ FpRange fp_range(int pair, int chunk, int chunks, int seq, int att, int causal) {
+  const int off = att - seq;
+  int total[2];
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = (pair * 2 + t) * FP_BM;
+    int k_end = att;
+    if (causal) k_end = min(att, off + r0 + FP_BM);
+    total[t] = r0 < seq ? (k_end + FP_BN - 1) / FP_BN : 0;
+  }
+  const int nmax = max(total[0], total[1]);
+  const int len = (nmax + chunks - 1) / chunks;
+  FpRange r;
+  r.jb0 = chunk * len;
+  for (int t = 0; t < 2; ++t) r.nblk[t] = max(0, min(total[t], r.jb0 + len) - r.jb0);
+  return r;
+}
 
 struct FpSmem {
   static constexpr int OFF_Q = 0;                          // 2 tiles
@@ -479,20 +508,17 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
   float *l_s = reinterpret_cast<float *>(base_ptr + FpSmem::OFF_L);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heaviest pairs first, the heads of one pair next to each other (a GQA group shares its K/V blocks through L2)
-  const int pair = g.pairs - 1 - (int)(blockIdx.x / g.nh);
+  // heaviest pairs first, the heads of one (pair, run) next to each other (a GQA group shares its K/V blocks through L2)
+  const int item = (int)(blockIdx.x / g.nh);
+  const int pair = g.pairs - 1 - item / g.chunks, chunk = item % g.chunks;
   const int head = (int)(blockIdx.x % g.nh);
   const int kv_head = head / g.group;
   const int q0 = pair * 2 * FP_BM;
   const int off = g.att - g.seq;  // causal row r sees keys <= off + r
-  int nblk[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int r0 = q0 + t * FP_BM;
-    int k_end = g.att;
-    if (g.causal) k_end = min(g.att, off + r0 + FP_BM);
-    nblk[t] = r0 < g.seq ? (k_end + FP_BN - 1) / FP_BN : 0;
-  }
+  // this CTA's run of key blocks: local block j is block jb0 + j of the pair; nblk[t] local blocks concern tile t
+  const FpRange range = fp_range(pair, chunk, g.chunks, g.seq, g.att, g.causal);
+  const int nblk[2] = {range.nblk[0], range.nblk[1]};
+  const int jb0 = range.jb0;
   const int nmax = max(nblk[0], nblk[1]);
 
   if (threadIdx.x == 0) {
@@ -545,14 +571,14 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
         mbar_arrive_expect_tx(k_full(s), FP_TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < 2; ++h)
-          tma_load_3d(base + FpSmem::OFF_K + s * FP_TILE_BYTES + h * (FP_BN * 128), &tmap_k, k_full(s), h * 64, j * FP_BN, kv_head);
+          tma_load_3d(base + FpSmem::OFF_K + s * FP_TILE_BYTES + h * (FP_BN * 128), &tmap_k, k_full(s), h * 64, (jb0 + j) * FP_BN, kv_head);
         if (!(ok = mbar_wait(v_empty(s), ph ^ 1u, g.status, 112))) break;
         mbar_arrive_expect_tx(v_full(s), FP_TILE_BYTES);
 #pragma unroll
         for (int kg = 0; kg < 2; ++kg)
 #pragma unroll
           for (int c = 0; c < 2; ++c)
-            tma_load_3d(base + FpSmem::OFF_V + s * FP_TILE_BYTES + (kg * 2 + c) * 8192, &tmap_v, v_full(s), c * 64, j * FP_BN + kg * 64, kv_head);
+            tma_load_3d(base + FpSmem::OFF_V + s * FP_TILE_BYTES + (kg * 2 + c) * 8192, &tmap_v, v_full(s), c * 64, (jb0 + j) * FP_BN + kg * 64, kv_head);
       }
     } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
@@ -626,7 +652,7 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk[t]; ++j) {
-      const int kv0 = j * FP_BN + h * 64;
+      const int kv0 = (jb0 + j) * FP_BN + h * 64;
       // After a wait has run out this thread only keeps its appointments at the named barrier (its partner may be in it)
       if (ok) ok = mbar_wait(s_full(t), (uint32_t)(j & 1), g.status, 131);
       if (!ok) {
@@ -715,7 +741,27 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
     l_s[(t * 2 + h) * FP_BM + row_in_tile] = l;
     named_bar_sync(pair_bar, 64);
     l += l_s[(t * 2 + (h ^ 1)) * FP_BM + row_in_tile];
-    if (ok && nblk[t] > 0 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
+    if (ok && nblk[t] > 0 && g.chunks > 1 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
+      // one run of several: park the unnormalised O with its reference point and row sum
+      tc_fence_after();
+      const uint32_t to = tmem_base + lane_addr + o_col(t) + (uint32_t)(h * 64);
+      float *prow = g.partial + (((long long)head * g.seq + q_row) * g.chunks + chunk) * FP_PART_LD;
+      if (q_row < g.seq && h == 0) {
+        prow[FP_DH] = m;
+        prow[FP_DH + 1] = l;
+      }
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(to + (uint32_t)c, v);
+        tmem_wait_ld();
+        if (q_row < g.seq) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<uint4 *>(prow + h * 64 + c + q4 * 4) = make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        }
+      }
+    } else if (ok && nblk[t] > 0 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
       tc_fence_after();
       const float inv = __frcp_rn(l);
       const uint32_t to = tmem_base + lane_addr + o_col(t) + (uint32_t)(h * 64);
@@ -760,6 +806,54 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
   }
 }
 
+
+// Merges the runs of a q row left by attention_pair_kernel (chunks > 1): one warp per (head, row), a lane per 4 columns.
+//   o = sum_c 2^(m_c - M) O_c / sum_c 2^(m_c - M) l_c,  M = max_c m_c, runs taken in order.
+template <bool BF>
+__global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_constant__ PairAttnArgs g) {
+  const long long row_id = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row_id >= (long long)g.nh * g.seq) return;
+  const int head = (int)(row_id / g.seq), q_row = (int)(row_id - (long long)head * g.seq);
+  const int pair = q_row / (2 * FP_BM), t = (q_row / FP_BM) & 1;
+  const float *prow = g.partial + row_id * g.chunks * FP_PART_LD;
+  float ms[8];
+  float top = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    ms[c] = -INFINITY;
+    if (c < g.chunks && fp_range(pair, c, g.chunks, g.seq, g.att, g.causal).nblk[t] > 0) ms[c] = prow[c * FP_PART_LD + FP_DH];
+    top = fmaxf(top, ms[c]);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    if (c < g.chunks && ms[c] != -INFINITY) {
+      const float w = fp_ex2(ms[c] - top);
+      const float4 v = *reinterpret_cast<const float4 *>(prow + c * FP_PART_LD + lane * 4);
+      den = fmaf(prow[c * FP_PART_LD + FP_DH + 1], w, den);
+      acc.x = fmaf(v.x, w, acc.x);
+      acc.y = fmaf(v.y, w, acc.y);
+      acc.z = fmaf(v.z, w, acc.z);
+      acc.w = fmaf(v.w, w, acc.w);
+    }
+  }
+  const float inv = den > 0.f ? __frcp_rn(den) : 0.f;
+  const uint32_t lo = fp_pack<BF>(acc.x * inv, acc.y * inv), hi = fp_pack<BF>(acc.z * inv, acc.w * inv);
+  unsigned short *orow = g.o + (long long)head * g.o_sh + (long long)q_row * g.o_ss + lane * 4;
+  if (g.vec_store) {
+    *reinterpret_cast<uint2 *>(orow) = make_uint2(lo, hi);
+  } else {
+    orow[0] = (unsigned short)(lo & 0xffffu);
+    orow[1] = (unsigned short)(lo >> 16);
+    orow[2] = (unsigned short)(hi & 0xffffu);
+    orow[3] = (unsigned short)(hi >> 16);
+  }
+}
+
+constexpr int FP_MAX_CHUNKS = OPS_ATTENTION_MAX_RUNS;
+static_assert(FP_PART_LD * sizeof(float) == OPS_ATTENTION_RUN_RECORD_BYTES, "record size published in the header");
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (shared with mat_mul.cu's approach)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -847,7 +941,7 @@ static int launch_fused(const OpBase &base, const ops_attention_args *a, usz nh,
 }
 
 static int launch_pair(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, int *status, bool *attr_set,
-                       cudaStream_t s) {
+                       void *ws, usz ws_len, cudaStream_t s) {
   CUtensorMap tq, tk, tv;
   const isz *sq = a->q_layout.strides, *sk = a->k_layout.strides, *sv = a->v_layout.strides, *so = a->o_layout.strides;
   const bool bf = a->q_layout.dt == OPS_DT_BF16;
@@ -877,16 +971,31 @@ static int launch_pair(const OpBase &base, const ops_attention_args *a, usz nh, 
     if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "attention: cannot reserve %d bytes of shared memory: %s", FpSmem::BYTES, cudaGetErrorString(e));
     *attr_set = true;
   }
-  const unsigned grid = (unsigned)(nh * (usz)g.pairs);
+  // Runs per pair: as many as it takes to give every SM about two CTAs, if the caller's workspace holds the partial
+  // results (the chain's own workspace request, which ops_attention_scheme reports, is far larger)
+  usz chunks = std::min<usz>(FP_MAX_CHUNKS, (usz)base.sm_count * 7 / 4 / (nh * (usz)g.pairs));
+  const usz longest = (att + FP_BN - 1) / FP_BN;
+  chunks = std::max<usz>(1, std::min(chunks, longest / 4));  // at least four key blocks per run
+  while (chunks > 1 && (!ws || !aligned(ws, 16) || ws_len < nh * seq * chunks * FP_PART_LD * sizeof(float))) --chunks;
+  g.chunks = (int)chunks;
+  g.partial = (float *)ws;
+  const unsigned grid = (unsigned)(nh * (usz)g.pairs * chunks);
   if (bf) attention_pair_kernel<true><<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
   else attention_pair_kernel<false><<<grid, FP_THREADS, FpSmem::BYTES, s>>>(tq, tk, tv, g);
-  return check_launch("attention(fused, tile pair)");
+  OPS_TRY(check_launch("attention(fused, tile pair)"));
+  if (chunks > 1) {
+    const unsigned cgrid = (unsigned)((nh * seq + 7) / 8);
+    if (bf) attention_combine_kernel<true><<<cgrid, 256, 0, s>>>(g);
+    else attention_combine_kernel<false><<<cgrid, 256, 0, s>>>(g);
+    return check_launch("attention(fused, combine)");
+  }
+  return OPS_OK;
 }
 
 int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
-                            bool *attr_set, cudaStream_t s, bool single_tile) {
+                            bool *attr_set, void *ws, usz ws_len, cudaStream_t s, bool single_tile) {
   // dh = 128 with more than one q tile: the two-tile kernel; everything else (and on request) one tile per CTA
-  if (dh == 128 && seq > (usz)FP_BM && !single_tile) return launch_pair(base, a, nh, nkvh, seq, att, status, &attr_set[2], s);
+  if (dh == 128 && seq > (usz)FP_BM && !single_tile) return launch_pair(base, a, nh, nkvh, seq, att, status, &attr_set[2], ws, ws_len, s);
   if (dh == 128) return launch_fused<128>(base, a, nh, nkvh, seq, att, status, &attr_set[0], s);
   return launch_fused<64>(base, a, nh, nkvh, seq, att, status, &attr_set[1], s);
 }

@@ -12,7 +12,7 @@ int fused_softmax_enqueue(const OpBase &base, const ops_fused_softmax_args *args
 int mat_mul_enqueue(const ops_mat_mul *op, const ops_mat_mul_args *args, cudaStream_t s);
 bool attention_fused_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh);
 int attention_fused_enqueue(const OpBase &base, const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh, int *status,
-                            bool *attr_set, cudaStream_t s, bool single_tile);
+                            bool *attr_set, void *ws, usz ws_len, cudaStream_t s, bool single_tile);
 
 bool attention_decode_supported(const ops_attention_args *a, usz nh, usz nkvh, usz seq, usz att, usz dh);
 usz attention_decode_scratch_bytes();

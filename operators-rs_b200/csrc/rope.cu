@@ -21,34 +21,57 @@ struct RopeDivisors {
   float v[ROPE_MAX_HALF];
 };
 
+// `toks` tokens per CTA: the sin/cos pairs of all of them are computed first, one per thread (one token per CTA left three
+// quarters of a 256-thread CTA idle through the sincosf latency, which then bounded the launch, not HBM), then the CTA
+// streams the tokens' rows with several 128-bit accesses in flight per thread.
 template <class E, class P>
 __global__ void __launch_bounds__(256) rope_f16_kernel(E *__restrict__ t, long long st, long long sh, const P *__restrict__ pos,
-                                                       long long sp, int nh, int half_dh, const __grid_constant__ RopeDivisors div) {
-  extern __shared__ float2 sincos_tab[];  // [half_dh] (sin, cos)
-  const long long tok = blockIdx.x;
-  const float p = (float)*byte_off(pos, tok * sp);
-  for (int k = threadIdx.x; k < half_dh; k += blockDim.x) {
+                                                       long long sp, int nt, int toks, int nh, int half_dh,
+                                                       const __grid_constant__ RopeDivisors div) {
+  extern __shared__ float2 sincos_tab[];  // [toks][half_dh] (sin, cos)
+  const long long tok0 = (long long)blockIdx.x * toks;
+  const int here = (int)min((long long)toks, (long long)nt - tok0);
+  for (int i = threadIdx.x; i < here * half_dh; i += blockDim.x) {
+    const int tk = i / half_dh, k = i - tk * half_dh;
+    const float p = (float)*byte_off(pos, (tok0 + tk) * sp);
     float s, c;
     sincosf(__fdiv_rn(p, div.v[k]), &s, &c);
-    sincos_tab[k] = make_float2(s, c);
+    sincos_tab[i] = make_float2(s, c);
   }
   __syncthreads();
-  E *row = byte_off(t, tok * st);
   const int vec_per_head = half_dh >> 2;  // 4 pairs = 8 halves per vector
-  const int total = nh * vec_per_head;
-  for (int v = threadIdx.x; v < total; v += blockDim.x) {
-    const int head = v / vec_per_head, kv = v - head * vec_per_head;
-    E *ptr = byte_off(row, (long long)head * sh) + kv * 8;
-    Vec8<E> in, out;
-    in.u = ld_global_16(ptr);
+  const int per_tok = nh * vec_per_head;
+  const int total = here * per_tok;
+  constexpr int UN = 4;
+  for (int v0 = threadIdx.x; v0 < total; v0 += UN * blockDim.x) {
+    Vec8<E> in[UN];
+    E *ptr[UN];
+    int tab[UN];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 sc = sincos_tab[kv * 4 + e];
-      const float a = to_f32(in.h[2 * e]), b = to_f32(in.h[2 * e + 1]);
-      out.h[2 * e] = from_f32<E>(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
-      out.h[2 * e + 1] = from_f32<E>(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
+    for (int u = 0; u < UN; ++u) {
+      const int v = v0 + u * blockDim.x;
+      if (v < total) {
+        const int tk = v / per_tok, r = v - tk * per_tok;
+        const int head = r / vec_per_head, kv = r - head * vec_per_head;
+        ptr[u] = byte_off(byte_off(t, (tok0 + tk) * st), (long long)head * sh) + kv * 8;
+        tab[u] = tk * half_dh + kv * 4;
+        in[u].u = ld_global_16(ptr[u]);
+      }
     }
-    st_global_16(ptr, out.u);
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      if (v0 + u * blockDim.x < total) {
+        Vec8<E> out;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 sc = sincos_tab[tab[u] + e];
+          const float a = to_f32(in[u].h[2 * e]), b = to_f32(in[u].h[2 * e + 1]);
+          out.h[2 * e] = from_f32<E>(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
+          out.h[2 * e + 1] = from_f32<E>(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
+        }
+        st_global_16(ptr[u], out.u);
+      }
+    }
   }
 }
 
@@ -139,8 +162,16 @@ OPS_API int ops_rope_launch(const ops_rope *op, const ops_rope_args *a, void *ws
   const bool fast = t16 && use_table && dh % 8 == 0 && st % 16 == 0 && sh % 16 == 0 && aligned(a->t_base, 16);
   const dim3 grid((unsigned)m.nt);
   if (fast) {
-    const usz smem = (usz)half_dh * sizeof(float2);
-#define ROPE_FAST(E, P) rope_f16_kernel<E, P><<<grid, 256, smem, s>>>((E *)a->t_base, st, sh, (const P *)a->p_base, sp, (int)nh, half_dh, div)
+    // tokens per CTA: one when a token's heads alone give every thread a 128-bit vector (a whole layer: measured faster
+    // with many small CTAs); with few heads per token (a tensor-parallel shard) as many as fill the CTA's threads, at
+    // most one sin/cos pair per thread (256 / half_dh); fewer when there are too few tokens to fill the machine otherwise
+    const int vec_per_tok = (int)nh * (half_dh >> 2);
+    int toks = std::max(1, std::min(256 / half_dh, 256 / std::max(1, vec_per_tok)));
+    while (toks > 1 && (m.nt + toks - 1) / toks < 2 * (usz)op->base.sm_count) toks >>= 1;
+    const dim3 fgrid((unsigned)((m.nt + toks - 1) / toks));
+    const usz smem = (usz)toks * half_dh * sizeof(float2);
+#define ROPE_FAST(E, P) \
+  rope_f16_kernel<E, P><<<fgrid, 256, smem, s>>>((E *)a->t_base, st, sh, (const P *)a->p_base, sp, (int)m.nt, toks, (int)nh, half_dh, div)
     if (m.dt_t == OPS_DT_F16 && m.dt_p == OPS_DT_U32) ROPE_FAST(__half, uint32_t);
     else if (m.dt_t == OPS_DT_F16) ROPE_FAST(__half, unsigned long long);
     else if (m.dt_p == OPS_DT_U32) ROPE_FAST(__nv_bfloat16, uint32_t);

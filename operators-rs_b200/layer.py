@@ -1,7 +1,7 @@
 """The decoder-layer operator chain, as a caller of the per-operator API.
 
 The reference crate ships operators only; the chain below is what a downstream runtime does with
-them for one Llama-shaped layer (BASELINE config 3) and its tensor-parallel form (config 4):
+them for one Llama-shaped layer (benchmark config 3) and its tensor-parallel form (config 4):
 
     rms_norm -> mat_mul(QKV) -> rope(q,k heads) -> attention -> mat_mul(O, beta=1 residual)
              -> [all_reduce] -> rms_norm -> mat_mul(gate|up) -> swiglu -> mat_mul(down, beta=1) -> [all_reduce]
@@ -13,7 +13,7 @@ how the partials and the residual meet.
 """
 from dataclasses import dataclass
 
-from . import (ALL_REDUCE_AUTO, MASK_CAUSAL, AllReduce, AllReduceArgs, Attention, AttentionArgs, FusedSoftmax, MatMul,
+from . import (ALL_REDUCE_AUTO, ATTENTION_MAX_RUNS, ATTENTION_RUN_RECORD_BYTES, MASK_CAUSAL, AllReduce, AllReduceArgs, Attention, AttentionArgs, FusedSoftmax, MatMul,
                MatMulArgs, Rearrange, RmsNorm, RmsNormArgs, Rope, RopeArgs, Swiglu, SwigluArgs)
 
 
@@ -131,7 +131,10 @@ class DecoderLayer:
         self.att_out = torch.empty(T, self.nq * cfg.dh, dtype=f16, device=device)
         self.gu = torch.empty(T, 2 * self.f, dtype=f16, device=device)
         self.scratch = torch.empty(T, cfg.d, dtype=f16, device=device) if (tp > 1 and rank != 0) else None
-        self.ws = torch.empty(16, dtype=torch.uint8, device=device)  # the fused attention kernels need none; the chain allocates
+        # The fused attention kernels need no workspace on a whole layer; a tensor-parallel shard has few heads, and with
+        # room for the partial results the kernel cuts the key blocks of every tile pair into runs so that all SMs work
+        ws_bytes = 16 if tp == 1 else self.nq * T * ATTENTION_MAX_RUNS * ATTENTION_RUN_RECORD_BYTES
+        self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
         self.max_tokens = T
 
     def forward(self, x, pos, on_step=None):

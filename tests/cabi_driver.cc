@@ -1,5 +1,5 @@
 // cabi_driver.cc — a C++ caller of the C ABI with nothing in between: includes include/ops_b200.h, links libops_b200.so,
-// owns its device memory through the CUDA runtime, and runs BASELINE config 1 (rms_norm -> rope on [64 tokens, 32 heads,
+// owns its device memory through the CUDA runtime, and runs benchmark config 1 (rms_norm -> rope on [64 tokens, 32 heads,
 // 64], causal fused_softmax on [32, 64, 64]) plus one tensor-core mat_mul and one argmax, each checked against the CPU
 // oracle (liboracle.so, test infrastructure).  It is what a Rust `impl Operator` shim does, written in the one compiled
 // language this environment has: create -> scheme -> launch on a stream -> destroy, errors as return values

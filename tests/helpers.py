@@ -9,7 +9,7 @@ def max_abs(got, ref):
 
 
 def assert_close(got, ref, tol=1e-2, what=""):
-    """BASELINE tolerance: max-abs error after f32 accumulation, f16 outputs."""
+    """The benchmark's tolerance: max-abs error after f32 accumulation, f16 outputs."""
     assert got.shape == ref.shape, (got.shape, ref.shape)
     assert np.isfinite(got.astype(np.float32)).all(), f"{what}: non-finite output"
     err = max_abs(got, ref)
@@ -33,7 +33,7 @@ def assert_reference_rule(got, ref64, rel_thr, what=""):
 
 
 def assert_close_scaled(got, ref, tol=1e-2, what=""):
-    """BASELINE's max-abs budget for values of magnitude O(1), widened in proportion where the reference value is large:
+    """the benchmark's max-abs budget for values of magnitude O(1), widened in proportion where the reference value is large:
     |got - ref| <= tol * max(1, |ref| / 4).  The residual stream of a decoder layer reaches |x| ~ 10, where ONE f16 ulp is
     already 7.8e-3; two implementations that round at different points differ by two ulps there (1.6e-2) while agreeing
     to 5e-3 wherever |x| < 4."""

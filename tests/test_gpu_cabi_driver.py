@@ -1,4 +1,4 @@
-"""The C ABI called from compiled C++ with nothing in between (tests/cabi_driver.cc): BASELINE config 1, one tensor-core
+"""The C ABI called from compiled C++ with nothing in between (tests/cabi_driver.cc): benchmark config 1, one tensor-core
 mat_mul, one argmax and one error path, each checked against the CPU oracle inside the driver.  This is the nearest
 compilable stand-in for the Rust `impl Operator` shim (no Rust toolchain in this environment)."""
 import os

@@ -3,14 +3,14 @@
 The layer driver (operators-rs_b200/layer.py) strings the operators together in ways no single-operator test
 exercises: the residual folded into the O and down projections with beta = 1, rope and attention on strided views
 of the fused QKV buffer, swiglu on the two halves of one buffer whose first half then feeds the down projection as
-an A operand with row stride 2*ffn.  Here that chain runs at the full width of BASELINE config 3 (d 4096, 32/8
+an A operand with row stride 2*ffn.  Here that chain runs at the full width of benchmark config 3 (d 4096, 32/8
 heads, dh 128, ffn 14336) and is compared with the oracle's chain of the restated common_cpu operators
 (oracle.decoder_layer; attention follows operators/src/attention/operator.rs:136-277).
 
 Also here: the gate|up and down projections and the causal softmax at their full config-2/3 sizes, checked on
 sampled rows (rows of a product and of a softmax are independent, so the oracle only needs the sampled ones).
 
-Tolerance: max-abs 1e-2 on f16 outputs (BASELINE's budget; one f16 ulp is 2e-3 at |x| in [2,4)); where outputs grow
+Tolerance: max-abs 1e-2 on f16 outputs (the benchmark's budget; one f16 ulp is 2e-3 at |x| in [2,4)); where outputs grow
 beyond |x| = 4 (the residual stream, the twice-accumulated down projection) the budget widens in proportion to |x|.
 """
 import importlib

@@ -3,7 +3,7 @@
 mat_mul: the reference's test shapes (batch 4, k 2048, n 5632, m in {1,7,64,255,1024}, alpha 0.5,
 beta 1; operators/src/mat_mul/cuda/mod.rs:137-254), every operand-major combination, ragged edges,
 broadcast batches and layouts the tensor-core path cannot take.  attention: the reference's shape
-(nh 32, nkvh 4, seq 7, att 127, dh 64; operators/src/attention/cuda.rs:75-159), BASELINE config 2 at
+(nh 32, nkvh 4, seq 7, att 127, dh 64; operators/src/attention/cuda.rs:75-159), benchmark config 2 at
 reduced and full size.  Tolerances are written at each assert.
 """
 import numpy as np
@@ -42,7 +42,7 @@ def gemm_case(pkg, orc, synth, dev, batch, m, n, k, a_t, b_t, c_t, alpha, beta, 
     torch.cuda.synchronize()
     assert mm.status() == 0, f"tensor-core kernel reported a timed-out wait: {mm.status()}"
     got = cd.cpu().numpy()
-    # f16 output of magnitude ~1-3: one f16 ulp is up to 2e-3; 1e-2 is the BASELINE budget
+    # f16 output of magnitude ~1-3: one f16 ulp is up to 2e-3; 1e-2 is the benchmark's budget
     assert_close(got, nc, 1e-2, f"mat_mul m{m} n{n} k{k}")
     return got, nc
 
@@ -70,6 +70,15 @@ def test_mat_mul_majors(pkg, orc, synth, dev, a_t, b_t, c_t):
 def test_mat_mul_edges(pkg, orc, synth, dev, m, n, k):
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, False, False, 1.0, 0.0, seed=30)
     gemm_case(pkg, orc, synth, dev, None, m, n, k, False, True, False, 1.0, 1.0, seed=40)
+
+
+@pytest.mark.parametrize("batch,m,n,k", [(None, 1024, 5120, 2048), (None, 1152, 4864, 3000), (None, 1536, 4096, 2560), (5, 512, 2048, 2304)])
+def test_mat_mul_remainder_wave_after_full_waves(pkg, orc, synth, dev, batch, m, n, k):
+    # more tiles than SMs with a partial last wave (160, 171, 192 tiles; 5 x 32 batched): whole tiles for the full waves, then
+    # the remainder tiles cut along K into slices that meet in the handle's scratch; with and without the old C, ragged K,
+    # transposed B
+    gemm_case(pkg, orc, synth, dev, batch, m, n, k, False, False, False, 1.0, 0.0, seed=180)
+    gemm_case(pkg, orc, synth, dev, batch, m, n, k, False, True, False, 0.5, 1.0, seed=190)
 
 
 @pytest.mark.parametrize("m,n,k", [(1024, 2048, 12288), (256, 512, 12288), (300, 700, 16000), (1, 4096, 4096), (64, 6144, 4096), (7, 4096, 14336)])
@@ -135,7 +144,7 @@ def attention_case(pkg, orc, synth, dev, nh, nkvh, seq, att, dh, token_major, ca
         op.launch(args, torch.empty(need, dtype=torch.uint8, device=dev))
         torch.cuda.synchronize()
         assert op.status() == 0, f"a bounded wait ran out: {op.status()}"
-        # outputs are convex combinations of N(0,1) values: |o| < ~4, f16 ulp <= 2e-3; BASELINE budget 1e-2
+        # outputs are convex combinations of N(0,1) values: |o| < ~4, f16 ulp <= 2e-3; benchmark budget 1e-2
         assert_close(od.cpu().numpy(), on, 1e-2, f"attention ({algo})")
         fused_ran = algo == "fused" and dh in (64, 128)
         if not token_major and not fused_ran:  # head-major q merges (nh, seq): the chain overwrites q with the result, like the crate
@@ -198,7 +207,7 @@ def test_attention_workspace_fallback(pkg, orc, synth, dev):
 
 
 def test_attention_config2_prefill(pkg, orc, synth, dev):
-    # BASELINE config 2 at full size: q [32,2048,128], k/v [8,2048,128]; the oracle runs the whole thing (a few seconds)
+    # benchmark config 2 at full size: q [32,2048,128], k/v [8,2048,128]; the oracle runs the whole thing (a few seconds)
     attention_case(pkg, orc, synth, dev, 32, 8, 2048, 2048, 128, False, seed=0xB2000020)
 
 

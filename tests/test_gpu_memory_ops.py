@@ -1,8 +1,8 @@
 """GPU parity of the memory-bound operators against the CPU oracle, through the C ABI.
 
-Shapes: BASELINE config 1 (the CPU-runnable chain), the shapes of the reference's own tests
+Shapes: benchmark config 1 (the CPU-runnable chain), the shapes of the reference's own tests
 (operators/src/<op>/cuda/mod.rs test_compute), ragged/strided/edge cases, and a full-size slice of the
-Llama-3-8B-shaped layer.  Tolerance: max-abs 1e-2 on f16 outputs vs the f16 oracle (BASELINE), plus the
+Llama-3-8B-shaped layer.  Tolerance: max-abs 1e-2 on f16 outputs vs the f16 oracle (the benchmark's budget), plus the
 reference's own outlier rule vs an f64 oracle run.  rearrange is bit-exact.
 """
 import numpy as np

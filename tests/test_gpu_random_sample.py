@@ -1,7 +1,7 @@
 """GPU parity of random_sample against the CPU oracle, through the C ABI: BIT-EXACT (index and value bits).
 
 Shapes: the reference's test (n = 32000 f32, argmax and t=0.9/p=0.9/k=200/seed=0.75;
-operators/src/random_sample/cuda/mod.rs:256-368) and BASELINE config 5 (64 x 128256 f16 ~N(0,3), argmax and
+operators/src/random_sample/cuda/mod.rs:256-368) and benchmark config 5 (64 x 128256 f16 ~N(0,3), argmax and
 t=0.8/p=0.9/k=50 with one seeded uniform draw per row).  Edge cases: ties (last index wins), -0/+0, NaN
 rows, tiny rows, k >= n, top_p = 1, seeds at the ends of [0,1).
 """
@@ -83,7 +83,7 @@ def test_sampling_many_equal_logits(pkg, orc, dev):
 
 
 def test_config5_batched(pkg, orc, synth, dev):
-    # BASELINE config 5: 64 rows x 128256 f16 ~N(0,3); argmax, then t=0.8 / top_p=0.9 / top_k=50 with a seeded draw per row
+    # benchmark config 5: 64 rows x 128256 f16 ~N(0,3); argmax, then t=0.8 / top_p=0.9 / top_k=50 with a seeded draw per row
     rows, n = 64, 128256
     lg = synth.normal(0xB2000050, (rows, n), 3.0).astype(np.float16)
     seeds = synth.uniform01(0xB2000051, (rows,))

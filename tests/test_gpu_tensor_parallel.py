@@ -1,7 +1,7 @@
 """Multi-GPU parity: all_reduce (NCCL and the NVLink peer-to-peer kernels) and the tensor-parallel layer, one process
 per GPU.  Skipped with fewer than 2 GPUs.  The oracle sums f16 partials in the crate's pairwise tree
 (operators/src/all_reduce/common_cpu.rs:66-145); the GPU paths accumulate in f32 and round once, so agreement is to f16
-rounding: max-abs <= 1e-2 (BASELINE's budget) for partials ~N(0,1)/sqrt(p) whose sum is ~N(0,1); the peer-to-peer
+rounding: max-abs <= 1e-2 (the benchmark's budget) for partials ~N(0,1)/sqrt(p) whose sum is ~N(0,1); the peer-to-peer
 kernels are additionally checked bit for bit against their own specification (f32 sum in rank order, one rounding).
 """
 import importlib
@@ -170,7 +170,7 @@ def test_all_reduce_and_tp_layer(tmp_path, orc, synth, world):
             for o in outs[1:]:
                 np.testing.assert_array_equal(o.view(np.uint16), outs[0].view(np.uint16))  # every rank holds the same bits
             # the oracle rounds to f16 after each of its log2(p) tree levels (up to 2e-3 per level at |x| in [4,8)); the GPU
-            # paths round once: BASELINE's max-abs 1e-2 budget covers three levels at p = 8
+            # paths round once: the benchmark's max-abs 1e-2 budget covers three levels at p = 8
             assert float(np.abs(outs[0].astype(np.float32) - ref.astype(np.float32)).max()) <= 1e-2, (T, name)
             if name in ("one_shot", "two_shot"):
                 np.testing.assert_array_equal(outs[0].view(np.uint16), acc.astype(np.float16).view(np.uint16))
