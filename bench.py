@@ -92,13 +92,16 @@ except Exception:
     h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[2]))
 out = open(sys.argv[3], "w", buffering=1)
 out.write("max %d\n" % nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+n, w = 0, 0.0
 while True:
     try:
-        out.write("%.6f %d %.1f %d\n" % (time.monotonic(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
-                                          nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+        if n % 8 == 0:
+            w = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+        out.write("%.6f %d %.1f %d\n" % (time.monotonic(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), w, nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
     except Exception:
         pass
-    time.sleep(0.001)
+    n += 1
+    time.sleep(0.0005)
 """
 
 
@@ -106,7 +109,8 @@ class ClockSampler:
     """SM clock, power and throttle reasons of one GPU DURING a timed region.  A child process polls NVML (read-only queries)
     about every millisecond from the start of the run and stamps every sample with the system-wide monotonic clock; a
     ClockSampler object is a window [construction, stop()) over that log.  (A thread in this process cannot do it: the
-    launch loop holds the interpreter lock.)"""
+    launch loop holds the interpreter lock.  While the GPU is saturated with launches the driver answers an NVML query in
+    tens of milliseconds, so a 30 ms region yields one to three samples; the seconds-long sustained legs yield thousands.)"""
     REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
     _proc, _path = None, None
 

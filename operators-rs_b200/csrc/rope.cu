@@ -23,7 +23,7 @@ struct RopeDivisors {
 
 // `toks` tokens per CTA: the sin/cos pairs of all of them are computed first, one per thread (one token per CTA left three
 // quarters of a 256-thread CTA idle through the sincosf latency, which then bounded the launch, not HBM), then the CTA
-// streams the tokens' rows with several 128-bit accesses in flight per thread.
+// streams the tokens' rows (few registers on purpose: eight CTAs per SM hide the latency of each other's phases).
 template <class E, class P>
 __global__ void __launch_bounds__(256) rope_f16_kernel(E *__restrict__ t, long long st, long long sh, const P *__restrict__ pos,
                                                        long long sp, int nt, int toks, int nh, int half_dh,
@@ -42,36 +42,21 @@ __global__ void __launch_bounds__(256) rope_f16_kernel(E *__restrict__ t, long l
   const int vec_per_head = half_dh >> 2;  // 4 pairs = 8 halves per vector
   const int per_tok = nh * vec_per_head;
   const int total = here * per_tok;
-  constexpr int UN = 4;
-  for (int v0 = threadIdx.x; v0 < total; v0 += UN * blockDim.x) {
-    Vec8<E> in[UN];
-    E *ptr[UN];
-    int tab[UN];
+  for (int v = threadIdx.x; v < total; v += blockDim.x) {
+    const int tk = v / per_tok, r = v - tk * per_tok;
+    const int head = r / vec_per_head, kv = r - head * vec_per_head;
+    E *ptr = byte_off(byte_off(t, (tok0 + tk) * st), (long long)head * sh) + kv * 8;
+    const float2 *tab = sincos_tab + tk * half_dh + kv * 4;
+    Vec8<E> in, out;
+    in.u = ld_global_16(ptr);
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int v = v0 + u * blockDim.x;
-      if (v < total) {
-        const int tk = v / per_tok, r = v - tk * per_tok;
-        const int head = r / vec_per_head, kv = r - head * vec_per_head;
-        ptr[u] = byte_off(byte_off(t, (tok0 + tk) * st), (long long)head * sh) + kv * 8;
-        tab[u] = tk * half_dh + kv * 4;
-        in[u].u = ld_global_16(ptr[u]);
-      }
+    for (int e = 0; e < 4; ++e) {
+      const float2 sc = tab[e];
+      const float a = to_f32(in.h[2 * e]), b = to_f32(in.h[2 * e + 1]);
+      out.h[2 * e] = from_f32<E>(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
+      out.h[2 * e + 1] = from_f32<E>(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
     }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      if (v0 + u * blockDim.x < total) {
-        Vec8<E> out;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 sc = sincos_tab[tab[u] + e];
-          const float a = to_f32(in[u].h[2 * e]), b = to_f32(in[u].h[2 * e + 1]);
-          out.h[2 * e] = from_f32<E>(__fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x)));
-          out.h[2 * e + 1] = from_f32<E>(__fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y)));
-        }
-        st_global_16(ptr[u], out.u);
-      }
-    }
+    st_global_16(ptr, out.u);
   }
 }
 
