@@ -673,6 +673,48 @@ def main():
             gathered = [torch.empty_like(outp) for _ in range(tp)]
             dist.all_gather(gathered, outp)
             identical = all(bool(torch.equal(gathered[0], t_)) for t_ in gathered[1:])
+        # the collectives themselves, with data whose sums are exact in f16 (small integers): every algorithm of
+        # all_reduce, the residual-folding form, and broadcast must reproduce the expected bits on every rank
+        collectives = None
+        if dist is not None and comm is not None:
+            try:
+                n_el = 1 << 20
+                base = torch.arange(n_el, device=device, dtype=torch.int32) % 64
+                mine = (base + rank).half()
+                expect = (tp * base + tp * (tp - 1) // 2).half()
+                flags = {}
+                ar = pkg.AllReduce(comm)
+                p2p = args.all_reduce != "nccl"
+                for nm, alg in (("nccl", pkg.ALL_REDUCE_NCCL), ("one_shot", pkg.ALL_REDUCE_P2P_ONE_SHOT), ("two_shot", pkg.ALL_REDUCE_P2P_TWO_SHOT),
+                                ("auto", pkg.ALL_REDUCE_AUTO)):
+                    if not p2p and nm in ("one_shot", "two_shot"):
+                        continue
+                    dstc = torch.zeros_like(mine)
+                    ar.set_algo(alg)
+                    ar.launch(pkg.AllReduceArgs.of(dstc, mine))
+                    torch.cuda.synchronize()
+                    flags["all_reduce_" + nm] = bool(torch.equal(dstc, expect))
+                if p2p:
+                    resid = (base % 7).half()
+                    dstc = resid.clone()
+                    ar.launch_add(pkg.AllReduceArgs.of(dstc, mine))
+                    torch.cuda.synchronize()
+                    flags["all_reduce_add"] = bool(torch.equal(dstc, (tp * base + tp * (tp - 1) // 2 + base % 7).half()))
+                root = tp - 1
+                bsrc = (base + 3).half() if rank == root else torch.zeros(n_el, dtype=torch.float16, device=device)
+                bdst = torch.zeros_like(bsrc)
+                pkg.Broadcast(comm).launch(pkg.BroadcastArgs.of(bdst, bsrc, root))
+                torch.cuda.synchronize()
+                flags["broadcast"] = bool(torch.equal(bdst, (base + 3).half()))
+                keys = sorted(flags)
+                vec = torch.tensor([1 if flags[k_] else 0 for k_ in keys], device=device, dtype=torch.int32)
+                dist.all_reduce(vec, op=dist.ReduceOp.MIN)
+                collectives = {k_: bool(v_) for k_, v_ in zip(keys, vec.cpu().tolist())}
+                collectives["elements"] = n_el
+                identical = identical and all(v_ for k_, v_ in collectives.items() if k_ != "elements")
+            except Exception as e:  # a failing collective must show in the line, not take the line away
+                collectives = {"error": repr(e)[:300]}
+                identical = False
         status = {"mat_mul": layer.mat_mul.status(), "attention": layer.attention.status(), "p2p": comm.p2p_status() if (comm and args.all_reduce != "nccl") else 0}
         if rank == 0:
             orc = graft.load_oracle()
@@ -693,6 +735,8 @@ def main():
                               "stream reaches |x| ~ 10-15, where one f16 ulp is already 7.8e-3",
                       "ok": bool(scaled <= 2e-2 and identical), "ranks_identical": identical,
                       "against": "CPU oracle chain (restated common_cpu operators) on the same shards", "kernel_status": status}
+            if collectives is not None:
+                parity["collectives_bit_exact_on_every_rank"] = collectives
     del full
 
     # per-operator durations (this rank), averaged over the marked steps

@@ -576,10 +576,15 @@ OPS_API int ops_all_reduce_scheme(ops_all_reduce *op, const ops_all_reduce_args 
 // behind NVSwitch (max over ranks, back-to-back calls): the one-shot kernel wins while the message is latency-bound, NCCL
 // in the middle, and from a few MiB the two-shot kernel, whose NVLink traffic (2 (p-1)/p S per rank) matches NCCL's with
 // fewer synchronisation rounds.
+// Measured on this machine (f16 sums; microseconds for 8 KiB / 512 KiB / 4 MiB / 32 MiB):
+//   2 ranks: NCCL 13.7 / 12.6 / 38.8 / 81.5, one-shot 14.4 / 22.6 / 42.8 / -, two-shot (staged) 22.1 / 37.5 / 42.1 / 100
+//   8 ranks: NCCL 27.2 / 30.6 / 54.7 / 158,  one-shot 15.3 / 28.4 / 69.8 / -, two-shot (staged) 24.0 / 47.3 / 56.3 / 140
+// (the zero-copy two-shot with the residual folded in, which a caller reaches through ops_all_reduce_add_launch, runs
+// 32 MiB in 82 us on 2 ranks and 123 us on 8).
 static int choose_algo(int p, usz bytes) {
-  if (bytes <= (usz)(64 << 10)) return OPS_ALL_REDUCE_P2P_ONE_SHOT;
-  if (p <= 2 && bytes <= (usz)(1 << 20)) return OPS_ALL_REDUCE_P2P_ONE_SHOT;  // with one peer one-shot moves no more bytes than two-shot
-  if (bytes >= (usz)(4 << 20) && p >= 8) return OPS_ALL_REDUCE_P2P_TWO_SHOT;
+  if (p <= 2) return bytes <= (usz)(16 << 10) ? OPS_ALL_REDUCE_P2P_ONE_SHOT : OPS_ALL_REDUCE_NCCL;
+  if (bytes <= (usz)(p >= 8 ? (1 << 20) : (256 << 10))) return OPS_ALL_REDUCE_P2P_ONE_SHOT;
+  if (bytes >= (usz)(p >= 8 ? (8 << 20) : (16 << 20))) return OPS_ALL_REDUCE_P2P_TWO_SHOT;
   return OPS_ALL_REDUCE_NCCL;
 }
 
