@@ -498,6 +498,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--sustain-seconds", type=float, default=2.0)
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
+    ap.add_argument("--no-nvls", action="store_true", help="tensor parallel: do not use the in-switch (multimem) reduction even where NVLink multicast is available")
     ap.add_argument("--no-direct", action="store_true", help="tensor parallel: stage the partials instead of the zero-copy exchange with the residual folded in")
     ap.add_argument("--pipeline", type=int, default=1, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
     ap.add_argument("--overlap-chunks", type=int, default=1, help="token chunks of the row-parallel projections whose all_reduce overlaps the next chunk's GEMM")
@@ -523,6 +524,7 @@ def main():
     device = torch.device("cuda", local_rank)
     ClockSampler.start_poller(local_rank)  # long before the first timed region: its first samples take a moment
     comms = []
+    nvls_region, nvls_keep = None, None
     dist = None
     pipeline = max(1, args.pipeline) if (tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct and args.overlap_chunks == 1) else 1
     if world > 1:
@@ -537,6 +539,23 @@ def main():
             handles = [None] * world
             dist.all_gather_object(handles, handle)
             c.p2p_attach(handles)
+            # In-switch reduction when this box offers NVLink multicast: torch's symmetric memory makes and binds the
+            # multicast object (plumbing); the reduction itself is this library's multimem kernel.  Every rank must agree.
+            if args.all_reduce == "auto" and not args.no_direct and not args.no_nvls:
+                mc_ptr, symm_buf, symm_hdl = 0, None, None
+                try:
+                    import torch.distributed._symmetric_memory as symm_mem
+                    symm_buf = symm_mem.empty(2 * args.tokens * CFG["d"] * 2, dtype=torch.uint8, device=device)
+                    symm_hdl = symm_mem.rendezvous(symm_buf, dist.group.WORLD)
+                    mc_ptr = int(symm_hdl.multicast_ptr or 0)
+                except Exception as e:
+                    print(f"bench: rank {rank}: no multicast buffer ({e!r}); peer-to-peer exchange instead", file=sys.stderr)
+                    mc_ptr = 0
+                agree = torch.tensor([1 if mc_ptr else 0], device=device, dtype=torch.int32)
+                dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+                if int(agree.item()):
+                    nvls_region = c.nvls_attach(mc_ptr, symm_buf).view(torch.float16)
+                    nvls_keep = (symm_buf, symm_hdl)
         comms.append(c)
     comm = comms[0] if comms else None
     algo = {"auto": pkg.ALL_REDUCE_AUTO, "nccl": pkg.ALL_REDUCE_NCCL, "one_shot": pkg.ALL_REDUCE_P2P_ONE_SHOT,
@@ -548,7 +567,7 @@ def main():
     shard = layer_mod.shard_weights(full, rank, tp, cfg) if tp > 1 else full
     direct = tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct
     layer = layer_mod.DecoderLayer(cfg, shard, T, device, comm=comm, tp=tp, rank=rank, all_reduce_algo=algo, overlap_chunks=args.overlap_chunks,
-                                   fused_all_reduce=args.all_reduce == "fused", direct=direct, pipeline=pipeline)
+                                   fused_all_reduce=args.all_reduce == "fused", direct=direct, pipeline=pipeline, direct_region=nvls_region)
     g = torch.Generator(device=device).manual_seed(SEED + 7)
     x0 = torch.randn(T, CFG["d"], generator=g, device=device, dtype=torch.float32).half()
     x = torch.empty_like(x0)
@@ -700,6 +719,17 @@ def main():
                     ar.launch_add(pkg.AllReduceArgs.of(dstc, mine))
                     torch.cuda.synchronize()
                     flags["all_reduce_add"] = bool(torch.equal(dstc, (tp * base + tp * (tp - 1) // 2 + base % 7).half()))
+                if nvls_region is not None:  # the same two through the in-switch reduction (src inside the multicast buffer)
+                    reg = nvls_region[:n_el]
+                    reg.copy_(mine)
+                    dstc = torch.zeros_like(mine)
+                    ar.launch(pkg.AllReduceArgs.of(dstc, reg))
+                    torch.cuda.synchronize()
+                    flags["all_reduce_nvls"] = bool(torch.equal(dstc, expect))
+                    dstc = (base % 7).half()
+                    ar.launch_add(pkg.AllReduceArgs.of(dstc, reg))
+                    torch.cuda.synchronize()
+                    flags["all_reduce_add_nvls"] = bool(torch.equal(dstc, (tp * base + tp * (tp - 1) // 2 + base % 7).half()))
                 root = tp - 1
                 bsrc = (base + 3).half() if rank == root else torch.zeros(n_el, dtype=torch.float16, device=device)
                 bdst = torch.zeros_like(bsrc)
@@ -813,7 +843,8 @@ def main():
         "metric": "layer_tokens_per_s", "value": T * args.steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic", "config": config,
-        "run": {"all_reduce": args.all_reduce if tp > 1 else None, "exchange": ("zero-copy partials + residual folded into the all_reduce kernel" if direct else "staged") if tp > 1 else None,
+        "run": {"all_reduce": args.all_reduce if tp > 1 else None, "exchange": (("in-switch reduction (multimem.ld_reduce / multimem.st on an NVLink multicast buffer), " if nvls_region is not None else "peer-to-peer two-shot kernel, ")
+                                                                               + "zero-copy partials + residual folded into the all_reduce kernel" if direct else "staged") if tp > 1 else None,
                 "pipeline_chunks": pipeline if tp > 1 else None,
                 "attention": "fused flash-attention kernel behind attention::Args (the crate's operator chain is measured in other_configs)",
                 "ms_per_step_with_per_operator_events": marked_ms / args.steps, "clocks_of_per_operator_pass": clocks_marked},

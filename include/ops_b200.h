@@ -360,6 +360,14 @@ int ops_comm_p2p_reset(ops_comm *c);
  * there — the same offset on every rank — lets ops_all_reduce_launch / ops_all_reduce_add_launch read
  * it in place when given that pointer as src: no copy-in.  No counterpart in the crate. */
 int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out);
+/* In-switch reduction (NVLS).  `local` is this rank's address of a buffer of `bytes` bytes that the caller has bound to an
+ * NVLink multicast object together with the same-sized buffers of every rank, `multicast` its multicast address (how the
+ * object is made is the caller's business: the CUDA driver's cuMulticast* calls, or a library that wraps them).  The
+ * first half of the buffer then serves as a zero-copy input region like the one above: an all_reduce (or all_reduce_add)
+ * whose src lies there is summed inside the NVSwitch with multimem.ld_reduce and delivered with multimem.st; the second
+ * half is scratch.  Needs ops_comm_p2p_attach first (the ranks synchronise through its flags).  Nulls detach.
+ * No counterpart in the crate. */
+int ops_comm_nvls_attach(ops_comm *c, void *multicast, void *local, size_t bytes);
 /* Test aid with no counterpart in the crate: a communicator of `group_size` ranks that all map this rank's own staging
  * buffer.  Its peers never run, so a peer-to-peer all_reduce on it ends through its bounded waits (about one second)
  * with a non-zero ops_comm_p2p_status and an intact context: the time-out path can be exercised on one GPU. */

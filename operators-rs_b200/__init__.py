@@ -708,6 +708,19 @@ class Comm:
         self._direct_owner = t
         return t if dtype is None else t.view(dtype)
 
+    def nvls_attach(self, multicast_ptr, local_tensor):
+        """ops_comm_nvls_attach: `local_tensor` (uint8, this rank's part of a buffer bound to an NVLink multicast object whose
+        multicast address is `multicast_ptr`) becomes [zero-copy input region | scratch] of the in-switch all_reduce.
+        Returns the input region as a tensor view (first half)."""
+        n = local_tensor.numel() * local_tensor.element_size()
+        _check(lib().ops_comm_nvls_attach(self._h, ctypes.c_void_p(int(multicast_ptr)), ctypes.c_void_p(local_tensor.data_ptr()), ctypes.c_size_t(n)), False)
+        self._nvls_owner = local_tensor
+        return local_tensor.view(-1)[: n // 2] if local_tensor.dtype.itemsize == 1 else local_tensor.view(-1).view(__import__("torch").uint8)[: n // 2]
+
+    def nvls_detach(self):
+        _check(lib().ops_comm_nvls_attach(self._h, ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_size_t(0)), False)
+        self._nvls_owner = None
+
     def destroy(self):
         h, self._h = self._h, None
         if h and h.value:
@@ -763,6 +776,6 @@ EXPORTS = [
     "ops_random_sample_batched_workspace", "ops_random_sample_launch_batched",
     "ops_random_sample_noalloc_max_logits", "ops_random_sample_launch_noalloc", "ops_comm_unique_id",
     "ops_comm_init_rank", "ops_comm_rank", "ops_comm_group_size", "ops_comm_destroy", "ops_comm_p2p_export",
-    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_comm_p2p_reset", "ops_comm_p2p_direct", "ops_all_reduce_add_launch",
+    "ops_comm_p2p_attach", "ops_comm_p2p_status", "ops_comm_p2p_reset", "ops_comm_p2p_direct", "ops_comm_nvls_attach", "ops_all_reduce_add_launch",
     "ops_rms_norm_add_launch", "ops_comm_create_loopback", "ops_all_reduce_set_algo", "ops_add_rows_status", "ops_mat_mul_all_reduce_launch",
 ]

@@ -325,6 +325,129 @@ __global__ void __maxnreg__(104) all_reduce_two_shot_kernel(const __grid_constan
   if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
 }
 
+// ------------------------------------------------------------------------------------------------
+// In-switch reduction (NVLS).  The partial of every rank lies in the "in" half of a buffer bound to an NVLink multicast
+// object, at the same offset.  Rank r owns the r-th 1/p of the message: one `multimem.ld_reduce` per 16 bytes returns the
+// sum over ALL ranks, added up inside the NVSwitch (f32 accumulation), so a rank's links carry its own part once instead
+// of p-1 peer copies; the result (plus the replicated residual, ADD) goes out with one `multimem.st`, which the switch
+// delivers to the "out" half of every rank.  After a second flag round every rank copies "out" to dst from its own HBM.
+// Per rank and direction about S bytes cross NVLink, against 2 (p-1)/p S of the peer-to-peer two-shot kernel.
+// Flags and epochs are those of the peer-to-peer staging buffer (same-index CTAs meet pairwise, every wait bounded).
+// ------------------------------------------------------------------------------------------------
+template <class T> struct Multimem;
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st_16(void *mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+struct NvlsArgs {
+  char *mc_in, *mc_out;          // multicast addresses of the message inside the "in" and "out" halves
+  const char *local_out;         // this rank's copy of the same place in "out"
+};
+
+template <class T, bool ADD>
+__global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(const __grid_constant__ P2PKernelArgs a, const __grid_constant__ NvlsArgs nv,
+                                                                               uint4 *__restrict__ dst, long long vecs, long long part_vecs) {
+  constexpr int U = 8;
+  const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
+  const long long per = (part_vecs + gridDim.x - 1) / gridDim.x;
+  const long long s_lo = (long long)blockIdx.x * per, s_hi = min(part_vecs, s_lo + per);
+  const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
+  bool ok = true;
+  // every rank's partial is in place (written by the kernel before this one on the same stream)
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < a.size) {
+    P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
+    st_release_sys(&pf->ready[a.rank][blockIdx.x], epoch);
+  }
+  ok = wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 4);
+  if (ok) {
+    const long long base = (long long)a.rank * part_vecs;
+    const long long stop = min(s_hi, vecs - base);
+    const uint4 *mc_in = reinterpret_cast<const uint4 *>(nv.mc_in) + base;
+    uint4 *mc_out = reinterpret_cast<uint4 *>(nv.mc_out) + base;
+    for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {
+      uint4 sum[U], old[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+        if (v < stop) {
+          sum[u] = Multimem<T>::ld_reduce(mc_in + v);
+          if constexpr (ADD) old[u] = dst[base + v];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+        if (v < stop) {
+          uint4 r = sum[u];
+          if constexpr (ADD) {
+            float acc[Acc8<T>::N] = {};
+            Acc8<T>::add(acc, old[u]);
+            Acc8<T>::add(acc, sum[u]);
+            r = Acc8<T>::pack(acc);
+          }
+          multimem_st_16(mc_out + v, r);
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < a.size) {
+      P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
+      st_release_sys(&pf->reduced[a.rank][blockIdx.x], epoch);
+    }
+    ok = wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 5);
+  }
+  if (ok) {
+    // every part, slice b: from this rank's own copy of "out" to dst
+    const uint4 *lo = reinterpret_cast<const uint4 *>(nv.local_out);
+    for (int part = 0; part < a.size; ++part) {
+      const long long base = (long long)part * part_vecs;
+      const long long stop = min(s_hi, vecs - base);
+      for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {
+        uint4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          if (v < stop) r[u] = ld_peer_16(lo + base + v);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          if (v < stop) dst[base + v] = r[u];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
+}
+
 struct AllReduceMeta {
   uint32_t dt;
   usz len;  // elements
@@ -611,6 +734,17 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     if (ctas > c->sm_count) ctas = c->sm_count;  // every CTA must be resident: same-index CTAs of different ranks wait for each other
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
+    // in-switch reduction: the partial lies in the "in" half of the attached multicast buffer
+    if (c->nvls_mc && (const char *)src >= c->nvls_local && (const char *)src + bytes <= c->nvls_local + c->nvls_region) {
+      const size_t off = (size_t)((const char *)src - c->nvls_local);
+      NvlsArgs nv;
+      nv.mc_in = c->nvls_mc + off;
+      nv.mc_out = c->nvls_mc + c->nvls_region + off;
+      nv.local_out = c->nvls_local + c->nvls_region + off;
+      if (add) all_reduce_nvls_kernel<T, true><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, nv, (uint4 *)dst, vecs, part);
+      else all_reduce_nvls_kernel<T, false><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, nv, (uint4 *)dst, vecs, part);
+      return check_launch("all_reduce(nvls)");
+    }
     // zero-copy: the partial already lies in this rank's direct region (the producing kernel wrote it there)
     const char *direct = region_direct(c->peers[c->rank], c->region_bytes);
     const bool in_direct = (const char *)src >= direct && (const char *)src + bytes <= direct + c->region_bytes;
@@ -662,6 +796,9 @@ static int all_reduce_impl(const ops_all_reduce *op, const ops_all_reduce_args *
       return fail(OPS_ARGS_NOT_SUPPORT, "all_reduce_add: needs >= 2 ranks, an attached staging buffer of >= %zu bytes, f16/bf16/f32 Sum, 16-byte aligned data", bytes);
     algo = OPS_ALL_REDUCE_P2P_TWO_SHOT;
   }
+  // a partial that already lies in the attached multicast buffer is reduced inside the switch whatever its size
+  const bool in_nvls = c->nvls_mc && (const char *)src >= c->nvls_local && (const char *)src + bytes <= c->nvls_local + c->nvls_region;
+  if (algo == OPS_ALL_REDUCE_AUTO && in_nvls && p2p_able) algo = OPS_ALL_REDUCE_P2P_TWO_SHOT;
   if (algo == OPS_ALL_REDUCE_AUTO) algo = p2p_able ? choose_algo(c->size, bytes) : OPS_ALL_REDUCE_NCCL;
   if (algo == OPS_ALL_REDUCE_NCCL) {
     if (!c->has_nccl) return fail(OPS_EXECUTION_FAILED, "all_reduce: communicator has no NCCL handle");
@@ -697,6 +834,26 @@ OPS_API int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out) 
   if (!c || !c->staging) return fail(OPS_ARGS_NOT_SUPPORT, "p2p: no staging buffer exported");
   if (ptr_out) *ptr_out = region_direct(c->staging, c->region_bytes);
   if (bytes_out) *bytes_out = c->region_bytes;
+  return OPS_OK;
+}
+
+// In-switch reduction: `local` is this rank's address of a buffer of `bytes` bytes that the caller has bound to an NVLink
+// multicast object together with the same-sized buffers of all ranks (same order of ranks as this communicator), `multicast`
+// its multicast address.  The first half is the zero-copy input region (what ops_comm_p2p_direct is to the peer-to-peer
+// kernels): an all_reduce whose src lies there is reduced inside the switch.  The second half is scratch.  Needs the
+// peer-to-peer staging buffer attached as well (its flags synchronise the ranks).  Pass nulls to detach.
+OPS_API int ops_comm_nvls_attach(ops_comm *c, void *multicast, void *local, size_t bytes) {
+  if (!c) return fail(OPS_ARGS_NOT_SUPPORT, "null communicator");
+  if (!multicast || !local || bytes == 0) {
+    c->nvls_mc = c->nvls_local = nullptr;
+    c->nvls_region = 0;
+    return OPS_OK;
+  }
+  if (!c->p2p_ready) return fail(OPS_ARGS_NOT_SUPPORT, "nvls: attach the peer-to-peer staging buffer first");
+  if (!aligned(multicast, 16) || !aligned(local, 16) || bytes % 512) return fail(OPS_ARGS_NOT_SUPPORT, "nvls: 16-byte aligned addresses and a multiple of 512 bytes expected");
+  c->nvls_mc = (char *)multicast;
+  c->nvls_local = (char *)local;
+  c->nvls_region = bytes / 2;
   return OPS_OK;
 }
 

@@ -69,6 +69,10 @@ struct ops_comm {
   bool loopback;               // every peer entry is the own buffer (time-out tests on one GPU)
   int *status_dev;
   int sm_count;
+  // NVLS: a buffer of 2 * nvls_region bytes ([in | out]) that the caller has bound to an NVLink multicast object — the
+  // same offsets on every rank; nvls_mc is its multicast address (multimem instructions), nvls_local this rank's own copy
+  char *nvls_mc, *nvls_local;
+  size_t nvls_region;
 };
 
 namespace ops {

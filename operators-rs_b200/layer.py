@@ -102,7 +102,7 @@ class DecoderLayer:
     PIPELINE_MIN_ROWS = 256  # rows per chunk below which cutting the tail does not pay
 
     def __init__(self, cfg, weights, max_tokens, device, comm=None, tp=1, rank=0, all_reduce_algo=ALL_REDUCE_AUTO, overlap_chunks=1,
-                 fused_all_reduce=False, direct=True, pipeline=1):
+                 fused_all_reduce=False, direct=True, pipeline=1, direct_region=None):
         import torch
         self.overlap_chunks = max(1, int(overlap_chunks))
         self.fused_all_reduce = bool(fused_all_reduce) and tp > 1  # row-parallel GEMM and its all_reduce as one kernel
@@ -115,10 +115,15 @@ class DecoderLayer:
         if tp > 1:
             self.all_reduce = AllReduce(comm)
             self.all_reduce.set_algo(all_reduce_algo)
-            try:
-                self.direct_buf = comm.p2p_direct(torch.float16)
-            except Exception:
-                self.direct_buf = None  # no staging attached: NCCL only
+            if direct_region is not None:
+                # the zero-copy input region of an attached NVLink multicast buffer (Comm.nvls_attach): the exchange is then
+                # reduced inside the switch
+                self.direct_buf = direct_region
+            else:
+                try:
+                    self.direct_buf = comm.p2p_direct(torch.float16)
+                except Exception:
+                    self.direct_buf = None  # no staging attached: NCCL only
         self.direct = bool(direct) and tp > 1 and not self.fused_all_reduce and self.overlap_chunks == 1 and self.direct_buf is not None
         self.pipeline = max(1, int(pipeline)) if self.direct else 1
         self.comm_stream = torch.cuda.Stream(device) if (tp > 1 and (self.overlap_chunks > 1 or self.pipeline > 1)) else None
