@@ -498,6 +498,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--sustain-seconds", type=float, default=2.0)
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
+    ap.add_argument("--nvls-min-ranks", type=int, default=4, help="tensor parallel: group size from which the in-switch reduction is used (with two ranks it "
+                    "moves as many bytes as the peer-to-peer kernel and measured slower: 135 vs 87 us per 32 MiB exchange)")
     ap.add_argument("--no-nvls", action="store_true", help="tensor parallel: do not use the in-switch (multimem) reduction even where NVLink multicast is available")
     ap.add_argument("--no-direct", action="store_true", help="tensor parallel: stage the partials instead of the zero-copy exchange with the residual folded in")
     ap.add_argument("--pipeline", type=int, default=1, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
@@ -541,7 +543,7 @@ def main():
             c.p2p_attach(handles)
             # In-switch reduction when this box offers NVLink multicast: torch's symmetric memory makes and binds the
             # multicast object (plumbing); the reduction itself is this library's multimem kernel.  Every rank must agree.
-            if args.all_reduce == "auto" and not args.no_direct and not args.no_nvls:
+            if args.all_reduce == "auto" and not args.no_direct and not args.no_nvls and world >= args.nvls_min_ranks:
                 mc_ptr, symm_buf, symm_hdl = 0, None, None
                 try:
                     import torch.distributed._symmetric_memory as symm_mem

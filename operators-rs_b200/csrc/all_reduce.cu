@@ -412,6 +412,7 @@ __global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(c
             r = Acc8<T>::pack(acc);
           }
           multimem_st_16(mc_out + v, r);
+          dst[base + v] = r;  // this rank's own part needs no trip through "out"
         }
       }
     }
@@ -424,9 +425,10 @@ __global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(c
     ok = wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 5);
   }
   if (ok) {
-    // every part, slice b: from this rank's own copy of "out" to dst
+    // every other part, slice b: from this rank's own copy of "out" to dst
     const uint4 *lo = reinterpret_cast<const uint4 *>(nv.local_out);
     for (int part = 0; part < a.size; ++part) {
+      if (part == a.rank) continue;
       const long long base = (long long)part * part_vecs;
       const long long stop = min(s_hi, vecs - base);
       for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {

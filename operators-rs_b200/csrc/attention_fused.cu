@@ -432,10 +432,13 @@ struct PairAttnArgs {
 };
 constexpr int FP_PART_LD = FP_DH + 4;  // 16-byte aligned records
 
-// key blocks of q tile `t` of pair `pair` (all of them), and the run [jb0, jb0 + len) chunk `chunk` of the pair takes
+// Key blocks of the two q tiles of pair `pair`, the number of runs the pair is cut into (longer pairs into more runs, so
+// that every run is about as long as a run of the longest pair: short pairs stay whole and write o themselves), and the
+// run [jb0, jb0 + len) that `chunk` takes (empty when chunk >= runs).
 struct FpRange {
   int nblk[2];  // blocks of each tile inside the run
   int jb0;
+  int runs;
 };
 __host__ __device__ __forceinline__ FpRange fp_range(int pair, int chunk, int chunks, int seq, int att, int causal) {
   const int off = att - seq;
@@ -447,10 +450,13 @@ __host__ __device__ __forceinline__ FpRange fp_range(int pair, int chunk, int ch
     total[t] = r0 < seq ? (k_end + FP_BN - 1) / FP_BN : 0;
   }
   const int nmax = max(total[0], total[1]);
-  const int len = (nmax + chunks - 1) / chunks;
+  const int longest = (att + FP_BN - 1) / FP_BN;            // the last pair's (or, unmasked, every pair's) block count
+  const int target = max(1, (longest + chunks - 1) / chunks);  // blocks per run of the longest pair
   FpRange r;
+  r.runs = min(chunks, max(1, (nmax + target / 2) / target));
+  const int len = (nmax + r.runs - 1) / r.runs;
   r.jb0 = chunk * len;
-  for (int t = 0; t < 2; ++t) r.nblk[t] = max(0, min(total[t], r.jb0 + len) - r.jb0);
+  for (int t = 0; t < 2; ++t) r.nblk[t] = chunk < r.runs ? max(0, min(total[t], r.jb0 + len) - r.jb0) : 0;
   return r;
 }
 
@@ -520,6 +526,7 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
   const int nblk[2] = {range.nblk[0], range.nblk[1]};
   const int jb0 = range.jb0;
   const int nmax = max(nblk[0], nblk[1]);
+  if (nmax == 0) return;  // a run beyond those this pair is cut into (CTA-uniform, before anything is set up)
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; ++t) {
@@ -741,7 +748,7 @@ __global__ void __launch_bounds__(FP_THREADS, 1)
     l_s[(t * 2 + h) * FP_BM + row_in_tile] = l;
     named_bar_sync(pair_bar, 64);
     l += l_s[(t * 2 + (h ^ 1)) * FP_BM + row_in_tile];
-    if (ok && nblk[t] > 0 && g.chunks > 1 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
+    if (ok && nblk[t] > 0 && range.runs > 1 && (ok = mbar_wait(o_final(t), 0, g.status, 142))) {
       // one run of several: park the unnormalised O with its reference point and row sum
       tc_fence_after();
       const uint32_t to = tmem_base + lane_addr + o_col(t) + (uint32_t)(h * 64);
@@ -816,20 +823,22 @@ __global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_con
   if (row_id >= (long long)g.nh * g.seq) return;
   const int head = (int)(row_id / g.seq), q_row = (int)(row_id - (long long)head * g.seq);
   const int pair = q_row / (2 * FP_BM), t = (q_row / FP_BM) & 1;
+  const int runs = fp_range(pair, 0, g.chunks, g.seq, g.att, g.causal).runs;
+  if (runs == 1) return;  // a pair that was not cut: its CTA has written o itself
   const float *prow = g.partial + row_id * g.chunks * FP_PART_LD;
   float ms[8];
   float top = -INFINITY;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     ms[c] = -INFINITY;
-    if (c < g.chunks && fp_range(pair, c, g.chunks, g.seq, g.att, g.causal).nblk[t] > 0) ms[c] = prow[c * FP_PART_LD + FP_DH];
+    if (c < runs && fp_range(pair, c, g.chunks, g.seq, g.att, g.causal).nblk[t] > 0) ms[c] = prow[c * FP_PART_LD + FP_DH];
     top = fmaxf(top, ms[c]);
   }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
-    if (c < g.chunks && ms[c] != -INFINITY) {
+    if (c < runs && ms[c] != -INFINITY) {
       const float w = fp_ex2(ms[c] - top);
       const float4 v = *reinterpret_cast<const float4 *>(prow + c * FP_PART_LD + lane * 4);
       den = fmaf(prow[c * FP_PART_LD + FP_DH + 1], w, den);
