@@ -41,7 +41,8 @@ using namespace sm100;
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;                       // 64 f16 = one 128-byte swizzle row
 constexpr int GEMM_UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 8;       // plain kernel: two epilogue warps per 32-row quarter, each half of the tile's columns
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 constexpr int GEMM_FUSED_THREADS = 448;  // + 8 warps that reduce finished tiles across ranks while the GEMM goes on
 constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr int GEMM_CHUNK_BYTES = 64 * GEMM_BK * 2;  // one 64 (MN) x 64 (K) MN-major box
@@ -71,7 +72,7 @@ struct GemmKernelArgs {
   int split_r, split_g;    // remainder tiles, slices per tile (1 = no split)
   int kb_per_slice;
   float *split_ws;         // [grid][4 quarters][BN/32 chunks][8][32 lanes] float4: a lane's 128-bit stores of one step are contiguous
-  unsigned int *split_tickets;  // [split_r][4][2] arrivals and departures per 32-row quarter, self-resetting
+  unsigned int *split_tickets;  // [split_r][4 quarters][2 column halves][2] arrivals and departures, self-resetting
 };
 
 // GEMM whose output is summed over the ranks of a tensor-parallel group inside the same kernel (row-parallel
@@ -144,7 +145,7 @@ template <int BN> struct GemmCfg {
   static constexpr int STAGES = BN == 256 ? 4 : 6;
   static constexpr int TMEM_COLS = BN == 128 ? 256 : 512;  // two accumulators of BN columns, rounded up to a power of two
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES + 256;            // after the barriers
-  static constexpr int EPI_BYTES = 4 * 32 * GEMM_EPI_LD * 4;               // one 32 x 32 f32 transposition pad per epilogue warp
+  static constexpr int EPI_BYTES = GEMM_EPI_WARPS * 16 * GEMM_EPI_LD * 4;  // one 16 x 32 f32 transposition pad per epilogue warp
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 };
 
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tmem_full_bar(b), 1);
-      mbar_init(tmem_empty_bar(b), 4);
+      mbar_init(tmem_empty_bar(b), FUSED ? 4 : GEMM_EPI_WARPS);
     }
     fence_barrier_init();
   }
@@ -275,9 +276,14 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         }
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+  } else if (warp < 2 + (FUSED ? 4 : GEMM_EPI_WARPS)) {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, plain kernel 2..9)
+    // Plain kernel: eight warps, two per 32-row quarter, warp 2 + 4h + i taking column half h of the tile — with short K
+    // (k = 128 attention products, 8-way row-parallel shards) the epilogue of four warps took longer than the mainloop.
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, +32) belong to this warp
+    const int col_half = FUSED ? 0 : (warp - 2) >> 2;
+    const int c_begin = FUSED ? 0 : col_half * (BN / 2), c_end = FUSED ? BN : c_begin + BN / 2;
+    const int qh = quarter * 2 + col_half;  // arrival counters of the K split: one per (quarter, column half)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -308,7 +314,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         constexpr int QUARTER_F4 = (BN / 32) * 8 * 32;
         float4 *mine = reinterpret_cast<float4 *>(g.split_ws) + ((long long)blockIdx.x * 4 + quarter) * QUARTER_F4 + lane;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_begin; c < c_end; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + (uint32_t)c, v);
           tmem_wait_ld();
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         }
         __threadfence();
         __syncwarp();
-        ticket = g.split_tickets + (tile_r * 4 + quarter) * 2;
+        ticket = g.split_tickets + (tile_r * 8 + qh) * 2;
         int there = 1;
         if (lane == 0) {
           atomicAdd(ticket, 1u);
@@ -339,7 +345,7 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
         part_q = reinterpret_cast<const float4 *>(g.split_ws) + (((long long)tile_r * g.split_g) * 4 + quarter) * QUARTER_F4 + lane;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN && finish; c += 32) {
+      for (int c = c_begin; c < c_end && finish; c += 32) {
         if (!FUSED && w.slice >= 0 && (c >> 5) % g.split_g != w.slice) continue;  // another slice's chunk (warp-uniform)
         uint32_t v[32];
         // interior fast path: the chunk's 32 columns are all inside C and rows are 16-byte aligned.  The old values of C
@@ -405,32 +411,40 @@ __global__ void __launch_bounds__(FUSED ? GEMM_FUSED_THREADS : GEMM_THREADS, 1)
               if (grow < g.m) oldc[it].u = ld_global_16(g.d + (long long)b * g.d_bs + (long long)grow * g.ldd + n0 + c + unit * 8);
             }
           }
-          float *pad = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) + Cfg::EPI_OFF) + (warp - 2) * 32 * GEMM_EPI_LD;
+          // the pad holds 16 rows: lanes 0-15 go first, then lanes 16-31 (half the shared memory per warp, which is what
+          // lets eight epilogue warps fit beside the four pipeline stages)
+          float *pad = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) + Cfg::EPI_OFF) + (warp - 2) * 16 * GEMM_EPI_LD;
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            *reinterpret_cast<uint4 *>(pad + lane * GEMM_EPI_LD + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          __syncwarp();
+          for (int hh = 0; hh < 2; ++hh) {
+            if ((lane >> 4) == hh) {
 #pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int rr = it * 8 + rsub, grow = tile_row0 + rr;
-            const float4 f0 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8);
-            const float4 f1 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8 + 4);
-            const float acc8[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-            Vec8<unsigned short> out;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float val = __fmul_rn(g.alpha, acc8[e]);
-              if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, h16_to_f32(oldc[it].h[e], bf)), val);
-              out.h[e] = f32_to_h16(val, bf);
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4 *>(pad + (lane & 15) * GEMM_EPI_LD + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             }
-            if (grow < g.m) {
-              unsigned short *wp;
-              if constexpr (FUSED) wp = reinterpret_cast<unsigned short *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa_epoch & 1u)) + (long long)grow * g.n;
-              else wp = g.d + (long long)b * g.d_bs + (long long)grow * g.ldd;
-              st_global_16(wp + n0 + c + unit * 8, out.u);
+            __syncwarp();
+#pragma unroll
+            for (int i2 = 0; i2 < 2; ++i2) {
+              const int it = hh * 2 + i2;
+              const int rr = i2 * 8 + rsub, grow = tile_row0 + it * 8 + rsub;
+              const float4 f0 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8);
+              const float4 f1 = *reinterpret_cast<const float4 *>(pad + rr * GEMM_EPI_LD + unit * 8 + 4);
+              const float acc8[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+              Vec8<unsigned short> out;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float val = __fmul_rn(g.alpha, acc8[e]);
+                if (g.read_c) val = __fadd_rn(__fmul_rn(g.beta, h16_to_f32(oldc[it].h[e], bf)), val);
+                out.h[e] = f32_to_h16(val, bf);
+              }
+              if (grow < g.m) {
+                unsigned short *wp;
+                if constexpr (FUSED) wp = reinterpret_cast<unsigned short *>(region_in(fa.peers[fa.rank], fa.region_bytes, fa_epoch & 1u)) + (long long)grow * g.n;
+                else wp = g.d + (long long)b * g.d_bs + (long long)grow * g.ldd;
+                st_global_16(wp + n0 + c + unit * 8, out.u);
+              }
             }
+            __syncwarp();  // the pad is rewritten by the other half / the next chunk
           }
-          __syncwarp();  // the pad is rewritten by the next chunk
         } else if (row < g.m) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -989,7 +1003,7 @@ OPS_API int ops_mat_mul_create(int device, ops_mat_mul **out) {
     delete h;
     return fail(OPS_EXECUTION_FAILED, "mat_mul: cannot allocate the status word");
   }
-  const size_t ws_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * GEMM_BM * 256 * sizeof(float), tk_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * 8 * sizeof(unsigned int);
+  const size_t ws_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * GEMM_BM * 256 * sizeof(float), tk_bytes = (size_t)GEMM_SPLIT_MAX_UNITS * 16 * sizeof(unsigned int);
   if (cudaMalloc(&h->st.split_ws, ws_bytes) != cudaSuccess || cudaMalloc(&h->st.split_tickets, tk_bytes) != cudaSuccess ||
       cudaMemset(h->st.split_tickets, 0, tk_bytes) != cudaSuccess) {
     cudaGetLastError();  // without the scratch the kernel simply runs its last wave unsplit
@@ -1026,7 +1040,7 @@ OPS_API int ops_mat_mul_status_reset(ops_mat_mul *op) {
   cudaSetDevice(op->base.device);
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemset(op->st.status_dev, 0, sizeof(int));
-  if (e == cudaSuccess && op->st.split_tickets) e = cudaMemset(op->st.split_tickets, 0, (size_t)GEMM_SPLIT_MAX_UNITS * 8 * sizeof(unsigned int));
+  if (e == cudaSuccess && op->st.split_tickets) e = cudaMemset(op->st.split_tickets, 0, (size_t)GEMM_SPLIT_MAX_UNITS * 16 * sizeof(unsigned int));
   if (e != cudaSuccess) return fail(OPS_EXECUTION_FAILED, "mat_mul status reset: %s", cudaGetErrorString(e));
   return OPS_OK;
 }
