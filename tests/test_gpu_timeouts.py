@@ -60,3 +60,14 @@ def test_status_reset_keeps_handles_usable(pkg, dev):
     mm.launch(pkg.MatMulArgs.of(c, 0.0, a, b, 1.0))
     torch.cuda.synchronize()
     assert torch.equal(first, c) and mm.status() == 0
+
+
+def test_nvls_attach_needs_attached_staging(pkg, dev):
+    # The in-switch all_reduce synchronises its ranks through the flags of the peer-to-peer staging buffer: a communicator
+    # without attached peers refuses a multicast buffer (argument error, nothing launched), and detaching is always allowed.
+    comm = pkg.Comm.loopback(0, 2, 1 << 20)
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device=dev)
+    with pytest.raises(pkg.SchemeError):
+        comm.nvls_attach(buf.data_ptr(), buf)  # not a multicast address either, but the check comes first
+    comm.nvls_detach()
+    comm.destroy()
