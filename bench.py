@@ -498,8 +498,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--sustain-seconds", type=float, default=2.0)
     ap.add_argument("--all-reduce", default="auto", choices=["auto", "nccl", "one_shot", "two_shot", "fused"])
-    ap.add_argument("--nvls-min-ranks", type=int, default=4, help="tensor parallel: group size from which the in-switch reduction is used (with two ranks it "
-                    "moves as many bytes as the peer-to-peer kernel and measured slower: 135 vs 87 us per 32 MiB exchange)")
+    ap.add_argument("--nvls-min-ranks", type=int, default=2, help="tensor parallel: group size from which the in-switch reduction is tried (the bench times both "
+                    "exchanges on the layer's message before the run and keeps the faster; with two ranks the peer-to-peer kernel measured faster: 87 vs 135 us)")
     ap.add_argument("--no-nvls", action="store_true", help="tensor parallel: do not use the in-switch (multimem) reduction even where NVLink multicast is available")
     ap.add_argument("--no-direct", action="store_true", help="tensor parallel: stage the partials instead of the zero-copy exchange with the residual folded in")
     ap.add_argument("--pipeline", type=int, default=1, help="tensor parallel: row chunks of the post-attention chain run on separate streams")
@@ -526,7 +526,7 @@ def main():
     device = torch.device("cuda", local_rank)
     ClockSampler.start_poller(local_rank)  # long before the first timed region: its first samples take a moment
     comms = []
-    nvls_region, nvls_keep = None, None
+    nvls_region, nvls_attached, nvls_keep, exchange_probe_us = None, None, None, None
     dist = None
     pipeline = max(1, args.pipeline) if (tp > 1 and args.all_reduce in ("auto", "two_shot") and not args.no_direct and args.overlap_chunks == 1) else 1
     if world > 1:
@@ -557,7 +557,31 @@ def main():
                 dist.all_reduce(agree, op=dist.ReduceOp.MIN)
                 if int(agree.item()):
                     nvls_region = c.nvls_attach(mc_ptr, symm_buf).view(torch.float16)
+                    nvls_attached = nvls_region
                     nvls_keep = (symm_buf, symm_hdl)
+                    # Which exchange is faster for this layer's message on this box and group size?  Both forms of
+                    # all_reduce_add (partial already in place, residual folded in) a few times each, slowest rank counts.
+                    n_el = args.tokens * CFG["d"]
+                    resid = torch.zeros(n_el, dtype=torch.float16, device=device)
+                    ar_probe = pkg.AllReduce(c)
+                    took = {}
+                    for nm, region in (("nvls", nvls_region), ("p2p", c.p2p_direct(torch.float16))):
+                        region[:n_el].zero_()
+                        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        for rep_ in range(6):
+                            if rep_ == 2:
+                                dist.barrier()
+                                ev0.record()
+                            ar_probe.launch_add(pkg.AllReduceArgs.of(resid, region[:n_el]))
+                        ev1.record()
+                        torch.cuda.synchronize()
+                        tt_ = torch.tensor([ev0.elapsed_time(ev1) / 4], device=device)
+                        dist.all_reduce(tt_, op=dist.ReduceOp.MAX)
+                        took[nm] = float(tt_.item())
+                    exchange_probe_us = {k_: round(v_ * 1e3, 1) for k_, v_ in took.items()}
+                    if took["p2p"] < took["nvls"]:
+                        nvls_region = None  # the buffer stays attached (the collectives check below still exercises it)
+                    del ar_probe
         comms.append(c)
     comm = comms[0] if comms else None
     algo = {"auto": pkg.ALL_REDUCE_AUTO, "nccl": pkg.ALL_REDUCE_NCCL, "one_shot": pkg.ALL_REDUCE_P2P_ONE_SHOT,
@@ -721,8 +745,8 @@ def main():
                     ar.launch_add(pkg.AllReduceArgs.of(dstc, mine))
                     torch.cuda.synchronize()
                     flags["all_reduce_add"] = bool(torch.equal(dstc, (tp * base + tp * (tp - 1) // 2 + base % 7).half()))
-                if nvls_region is not None:  # the same two through the in-switch reduction (src inside the multicast buffer)
-                    reg = nvls_region[:n_el]
+                if nvls_attached is not None:  # the same two through the in-switch reduction (src inside the multicast buffer)
+                    reg = nvls_attached[:n_el]
                     reg.copy_(mine)
                     dstc = torch.zeros_like(mine)
                     ar.launch(pkg.AllReduceArgs.of(dstc, reg))
@@ -845,7 +869,7 @@ def main():
         "metric": "layer_tokens_per_s", "value": T * args.steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic", "config": config,
-        "run": {"all_reduce": args.all_reduce if tp > 1 else None, "exchange": (("in-switch reduction (multimem.ld_reduce / multimem.st on an NVLink multicast buffer), " if nvls_region is not None else "peer-to-peer two-shot kernel, ")
+        "run": {"all_reduce": args.all_reduce if tp > 1 else None, "exchange_probe_us_per_all_reduce": exchange_probe_us, "exchange": (("in-switch reduction (multimem.ld_reduce / multimem.st on an NVLink multicast buffer), " if nvls_region is not None else "peer-to-peer two-shot kernel, ")
                                                                                + "zero-copy partials + residual folded into the all_reduce kernel" if direct else "staged") if tp > 1 else None,
                 "pipeline_chunks": pipeline if tp > 1 else None,
                 "attention": "fused flash-attention kernel behind attention::Args (the crate's operator chain is measured in other_configs)",
