@@ -364,8 +364,8 @@ int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out);
  * NVLink multicast object together with the same-sized buffers of every rank, `multicast` its multicast address (how the
  * object is made is the caller's business: the CUDA driver's cuMulticast* calls, or a library that wraps them).  The
  * first half of the buffer then serves as a zero-copy input region like the one above: an all_reduce (or all_reduce_add)
- * whose src lies there is summed inside the NVSwitch with multimem.ld_reduce and delivered with multimem.st; the second
- * half is scratch.  Needs ops_comm_p2p_attach first (the ranks synchronise through its flags).  Nulls detach.
+ * whose src lies there has its reduce-scatter half done inside the NVSwitch (multimem.ld_reduce); the second half is
+ * reserved.  Needs ops_comm_p2p_attach first (the ranks synchronise through its flags).  Nulls detach.
  * No counterpart in the crate. */
 int ops_comm_nvls_attach(ops_comm *c, void *multicast, void *local, size_t bytes);
 /* Test aid with no counterpart in the crate: a communicator of `group_size` ranks that all map this rank's own staging

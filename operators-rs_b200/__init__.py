@@ -710,7 +710,7 @@ class Comm:
 
     def nvls_attach(self, multicast_ptr, local_tensor):
         """ops_comm_nvls_attach: `local_tensor` (uint8, this rank's part of a buffer bound to an NVLink multicast object whose
-        multicast address is `multicast_ptr`) becomes [zero-copy input region | scratch] of the in-switch all_reduce.
+        multicast address is `multicast_ptr`) becomes [zero-copy input region | reserved] of the in-switch all_reduce.
         Returns the input region as a tensor view (first half)."""
         n = local_tensor.numel() * local_tensor.element_size()
         _check(lib().ops_comm_nvls_attach(self._h, ctypes.c_void_p(int(multicast_ptr)), ctypes.c_void_p(local_tensor.data_ptr()), ctypes.c_size_t(n)), False)

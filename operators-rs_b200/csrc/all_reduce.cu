@@ -212,6 +212,39 @@ __device__ __forceinline__ const uint4 *two_shot_in(const P2PKernelArgs &a, int 
   return reinterpret_cast<const uint4 *>(DIRECT ? region_direct(pb, a.region_bytes) + direct_off : region_in(pb, a.region_bytes, parity));
 }
 
+// Second half of the two-shot exchange: slice b of every other rank's reduced part, from that rank's "out" region to dst;
+// U vectors from every peer in flight per thread and trip.
+template <int P>
+__device__ __forceinline__ void two_shot_gather(const P2PKernelArgs &a, unsigned int parity, uint4 *__restrict__ dst, long long vecs, long long part_vecs,
+                                                long long s_lo, long long s_hi) {
+  constexpr int U = 8 / P;
+  for (long long v0 = s_lo + threadIdx.x; v0 < s_hi; v0 += (long long)U * blockDim.x) {
+    uint4 raw[U][P - 1];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+#pragma unroll
+      for (int i = 0; i < P - 1; ++i)
+        if (i < a.size - 1 && v < s_hi) {
+          int q = a.rank + 1 + i;  // rank r starts at peer r+1: spreads the load over the links
+          if (q >= a.size) q -= a.size;
+          if ((long long)q * part_vecs + v < vecs) raw[u][i] = ld_peer_16(reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity)) + v);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+#pragma unroll
+      for (int i = 0; i < P - 1; ++i)
+        if (i < a.size - 1 && v < s_hi) {
+          int q = a.rank + 1 + i;
+          if (q >= a.size) q -= a.size;
+          if ((long long)q * part_vecs + v < vecs) dst[(long long)q * part_vecs + v] = raw[u][i];
+        }
+    }
+  }
+}
+
 template <class T, bool DIRECT, bool ADD, int P>
 __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned int epoch, const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                               long long vecs, long long part_vecs, unsigned long long direct_off) {
@@ -287,32 +320,7 @@ __device__ __forceinline__ void two_shot_body(const P2PKernelArgs &a, unsigned i
     st_release_sys(&pf->reduced[a.rank][blockIdx.x], epoch);
   }
   if (!wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 3)) return;
-  // gather the other parts: U vectors from every peer in flight per thread and trip
-  for (long long v0 = s_lo + threadIdx.x; v0 < s_hi; v0 += (long long)U * blockDim.x) {
-    uint4 raw[U][P - 1];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + (long long)u * blockDim.x;
-#pragma unroll
-      for (int i = 0; i < P - 1; ++i)
-        if (i < a.size - 1 && v < s_hi) {
-          int q = a.rank + 1 + i;  // rank r starts at peer r+1: spreads the load over the links
-          if (q >= a.size) q -= a.size;
-          if ((long long)q * part_vecs + v < vecs) raw[u][i] = ld_peer_16(reinterpret_cast<const uint4 *>(region_out(a.peers[q], a.region_bytes, parity)) + v);
-        }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + (long long)u * blockDim.x;
-#pragma unroll
-      for (int i = 0; i < P - 1; ++i)
-        if (i < a.size - 1 && v < s_hi) {
-          int q = a.rank + 1 + i;
-          if (q >= a.size) q -= a.size;
-          if ((long long)q * part_vecs + v < vecs) dst[(long long)q * part_vecs + v] = raw[u][i];
-        }
-    }
-  }
+  two_shot_gather<P>(a, parity, dst, vecs, part_vecs, s_lo, s_hi);
 }
 
 template <class T, bool DIRECT, bool ADD, int P>
@@ -326,12 +334,13 @@ __global__ void __maxnreg__(104) all_reduce_two_shot_kernel(const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
-// In-switch reduction (NVLS).  The partial of every rank lies in the "in" half of a buffer bound to an NVLink multicast
+// In-switch reduction (NVLS).  The partial of every rank lies in the first half of a buffer bound to an NVLink multicast
 // object, at the same offset.  Rank r owns the r-th 1/p of the message: one `multimem.ld_reduce` per 16 bytes returns the
-// sum over ALL ranks, added up inside the NVSwitch (f32 accumulation), so a rank's links carry its own part once instead
-// of p-1 peer copies; the result (plus the replicated residual, ADD) goes out with one `multimem.st`, which the switch
-// delivers to the "out" half of every rank.  After a second flag round every rank copies "out" to dst from its own HBM.
-// Per rank and direction about S bytes cross NVLink, against 2 (p-1)/p S of the peer-to-peer two-shot kernel.
+// sum over ALL ranks, added up inside the NVSwitch (f32 accumulation), so the reduce-scatter half brings S/p bytes into a
+// rank instead of (p-1)/p S; the result (plus the replicated residual, ADD) goes to dst and to the rank's peer-mapped "out"
+// region, and the all-gather half is the two-shot kernel's: ordinary peer loads.  (A first form delivered the result with
+// `multimem.st` to every rank and copied it out locally: 147-150 us per 32 MiB at 2 and 4 ranks, 85-100 us of it in the
+// loop where 16-byte multicast stores and reducing loads queue behind each other, 20 us in the fence behind the stores.)
 // Flags and epochs are those of the peer-to-peer staging buffer (same-index CTAs meet pairwise, every wait bounded).
 // ------------------------------------------------------------------------------------------------
 template <class T> struct Multimem;
@@ -359,24 +368,17 @@ template <> struct Multimem<float> {
     return v;
   }
 };
-__device__ __forceinline__ void multimem_st_16(void *mc, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
-struct NvlsArgs {
-  char *mc_in, *mc_out;          // multicast addresses of the message inside the "in" and "out" halves
-  const char *local_out;         // this rank's copy of the same place in "out"
-};
-
-template <class T, bool ADD>
-__global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(const __grid_constant__ P2PKernelArgs a, const __grid_constant__ NvlsArgs nv,
-                                                                               uint4 *__restrict__ dst, long long vecs, long long part_vecs) {
+template <class T, bool ADD, int P>
+__global__ void __maxnreg__(104) all_reduce_nvls_kernel(const __grid_constant__ P2PKernelArgs a, const char *__restrict__ mc_in, uint4 *__restrict__ dst,
+                                                        long long vecs, long long part_vecs) {
   constexpr int U = 8;
   const unsigned int epoch = p2p_epoch(a.peers[a.rank]);
+  const unsigned int parity = epoch & 1u;
   const long long per = (part_vecs + gridDim.x - 1) / gridDim.x;
   const long long s_lo = (long long)blockIdx.x * per, s_hi = min(part_vecs, s_lo + per);
   const P2PFlags *own = reinterpret_cast<const P2PFlags *>(a.peers[a.rank]);
-  bool ok = true;
+  uint4 *mine_out = reinterpret_cast<uint4 *>(region_out(a.peers[a.rank], a.region_bytes, parity));
   // every rank's partial is in place (written by the kernel before this one on the same stream)
   __threadfence_system();
   __syncthreads();
@@ -384,19 +386,19 @@ __global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(c
     P2PFlags *pf = reinterpret_cast<P2PFlags *>(a.peers[threadIdx.x]);
     st_release_sys(&pf->ready[a.rank][blockIdx.x], epoch);
   }
-  ok = wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 4);
+  bool ok = wait_flags(&own->ready[0][blockIdx.x], a.size, epoch, a.status, 4);
   if (ok) {
+    // reduce-scatter half inside the switch: this rank's part, slice b
     const long long base = (long long)a.rank * part_vecs;
     const long long stop = min(s_hi, vecs - base);
-    const uint4 *mc_in = reinterpret_cast<const uint4 *>(nv.mc_in) + base;
-    uint4 *mc_out = reinterpret_cast<uint4 *>(nv.mc_out) + base;
+    const uint4 *in = reinterpret_cast<const uint4 *>(mc_in) + base;
     for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {
       uint4 sum[U], old[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long v = v0 + (long long)u * blockDim.x;
         if (v < stop) {
-          sum[u] = Multimem<T>::ld_reduce(mc_in + v);
+          sum[u] = Multimem<T>::ld_reduce(in + v);
           if constexpr (ADD) old[u] = dst[base + v];
         }
       }
@@ -411,8 +413,8 @@ __global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(c
             Acc8<T>::add(acc, sum[u]);
             r = Acc8<T>::pack(acc);
           }
-          multimem_st_16(mc_out + v, r);
-          dst[base + v] = r;  // this rank's own part needs no trip through "out"
+          mine_out[v] = r;
+          dst[base + v] = r;
         }
       }
     }
@@ -424,28 +426,8 @@ __global__ void __launch_bounds__(P2P_TWO_SHOT_THREADS) all_reduce_nvls_kernel(c
     }
     ok = wait_flags(&own->reduced[0][blockIdx.x], a.size, epoch, a.status, 5);
   }
-  if (ok) {
-    // every other part, slice b: from this rank's own copy of "out" to dst
-    const uint4 *lo = reinterpret_cast<const uint4 *>(nv.local_out);
-    for (int part = 0; part < a.size; ++part) {
-      if (part == a.rank) continue;
-      const long long base = (long long)part * part_vecs;
-      const long long stop = min(s_hi, vecs - base);
-      for (long long v0 = s_lo + threadIdx.x; v0 < stop; v0 += (long long)U * blockDim.x) {
-        uint4 r[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long v = v0 + (long long)u * blockDim.x;
-          if (v < stop) r[u] = ld_peer_16(lo + base + v);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long v = v0 + (long long)u * blockDim.x;
-          if (v < stop) dst[base + v] = r[u];
-        }
-      }
-    }
-  }
+  // all-gather half: ordinary peer loads from the other ranks' "out" regions, as in the two-shot kernel
+  if (ok) two_shot_gather<P>(a, parity, dst, vecs, part_vecs, s_lo, s_hi);
   __syncthreads();
   if (threadIdx.x == 0) p2p_launch_done(a.peers[a.rank]);
 }
@@ -738,13 +720,18 @@ static int launch_p2p(ops_comm *c, int algo, const void *src, void *dst, usz byt
     if (ctas < 1) ctas = 1;
     // in-switch reduction: the partial lies in the "in" half of the attached multicast buffer
     if (c->nvls_mc && (const char *)src >= c->nvls_local && (const char *)src + bytes <= c->nvls_local + c->nvls_region) {
-      const size_t off = (size_t)((const char *)src - c->nvls_local);
-      NvlsArgs nv;
-      nv.mc_in = c->nvls_mc + off;
-      nv.mc_out = c->nvls_mc + c->nvls_region + off;
-      nv.local_out = c->nvls_local + c->nvls_region + off;
-      if (add) all_reduce_nvls_kernel<T, true><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, nv, (uint4 *)dst, vecs, part);
-      else all_reduce_nvls_kernel<T, false><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, nv, (uint4 *)dst, vecs, part);
+      const char *mc_in = c->nvls_mc + (size_t)((const char *)src - c->nvls_local);
+#define OPS_NVLS(ADD, P) all_reduce_nvls_kernel<T, ADD, P><<<(unsigned)ctas, P2P_TWO_SHOT_THREADS, 0, s>>>(a, mc_in, (uint4 *)dst, vecs, part)
+      if (add) {
+        if (c->size <= 2) OPS_NVLS(true, 2);
+        else if (c->size <= 4) OPS_NVLS(true, 4);
+        else OPS_NVLS(true, 8);
+      } else {
+        if (c->size <= 2) OPS_NVLS(false, 2);
+        else if (c->size <= 4) OPS_NVLS(false, 4);
+        else OPS_NVLS(false, 8);
+      }
+#undef OPS_NVLS
       return check_launch("all_reduce(nvls)");
     }
     // zero-copy: the partial already lies in this rank's direct region (the producing kernel wrote it there)
@@ -842,7 +829,7 @@ OPS_API int ops_comm_p2p_direct(ops_comm *c, void **ptr_out, size_t *bytes_out) 
 // In-switch reduction: `local` is this rank's address of a buffer of `bytes` bytes that the caller has bound to an NVLink
 // multicast object together with the same-sized buffers of all ranks (same order of ranks as this communicator), `multicast`
 // its multicast address.  The first half is the zero-copy input region (what ops_comm_p2p_direct is to the peer-to-peer
-// kernels): an all_reduce whose src lies there is reduced inside the switch.  The second half is scratch.  Needs the
+// kernels): an all_reduce whose src lies there is reduced inside the switch.  The second half is reserved.  Needs the
 // peer-to-peer staging buffer attached as well (its flags synchronise the ranks).  Pass nulls to detach.
 OPS_API int ops_comm_nvls_attach(ops_comm *c, void *multicast, void *local, size_t bytes) {
   if (!c) return fail(OPS_ARGS_NOT_SUPPORT, "null communicator");
