@@ -815,6 +815,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_hist_kernel(const T *__
     hs.s = 1.f;
   }
   __syncthreads();
+  // Passes over a WINDOW of bins behind i0, k bins per thread (thread t: bins i0 + k t ..): the sum doubles from binade to
+  // binade, so the first binades end after a handful of bins — a pass that walked all 50176 bins to find a crossing a
+  // few bins ahead cost 17 us, and there are 5-12 of them per row.  The window starts at one bin per thread and grows
+  // (odd k: the threads' reads of `hist` stay on different banks) each time a window ends without leaving the binade.
+  int k = 1;
   while (true) {
     const int i0 = hs.i0;
     if (i0 >= nbins) break;
@@ -825,9 +830,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_hist_kernel(const T *__
     const float u_inv = __uint_as_float((uint32_t)(23 - ex + 127) << 23);
     const long long S = (long long)(s * u_inv);  // exact integer in [2^23, 2^24)
     if (tid == 0) hs.cross = 0x7fffffff;
+    const int win_end = (int)min((long long)nbins, (long long)i0 + (long long)SAMPLE_THREADS * k);
+    const int w_lo = (int)min((long long)win_end, (long long)i0 + (long long)tid * k), w_hi = min(win_end, w_lo + k);
     // this thread's bins as one composed pair
     Pair64 mine{0, 0};
-    for (int b = max(b_lo, i0); b < b_hi; ++b) {
+    for (int b = w_lo; b < w_hi; ++b) {
       const long long m = b == i0 ? rem0 : (long long)hist[b];
       if (m > 0) {
         long long q;
@@ -865,7 +872,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_hist_kernel(const T *__
     long long St = S + ((S & 1) ? before.d1 : before.d0);
     // second walk: the sum behind every bin, until a run leaves the binade
     long long cross_S = 0;
-    for (int b = max(b_lo, i0); b < b_hi; ++b) {
+    for (int b = w_lo; b < w_hi; ++b) {
       const long long m = b == i0 ? rem0 : (long long)hist[b];
       if (m > 0) {
         long long q;
@@ -884,8 +891,19 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_hist_kernel(const T *__
     }
     __syncthreads();
     const int cross = hs.cross;
-    if (cross == 0x7fffffff) break;
-    if (cross >= b_lo && cross < b_hi) {
+    if (cross == 0x7fffffff) {
+      // the whole window lies inside this binade: go on behind it with the same ulp and a wider window
+      if (win_end >= nbins) break;
+      if (w_hi == win_end && w_lo < w_hi) {  // the thread that owns the window's last bin knows the sum behind it
+        hs.s = (float)St * u;
+        hs.i0 = win_end;
+        hs.rem0 = (long long)hist[win_end];
+      }
+      k = k >= HIST_BPT ? HIST_BPT : min(HIST_BPT, 2 * k + 1);
+      __syncthreads();
+      continue;
+    }
+    if (cross >= w_lo && cross < w_hi) {
       // the owner finishes the crossing run through as many binades as it takes (its own walk stopped exactly there,
       // and no earlier bin crossed, so cross_S is the true sum in front of the run)
       const long long m = cross == i0 ? rem0 : (long long)hist[cross];
